@@ -1,0 +1,130 @@
+"""`create_mask` with the reference's contract (flash_sparse_attn/utils/mask.py:163-240), computed by the
+radix-select kernel behind `fdma_create_mask` instead of torch.topk + scatter_.
+
+Differences a caller can observe: equal bias values at the selection threshold are taken in ascending key
+order (torch.topk leaves that choice unspecified), and tensors must live on a CUDA device.
+"""
+import ctypes
+from typing import Optional
+
+import torch
+
+from .. import _lib
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    try:
+        return {torch.bfloat16: _lib.FDMA_BF16, torch.float16: _lib.FDMA_FP16, torch.float32: _lib.FDMA_FP32}[t.dtype]
+    except KeyError:
+        raise RuntimeError(f"create_mask: unsupported bias dtype {t.dtype}") from None
+
+
+def _launch(attention_bias, attention_mask, window_size, min_dtype, block_size, kind) -> torch.Tensor:
+    bias = attention_bias.detach()
+    if not bias.is_cuda:
+        raise RuntimeError("create_mask: attention_bias must be a CUDA tensor (this build has no CPU path)")
+    if bias.dim() != 4:
+        raise RuntimeError("create_mask: attention_bias must have 4 dimensions")
+    if bias.stride(-1) != 1:
+        bias = bias.contiguous()
+    pm = attention_mask
+    if pm is not None:
+        if pm.dtype != torch.bool:
+            pm = pm.to(torch.bool)
+        if pm.dim() != 4:
+            raise RuntimeError("create_mask: attention_mask must have 2 or 4 dimensions")
+        if pm.device != bias.device:
+            raise RuntimeError("create_mask: attention_mask must be on the same device as attention_bias")
+        if pm.stride(-1) != 1:
+            pm = pm.contiguous()
+    out_shape = torch.broadcast_shapes(bias.shape, pm.shape) if pm is not None else tuple(bias.shape)
+    keys = out_shape[-1]
+    if bias.shape[-1] != keys or (pm is not None and pm.shape[-1] != keys):
+        # key-dimension broadcast is legal in torch but never used by callers; materialise it
+        bias = bias.expand(*bias.shape[:-1], keys).contiguous()
+        if pm is not None:
+            pm = pm.expand(*pm.shape[:-1], keys).contiguous()
+    if kind == _lib.MASK_TOPK and window_size > keys:
+        raise RuntimeError("selected index k out of range")  # what torch.topk raises in the reference
+    out = torch.empty(out_shape, dtype=torch.bool, device=bias.device)
+    p = _lib.MaskParams()
+    p.bias, p.premask, p.out = bias.data_ptr(), (pm.data_ptr() if pm is not None else None), out.data_ptr()
+
+    def strides(t):
+        return [0 if t.shape[i] == 1 else t.stride(i) for i in range(3)]
+
+    p.bias_batch_stride, p.bias_head_stride, p.bias_row_stride = strides(bias)
+    if pm is not None:
+        p.pm_batch_stride, p.pm_head_stride, p.pm_row_stride = strides(pm)
+    p.out_b, p.out_h, p.out_rows, p.keys = out_shape
+    p.window = int(window_size) if window_size is not None else 0
+    p.dtype = _dtype_code(bias)
+    p.kind = kind
+    p.block_size = int(block_size) if block_size is not None else 0
+    p.min_value = float(min_dtype)
+    lib = _lib.load()
+    with torch.cuda.device(bias.device):
+        stream = torch.cuda.current_stream(bias.device).cuda_stream
+        _lib.check(lib.fdma_create_mask(ctypes.byref(p), stream), "fdma_create_mask")
+    return out
+
+
+def topk_mask(attention_bias, attention_mask, window_size, min_dtype, block_size=None, **kwargs):
+    """Top-`window_size` keys per row by bias value (reference: utils/mask.py:76-120)."""
+    if block_size is not None and block_size <= 0:
+        raise ValueError(f"block_size must be a positive integer, got {block_size}.")
+    return _launch(attention_bias, attention_mask, window_size, min_dtype, block_size, _lib.MASK_TOPK)
+
+
+def relu_mask(attention_bias, attention_mask, min_dtype, block_size=None, **kwargs):
+    """Keys whose (pre-masked) bias is positive (reference: utils/mask.py:123-159)."""
+    if block_size is not None and block_size <= 0:
+        raise ValueError(f"block_size must be a positive integer, got {block_size}.")
+    return _launch(attention_bias, attention_mask, 0, min_dtype, block_size, _lib.MASK_RELU)
+
+
+def topk_indices(attention_bias: torch.Tensor, window_size: int, **kwargs) -> torch.Tensor:
+    """Sorted indices of the top-`window_size` keys of a (batch, kv_heads, key_len) bias
+    (reference: utils/mask.py:20-44), derived from the selection kernel's mask."""
+    b3 = attention_bias.detach()
+    mask = _launch(b3.unsqueeze(2), None, window_size, float("-inf"), None, _lib.MASK_TOPK).squeeze(2)
+    idx = torch.nonzero(mask, as_tuple=False)[:, -1]
+    return idx.view(*b3.shape[:-1], window_size)
+
+
+def create_mask(
+    attention_bias: torch.Tensor,
+    attention_mask: Optional[torch.Tensor],
+    batch_size: int,
+    query_len: int,
+    key_len: int,
+    window_size: int,
+    min_dtype: float,
+    block_size: Optional[int] = None,
+    type: str = "topk",
+) -> torch.Tensor:
+    """Bool attention mask from the bias; same arguments and result shape as the reference's create_mask.
+
+    attention_bias ({B|1}, {H|Hk|1}, {Sq|1}, Sk); attention_mask None, 4-D broadcastable to the bias, or
+    2-D (B, Sk) / (B, Sq) padding mask (left-padded with True up to key_len). type "topk" keeps the
+    window_size largest entries per row (never an entry equal to min_dtype); "relu" keeps bias > 0.
+    block_size > 1 then replaces each block of keys by its majority vote.
+    """
+    if attention_mask is not None and attention_mask.dim() == 2:
+        if attention_mask.shape[-1] == key_len:
+            attention_mask = attention_mask.view(batch_size, 1, 1, key_len)
+        elif attention_mask.shape[-1] == query_len:
+            pad_len = key_len - query_len
+            attention_mask = attention_mask.view(batch_size, 1, 1, query_len)
+            if pad_len > 0:
+                attention_mask = torch.nn.functional.pad(attention_mask, [pad_len, 0], value=True)
+        else:
+            raise ValueError(
+                f"attention_mask shape {attention_mask.shape} is not compatible with key_len {key_len} "
+                f"or query_len {query_len}."
+            )
+    if type == "topk":
+        return topk_mask(attention_bias, attention_mask, window_size, min_dtype, block_size)
+    if type == "relu":
+        return relu_mask(attention_bias, attention_mask, min_dtype, block_size)
+    raise ValueError(f"Unsupported mask type: {type}. Supported types are 'topk' and 'relu'.")

@@ -1,0 +1,167 @@
+/*
+ * fdma.h -- C ABI of libfdma_sm100.so: dynamic-mask attention for NVIDIA B200 (sm_100a).
+ *
+ * The library replaces the pybind11 module `flash_sparse_attn_cuda` of SmallDoges/flash-dmattn
+ * (csrc/flash_sparse_attn/flash_api.cpp:1270-1276: `fwd`, `bwd`) and the ATen calls inside
+ * flash_sparse_attn/utils/mask.py:76-120 (`topk_mask`) with plain-C entry points:
+ * POD parameter blocks, raw device pointers, element strides, an explicit CUDA stream.
+ *
+ * Rules common to every entry point
+ *  - Nothing here allocates or frees device memory unless its comment says so. The caller owns
+ *    inputs, outputs and the scratch buffer (`workspace`), whose size comes from the matching
+ *    *_workspace_bytes() call, and keeps them alive until the stream work has finished.
+ *  - All work is enqueued on `stream` (a cudaStream_t passed as void*); no hidden synchronisation.
+ *  - Return value: 0 on success, a negative fdma_status, or a positive cudaError_t value.
+ *    fdma_strerror() turns either into text. Nothing throws and nothing calls exit().
+ *  - Strides are in ELEMENTS of the tensor's dtype. The innermost (head-dim / key) stride is 1.
+ *    A stride of 0 means "broadcast along that dimension" (the reference does the same,
+ *    flash_api.cpp:79-82, :90-91).
+ */
+#ifndef FDMA_H_
+#define FDMA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FDMA_VERSION 10000 /* 1.0.0 */
+
+enum fdma_dtype { FDMA_BF16 = 0, FDMA_FP16 = 1, FDMA_FP32 = 2 };
+
+enum fdma_status {
+  FDMA_OK = 0,
+  FDMA_ERR_BAD_ARG = -1,       /* NULL pointer, negative size, inconsistent heads ...           */
+  FDMA_ERR_UNSUPPORTED = -2,   /* head dim > 256 or not a multiple of 8, dtype not handled ...  */
+  FDMA_ERR_WORKSPACE = -3,     /* workspace missing or smaller than *_workspace_bytes()         */
+  FDMA_ERR_ARCH = -4,          /* device is not compute capability 10.x                         */
+  FDMA_ERR_DRIVER = -5,        /* tensor-map encode entry point unavailable                     */
+  FDMA_ERR_TIMEOUT = -6,       /* a bounded in-kernel wait gave up (reported by fdma_last_kernel_status) */
+  FDMA_ERR_TOO_LARGE = -7      /* static-scratch variant: problem exceeds the compiled-in limit  */
+};
+
+/* Which kernel family the launcher picks. AUTO: tcgen05/TMA kernels where shape and alignment
+ * allow, the CUDA-core kernels otherwise. The other two values force one family (tests use them);
+ * forcing TCGEN05 on an unsupported shape returns FDMA_ERR_UNSUPPORTED. */
+enum fdma_path { FDMA_PATH_AUTO = 0, FDMA_PATH_SIMT = 1, FDMA_PATH_TCGEN05 = 2 };
+
+/*
+ * Forward: O = softmax(scale * Q K^T + bias, masked) V, LSE = logsumexp of the masked scores.
+ * Replaces `mha_fwd` (flash_api.cpp:351-554) + `set_params_fprop` (:24-153) and the kernels behind
+ * `run_mha_fwd` (:251-267). Tensor meaning follows Flash_fwd_params (src/flash.h:80-160):
+ *   q (B,Sq,H,d)  k,v (B,Sk,Hk,d)  out (B,Sq,H,d)  lse (B,H,Sq) fp32 contiguous
+ *   mask: bool bytes ({B|1},{H|Hk|1},{Sq|1},Sk...) , bias: dtype of q, same broadcast rules.
+ * mask/bias rows must be readable up to round_up(Sk,128) keys (the Python layer pads them the way
+ * flash_sparse_attn_interface.py:420-430 does); keys >= Sk are ignored.
+ * Causal alignment is bottom-right: key k is visible to query q iff k <= q + Sk - Sq (src/mask.h:39).
+ * Rows with no visible key give O = 0 and LSE = +inf (src/softmax.h:211-214).
+ */
+typedef struct fdma_fwd_params {
+  const void* q;
+  const void* k;
+  const void* v;
+  const void* mask; /* may be NULL: nothing masked  */
+  const void* bias; /* may be NULL: zero bias       */
+  void* out;
+  float* lse;
+  int64_t q_batch_stride, q_row_stride, q_head_stride;
+  int64_t k_batch_stride, k_row_stride, k_head_stride;
+  int64_t v_batch_stride, v_row_stride, v_head_stride;
+  int64_t o_batch_stride, o_row_stride, o_head_stride;
+  int64_t mask_batch_stride, mask_head_stride, mask_row_stride;
+  int64_t bias_batch_stride, bias_head_stride, bias_row_stride;
+  int32_t b, seqlen_q, seqlen_k, h, h_k, h_mask, h_bias, d;
+  int32_t dtype;     /* fdma_dtype of q/k/v/out/bias: BF16 or FP16 */
+  int32_t is_causal; /* ignored (treated as 0) when seqlen_q == 1, flash_api.cpp:441 */
+  float softmax_scale;
+  int32_t path;      /* fdma_path */
+  void* workspace;
+  size_t workspace_bytes;
+} fdma_fwd_params;
+
+size_t fdma_fwd_workspace_bytes(const fdma_fwd_params* p);
+int fdma_fwd(const fdma_fwd_params* p, void* stream);
+
+/*
+ * Backward: dQ, dK, dV and dBias for the forward above, given dOut, Out and LSE.
+ * Replaces `mha_bwd` (flash_api.cpp:792-1050) + `set_params_dgrad` (:155-249), the three launches of
+ * run_flash_bwd_seqk_parallel (src/flash_bwd_launch_template.h:71-117) and the at::sum_out
+ * reductions over the query-head group and broadcast dimensions (flash_api.cpp:1027-1047), which
+ * happen inside the kernels here.
+ *   dq like q, dk/dv like k/v (already summed over the H/Hk query heads that share a kv head),
+ *   dbias has the SHAPE OF BIAS (strides given), already summed over every dimension in which
+ *   bias is broadcast (batch, head group, query).  dbias may be NULL (no bias gradient wanted).
+ * Outputs are overwritten; they need not be zeroed by the caller.
+ */
+typedef struct fdma_bwd_params {
+  fdma_fwd_params f; /* q,k,v,mask,bias,out,lse + geometry exactly as given to fdma_fwd */
+  const void* dout;  /* (B,Sq,H,d) */
+  int64_t do_batch_stride, do_row_stride, do_head_stride;
+  void* dq;
+  void* dk;
+  void* dv;
+  void* dbias; /* may be NULL */
+  int64_t dq_batch_stride, dq_row_stride, dq_head_stride;
+  int64_t dk_batch_stride, dk_row_stride, dk_head_stride;
+  int64_t dv_batch_stride, dv_row_stride, dv_head_stride;
+  int64_t dbias_batch_stride, dbias_head_stride, dbias_row_stride;
+  int32_t dbias_b, dbias_h, dbias_rows; /* extents of dbias dims 0..2 (1 where bias is broadcast) */
+  int32_t dbias_keys;                   /* extent of the key dimension of dbias (>= Sk)          */
+  int32_t deterministic;                /* accepted for API parity (flash_api.cpp:809); dQ uses fp32 atomics either way */
+  int32_t reserved;
+} fdma_bwd_params;
+
+size_t fdma_bwd_workspace_bytes(const fdma_bwd_params* p);
+int fdma_bwd(const fdma_bwd_params* p, void* stream);
+
+/*
+ * create_mask: bool mask of the `window` largest bias entries along the key dimension of each row.
+ * Replaces `topk_mask` / `relu_mask` / `block_smooth` of flash_sparse_attn/utils/mask.py:47-160
+ * (torch.topk + scatter_ there). Output rows follow the broadcast of bias and pre-mask shapes.
+ *   value(row,k) = premask(row,k) ? bias(row,k) : min_value
+ *   kind TOPK : out = 1 for the `window` largest values of the row, except where value == min_value
+ *               (mask.py:102-110). Equal values at the selection threshold are taken in ascending
+ *               key order.
+ *   kind RELU : out = value > 0 (mask.py:147-149)
+ *   block_size > 1: afterwards each block of `block_size` keys (and the shorter tail block) is set
+ *               to "more than half of the block was selected" (mask.py:47-73).
+ * Rows are indexed (b, h, r) over out_b x out_h x out_rows; bias / premask strides may be 0.
+ */
+enum fdma_mask_kind { FDMA_MASK_TOPK = 0, FDMA_MASK_RELU = 1 };
+
+typedef struct fdma_mask_params {
+  const void* bias;
+  const void* premask; /* bool bytes, may be NULL */
+  void* out;           /* bool bytes, contiguous (out_b,out_h,out_rows,keys) */
+  int64_t bias_batch_stride, bias_head_stride, bias_row_stride;
+  int64_t pm_batch_stride, pm_head_stride, pm_row_stride;
+  int32_t out_b, out_h, out_rows, keys;
+  int32_t window;
+  int32_t dtype;      /* fdma_dtype of bias: BF16, FP16 or FP32 */
+  int32_t kind;       /* fdma_mask_kind */
+  int32_t block_size; /* 0 or 1: no smoothing */
+  float min_value;    /* the caller's min_dtype (mask.py:171) */
+} fdma_mask_params;
+
+int fdma_create_mask(const fdma_mask_params* p, void* stream);
+
+/* Text for a status returned by any call above (fdma_status or cudaError_t). Never NULL. */
+const char* fdma_strerror(int status);
+
+/* FDMA_VERSION the library was built from. */
+int fdma_version(void);
+
+/*
+ * The tcgen05 kernels bound every wait on an mbarrier; a wait that runs out records a code in a
+ * per-device status word instead of hanging. This call copies the word to the host (it
+ * synchronises `stream`), clears it, and returns 0 or FDMA_ERR_TIMEOUT. `detail`, if not NULL,
+ * receives the raw code (which wait gave up).
+ */
+int fdma_last_kernel_status(void* stream, int32_t* detail);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FDMA_H_ */

@@ -1,0 +1,106 @@
+"""Host-side logic of the operator layer that needs no GPU: argument checks, stride handling, padding rules,
+shape inference for torch.compile, and the 2-D padding-mask reshape of create_mask."""
+import pytest
+import torch
+
+import flash_sparse_attn
+from flash_sparse_attn import flash_sparse_attn_interface as iface
+from flash_sparse_attn.utils import mask as mask_mod
+
+
+def test_public_names_and_signature():
+    import inspect
+
+    sig = inspect.signature(flash_sparse_attn.flash_sparse_attn_func)
+    assert list(sig.parameters) == [
+        "query", "key", "value", "attn_mask", "attn_bias", "softmax_scale", "is_causal", "softcap",
+        "deterministic", "return_attn_probs",
+    ]
+    assert all(p.default is None for n, p in sig.parameters.items() if n not in ("query", "key", "value"))
+    sig = inspect.signature(mask_mod.create_mask)
+    assert list(sig.parameters) == [
+        "attention_bias", "attention_mask", "batch_size", "query_len", "key_len", "window_size", "min_dtype",
+        "block_size", "type",
+    ]
+    assert sig.parameters["type"].default == "topk"
+    assert hasattr(torch.ops.flash_sparse_attn, "_flash_sparse_attn_forward")
+    assert hasattr(torch.ops.flash_sparse_attn, "_flash_sparse_attn_backward")
+
+
+def test_cpu_tensors_are_rejected_loudly():
+    q = torch.randn(1, 8, 2, 64, dtype=torch.bfloat16)
+    with pytest.raises((RuntimeError, NotImplementedError)):
+        flash_sparse_attn.flash_sparse_attn_func(q, q, q)
+    with pytest.raises(RuntimeError):
+        mask_mod.create_mask(torch.randn(1, 1, 1, 16), None, 1, 1, 16, 4, -1e30)
+
+
+def test_input_checks():
+    dev_q = torch.empty(2, 16, 4, 64, dtype=torch.bfloat16, device="meta")
+
+    class FakeCuda:  # _check_inputs only looks at metadata; emulate is_cuda on meta tensors
+        pass
+
+    def chk(q, k, v, mask=None, bias=None):
+        orig = torch.Tensor.is_cuda
+        try:
+            torch.Tensor.is_cuda = property(lambda self: True)
+            iface._check_inputs(q, k, v, mask, bias)
+        finally:
+            torch.Tensor.is_cuda = orig
+
+    k = torch.empty(2, 32, 2, 64, dtype=torch.bfloat16, device="meta")
+    chk(dev_q, k, k)
+    with pytest.raises(RuntimeError, match="divide"):
+        chk(dev_q, torch.empty(2, 32, 3, 64, dtype=torch.bfloat16, device="meta"),
+            torch.empty(2, 32, 3, 64, dtype=torch.bfloat16, device="meta"))
+    with pytest.raises(RuntimeError, match="multiple of 8"):
+        q2 = torch.empty(2, 16, 4, 60, dtype=torch.bfloat16, device="meta")
+        k2 = torch.empty(2, 32, 2, 60, dtype=torch.bfloat16, device="meta")
+        chk(q2, k2, k2)
+    with pytest.raises(RuntimeError, match="fp16 and bf16"):
+        chk(dev_q.float(), k.float(), k.float())
+    with pytest.raises(RuntimeError, match="bool"):
+        chk(dev_q, k, k, mask=torch.empty(2, 2, 16, 128, dtype=torch.uint8, device="meta"))
+    with pytest.raises(RuntimeError, match="key dimension"):
+        chk(dev_q, k, k, mask=torch.empty(2, 2, 16, 32, dtype=torch.bool, device="meta"))
+    with pytest.raises(RuntimeError, match="head dimension"):
+        chk(dev_q, k, k, bias=torch.empty(2, 3, 16, 128, dtype=torch.bfloat16, device="meta"))
+    with pytest.raises(RuntimeError, match="same dtype"):
+        chk(dev_q, k, k, bias=torch.empty(2, 2, 16, 128, dtype=torch.float16, device="meta"))
+    chk(dev_q, k, k, mask=torch.empty(1, 1, 1, 128, dtype=torch.bool, device="meta"),
+        bias=torch.empty(2, 4, 16, 128, dtype=torch.bfloat16, device="meta"))
+
+
+def test_stride_helpers():
+    t = torch.empty(2, 16, 4, 64)
+    assert iface._bsh(t) == (16 * 4 * 64, 4 * 64, 64)
+    tt = torch.empty(2, 4, 16, 64).transpose(1, 2)  # (B,S,H,d) view of a (B,H,S,d) buffer
+    assert iface._bsh(tt) == (4 * 16 * 64, 64, 16 * 64)
+    m = torch.empty(2, 1, 1, 128, dtype=torch.bool)
+    assert iface._mb_strides(m) == (128, 0, 0)
+    e = torch.empty(1, 2, 1, 128).expand(3, 2, 16, 128)
+    assert iface._mb_strides(e) == (0, 128, 0)
+    assert iface._mb_strides(None) == (0, 0, 0)
+    assert iface.round_multiple(129, 128) == 256 and iface.round_multiple(128, 128) == 128
+
+
+def test_fake_kernels_infer_shapes():
+    q = torch.empty(2, 16, 4, 64, dtype=torch.bfloat16, device="meta")
+    k = torch.empty(2, 32, 2, 64, dtype=torch.bfloat16, device="meta")
+    out, lse, p = torch.ops.flash_sparse_attn._flash_sparse_attn_forward(q, k, k, None, None, 0.125, True, 0.0, False)
+    assert out.shape == q.shape and lse.shape == (2, 4, 16) and lse.dtype == torch.float32 and p.numel() == 0
+    sd = torch.ops.flash_sparse_attn._flash_sparse_attn_backward(
+        q, q, k, k, None, None, out, lse, torch.empty_like(q), torch.empty_like(k), torch.empty_like(k), None,
+        0.125, True, 0.0, False)
+    assert sd.shape == (2, 4, 128)
+
+
+def test_create_mask_argument_errors():
+    bias = torch.randn(2, 1, 1, 16)
+    with pytest.raises(ValueError, match="not compatible"):
+        mask_mod.create_mask(bias, torch.ones(2, 7, dtype=torch.bool), 2, 4, 16, 4, -1e30)
+    with pytest.raises(ValueError, match="Unsupported mask type"):
+        mask_mod.create_mask(bias, None, 2, 4, 16, 4, -1e30, type="sigmoid")
+    with pytest.raises(ValueError, match="block_size"):
+        mask_mod.create_mask(bias, None, 2, 4, 16, 4, -1e30, block_size=0)
