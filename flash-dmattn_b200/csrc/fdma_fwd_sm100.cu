@@ -574,26 +574,24 @@ int launch(const fdma_fwd_params& p, const FwdPlan& pl, cudaStream_t stream) {
   using L = Smem<D>;
   FwdKernelParams kp;
   const uint32_t box[4] = {64, 1, static_cast<uint32_t>(kBM), 1};
-  {
-    const uint64_t dims[4] = {static_cast<uint64_t>(p.d), static_cast<uint64_t>(p.h),
-                              static_cast<uint64_t>(p.seqlen_q), static_cast<uint64_t>(p.b)};
-    const uint64_t str[3] = {static_cast<uint64_t>(p.q_head_stride) * 2, static_cast<uint64_t>(p.q_row_stride) * 2,
-                             static_cast<uint64_t>(p.q_batch_stride) * 2};
-    int st = encode_tmap_4d(&kp.tm_q, p.q, 2, dims, str, box);
-    if (st) return st;
-  }
-  {
-    const uint64_t dims[4] = {static_cast<uint64_t>(p.d), static_cast<uint64_t>(p.h_k),
-                              static_cast<uint64_t>(p.seqlen_k), static_cast<uint64_t>(p.b)};
-    const uint64_t sk[3] = {static_cast<uint64_t>(p.k_head_stride) * 2, static_cast<uint64_t>(p.k_row_stride) * 2,
-                            static_cast<uint64_t>(p.k_batch_stride) * 2};
-    int st = encode_tmap_4d(&kp.tm_k, p.k, 2, dims, sk, box);
-    if (st) return st;
-    const uint64_t sv[3] = {static_cast<uint64_t>(p.v_head_stride) * 2, static_cast<uint64_t>(p.v_row_stride) * 2,
-                            static_cast<uint64_t>(p.v_batch_stride) * 2};
-    st = encode_tmap_4d(&kp.tm_v, p.v, 2, dims, sv, box);
-    if (st) return st;
-  }
+  // Tensor maps over (d, heads, rows, batch). A dimension of extent 1 is never stepped over, so whatever stride
+  // the caller reports for it is replaced by a dense one (the encoder wants non-zero multiples of 16 bytes).
+  auto encode = [&](CUtensorMap* tm, const void* base, int heads, int rows, int64_t sb, int64_t sr, int64_t sh) {
+    if (heads == 1) sh = p.d;
+    if (rows == 1) sr = static_cast<int64_t>(heads) * p.d;
+    if (p.b == 1) sb = static_cast<int64_t>(rows) * heads * p.d;
+    const uint64_t dims[4] = {static_cast<uint64_t>(p.d), static_cast<uint64_t>(heads), static_cast<uint64_t>(rows),
+                              static_cast<uint64_t>(p.b)};
+    const uint64_t str[3] = {static_cast<uint64_t>(sh) * 2, static_cast<uint64_t>(sr) * 2,
+                             static_cast<uint64_t>(sb) * 2};
+    return encode_tmap_4d(tm, base, 2, dims, str, box);
+  };
+  int st = encode(&kp.tm_q, p.q, p.h, p.seqlen_q, p.q_batch_stride, p.q_row_stride, p.q_head_stride);
+  if (st) return st;
+  st = encode(&kp.tm_k, p.k, p.h_k, p.seqlen_k, p.k_batch_stride, p.k_row_stride, p.k_head_stride);
+  if (st) return st;
+  st = encode(&kp.tm_v, p.v, p.h_k, p.seqlen_k, p.v_batch_stride, p.v_row_stride, p.v_head_stride);
+  if (st) return st;
   kp.mask = static_cast<const uint8_t*>(p.mask);
   kp.bias = p.bias;
   kp.out = p.out;
@@ -655,12 +653,16 @@ bool tc_fwd_supported(const fdma_fwd_params& p) {
   const void* ptrs[4] = {p.q, p.k, p.v, p.out};
   for (const void* x : ptrs)
     if (!aligned16(x)) return false;
-  const int64_t strides[12] = {p.q_batch_stride, p.q_row_stride, p.q_head_stride, p.k_batch_stride,
-                               p.k_row_stride,   p.k_head_stride, p.v_batch_stride, p.v_row_stride,
-                               p.v_head_stride,  p.o_batch_stride, p.o_row_stride,  p.o_head_stride};
-  for (int64_t s : strides)
-    if (s % 8 != 0 || s < 0) return false;
-  if (p.q_row_stride == 0 || p.k_row_stride == 0 || p.v_row_stride == 0) return false;
+  auto ok_strides = [&](int heads, int rows, int64_t sb, int64_t sr, int64_t sh) {
+    if (heads > 1 && (sh <= 0 || sh % 8)) return false;
+    if (rows > 1 && (sr <= 0 || sr % 8)) return false;
+    if (p.b > 1 && (sb <= 0 || sb % 8)) return false;
+    return true;
+  };
+  if (!ok_strides(p.h, p.seqlen_q, p.q_batch_stride, p.q_row_stride, p.q_head_stride)) return false;
+  if (!ok_strides(p.h_k, p.seqlen_k, p.k_batch_stride, p.k_row_stride, p.k_head_stride)) return false;
+  if (!ok_strides(p.h_k, p.seqlen_k, p.v_batch_stride, p.v_row_stride, p.v_head_stride)) return false;
+  if (p.o_batch_stride % 8 || p.o_row_stride % 8 || p.o_head_stride % 8) return false;
   // 16-byte vector loads of bias (2-byte elements) and mask (bytes)
   if (p.bias) {
     if (!aligned16(p.bias)) return false;

@@ -2,8 +2,9 @@
 oracle on identical seeded inputs.
 
 Tolerances (bf16/fp16 inputs, fp32 oracle): max-abs <= 2e-2 and mean-abs <= 2e-3. dK, dV and dBias are sums over
-many queries and reach magnitudes where ONE bf16 rounding of the exact result already exceeds 2e-2
-(`floor` = |ref - bf16(ref)|); for those three the max-abs bound is 2e-2 + 3 * floor_max, mean-abs stays 2e-3."""
+many queries and reach magnitudes where ONE bf16 rounding of the exact result already exceeds the bound
+(`floor` = |ref - bf16(ref)|, the error of a perfect kernel that returns bf16); for those three the bounds are
+max-abs <= 2e-2 + 3 * floor_max and mean-abs <= 2e-3 + 2 * floor_mean."""
 import itertools
 
 import pytest
@@ -83,7 +84,8 @@ def check(name, got, ref, dtype, reduced=False):
     assert torch.isfinite(got.float()).all(), f"{name}: non-finite values"
     lim = MAX_ABS + (3.0 * r["floor_max_abs"] if reduced else 0.0)
     assert r["max_abs"] <= lim, f"{name}: max-abs {r['max_abs']:.4g} > {lim:.4g} (floor {r['floor_max_abs']:.3g})"
-    assert r["mean_abs"] <= MEAN_ABS, f"{name}: mean-abs {r['mean_abs']:.4g}"
+    mlim = MEAN_ABS + (2.0 * r["floor_mean_abs"] if reduced else 0.0)
+    assert r["mean_abs"] <= mlim, f"{name}: mean-abs {r['mean_abs']:.4g} > {mlim:.4g} (floor {r['floor_mean_abs']:.3g})"
 
 
 def compare_all(case, is_causal, dtype, scale=None, fwd_only=False):
