@@ -1,7 +1,861 @@
-// placeholder until the tcgen05 backward lands: declines every shape so the launcher uses the CUDA-core path
+// Backward dynamic-mask attention for sm_100a (head dim 128): dQ, dK, dV and dBias from dO, O, LSE.
+//
+// Math of the reference's compute_dq_dk_dv_1colblock (csrc/flash_sparse_attn/src/flash_bwd_kernel.h:79-1142):
+//   P = exp(S - LSE), dP = dO V^T, dS = P o (dP - D), D = rowsum(dO o O),
+//   dV = P^T dO, dK = scale dS^T Q, dQ = scale dS K, dBias = dS,
+// laid out for tcgen05 instead of mma.sync. One CTA owns one tile of 128 keys of one (batch, kv head) and walks
+// over every 64-row query tile of every query head that shares the kv head, so dK, dV and dBias leave the CTA
+// already summed over the head group (the reference writes per-query-head temporaries and reduces them on the
+// host with at::sum_out, flash_api.cpp:970-983, :1027-1047). Everything is computed TRANSPOSED so that the
+// softmax threads own one KEY each (TMEM lane = key):
+//   St  = K Q^T        (128 keys x 64 queries, SS MMA)        dPt = V dO^T        (SS MMA)
+//   P^T, dS^T          written back into the St / dPt columns as 16-bit, used as the A operand (from TMEM) of
+//   dV += P^T dO,  dK += dS^T Q   (B = dO / Q tiles read MN-major from the same shared-memory copy)
+//   dQ^T = K^T dS^T    (A = K MN-major, B = dS^T staged in shared memory), added to an fp32 dQ buffer with
+//                      red.global.add by a dedicated warpgroup (lane = head-dim index -> 128-byte coalesced)
+// Query-broadcast bias gives dBias = column sums of dS: one fp32 register per softmax thread for the whole CTA.
+//
+// Warps: 0 TMA producer | 1 MMA issuer | 4-7, 8-11 softmax (query columns 0-31 / 32-63) | 12-15 dQ writer.
+// TMEM: St[2] 2x64 | dPt 64 | dQ^T 64 | dV 128 | dK 128 = 512 columns.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <math_constants.h>
+
+#include <algorithm>
+
 #include "fdma_internal.h"
+#include "fdma_ptx.cuh"
+
 namespace fdma {
-bool tc_bwd_supported(const fdma_bwd_params&) { return false; }
-size_t tc_bwd_workspace_bytes(const fdma_bwd_params&) { return 0; }
-int tc_bwd(const fdma_bwd_params&, cudaStream_t) { return FDMA_ERR_UNSUPPORTED; }
+namespace {
+
+constexpr int kD = 128;
+constexpr int kBN = 128;  // keys per CTA
+constexpr int kBM = 64;   // query rows per step
+constexpr int kQStages = 3;
+constexpr int kThreads = 512;
+constexpr int kMaxAct = 4096;  // bytes of the per-CTA tile-activity table
+constexpr float kLog2e = 1.4426950408889634f;
+
+enum DbiasMode { kDbNone = 0, kDbColsum = 1, kDbDirect = 2, kDbAtomic = 3 };
+
+enum WaitCode {
+  kWaitKv = 201, kWaitQdoEmpty = 202, kWaitQdoFull = 203, kWaitSFull = 204, kWaitDpFull = 205, kWaitPds = 206,
+  kWaitDqFull = 207, kWaitDqEmpty = 208, kWaitDsEmpty = 209, kWaitFinal = 210
+};
+
+struct BwdKernelParams {
+  CUtensorMap tm_q, tm_do, tm_k, tm_v;  // q/do: 64-row boxes, k/v: 128-row boxes
+  const uint8_t* mask;
+  const void* bias;
+  const float* lse2;   // (B,H,Sq_r) LSE * log2(e); +inf for empty and padded rows
+  const float* dsum;   // (B,H,Sq_r) D = rowsum(dO o O)
+  float* dq_acc;       // (B,Sq,H,128) fp32, zeroed by the launcher
+  void* dk;
+  void* dv;
+  void* dbias;         // direct / column-sum modes: the output tensor
+  float* dbias_acc;    // atomic mode: fp32 buffer (dbias_b, dbias_h, dbias_rows, dbias_keys), zeroed
+  const uint8_t* act;  // per-query mask: activity bytes [B][h_mask][ceil(Sq/128)][ceil(Sk/128)], else null
+  int* status;
+  int64_t mask_batch_stride, mask_head_stride, mask_row_stride;
+  int64_t bias_batch_stride, bias_head_stride, bias_row_stride;
+  int64_t dk_batch_stride, dk_row_stride, dk_head_stride;
+  int64_t dv_batch_stride, dv_row_stride, dv_head_stride;
+  int64_t dbias_batch_stride, dbias_head_stride, dbias_row_stride;
+  int b, seqlen_q, seqlen_k, sq_r, h, h_k, h_mask, h_bias;
+  int dbias_b, dbias_h, dbias_rows, dbias_keys, dbias_mode;
+  int is_causal;
+  float scale_log2, scale;
+};
+
+struct SmemB {
+  static constexpr int kKOff = 0;
+  static constexpr int kVOff = kBN * kD * 2;                       // 32 KB
+  static constexpr int kQdoOff = 2 * kBN * kD * 2;                 // 64 KB
+  static constexpr int kQBytes = kBM * kD * 2;                     // 16 KB
+  static constexpr int kStageBytes = 2 * kQBytes;                  // Q then dO
+  static constexpr int kDsOff = kQdoOff + kQStages * kStageBytes;  // 160 KB
+  static constexpr int kDsBytes = kBN * kBM * 2;                   // 16 KB
+  static constexpr int kActOff = kDsOff + 2 * kDsBytes;            // 192 KB
+  static constexpr int kRedOff = kActOff + kMaxAct;
+  static constexpr int kBarOff = kRedOff + kBN * 4;
+  static constexpr int kNumBars = 1 + 2 * kQStages + 2 + 1 + 1 + 1 + 1 + 2 + 1;
+  static constexpr int kMiscOff = kBarOff + kNumBars * 8;
+  static constexpr int kTotal = kMiscOff + 32;
+  static constexpr int kAlloc = kTotal + 1024;
+};
+
+// D = rowsum(dO o O), LSE in log2 units; rows [Sq, Sq_r) are padding (+inf / 0). One warp per (b, h, row).
+template <bool kBf16>
+__global__ void bwd_prep_kernel(const void* __restrict__ out, const void* __restrict__ dout,
+                                const float* __restrict__ lse, float* __restrict__ lse2, float* __restrict__ dsum,
+                                int B, int H, int Sq, int Sq_r, int d, int64_t ob, int64_t orow, int64_t oh,
+                                int64_t gb, int64_t grow, int64_t gh) {
+  const int lane = threadIdx.x & 31;
+  const int64_t w = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
+  const int64_t total = static_cast<int64_t>(B) * H * Sq_r;
+  if (w >= total) return;
+  const int q = static_cast<int>(w % Sq_r);
+  const int h = static_cast<int>((w / Sq_r) % H);
+  const int b = static_cast<int>(w / (static_cast<int64_t>(Sq_r) * H));
+  if (q >= Sq) {
+    if (lane == 0) {
+      lse2[w] = CUDART_INF_F;
+      dsum[w] = 0.f;
+    }
+    return;
+  }
+  const uint16_t* o = reinterpret_cast<const uint16_t*>(out) + b * ob + q * orow + h * oh;
+  const uint16_t* g = reinterpret_cast<const uint16_t*>(dout) + b * gb + q * grow + h * gh;
+  float acc = 0.f;
+  for (int i = lane * 8; i < d; i += 256) {
+    const uint4 a = *reinterpret_cast<const uint4*>(o + i);
+    const uint4 c = *reinterpret_cast<const uint4*>(g + i);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, cw[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float a0, a1, c0, c1;
+      if (kBf16) {
+        a0 = __uint_as_float(aw[j] << 16); a1 = __uint_as_float(aw[j] & 0xFFFF0000u);
+        c0 = __uint_as_float(cw[j] << 16); c1 = __uint_as_float(cw[j] & 0xFFFF0000u);
+      } else {
+        const __half2 ah = *reinterpret_cast<const __half2*>(&aw[j]);
+        const __half2 ch = *reinterpret_cast<const __half2*>(&cw[j]);
+        a0 = __low2float(ah); a1 = __high2float(ah); c0 = __low2float(ch); c1 = __high2float(ch);
+      }
+      acc = fmaf(a0, c0, acc);
+      acc = fmaf(a1, c1, acc);
+    }
+  }
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+  if (lane == 0) {
+    const float l = lse[(static_cast<int64_t>(b) * H + h) * Sq + q];
+    lse2[w] = l * kLog2e;  // +inf stays +inf
+    dsum[w] = acc;
+  }
+}
+
+// fp32 dQ accumulator (B,Sq,H,128) * scale -> dq (strided, 16-bit)
+template <bool kBf16>
+__global__ void bwd_convert_dq_kernel(const float* __restrict__ acc, void* __restrict__ dq, int64_t n_vec, int Sq,
+                                      int H, int64_t sb, int64_t sr, int64_t sh, float scale) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n_vec;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t e = i * 8;
+    const int dd = static_cast<int>(e % kD);
+    const int h = static_cast<int>((e / kD) % H);
+    const int q = static_cast<int>((e / (static_cast<int64_t>(kD) * H)) % Sq);
+    const int b = static_cast<int>(e / (static_cast<int64_t>(kD) * H * Sq));
+    const float4 x = *reinterpret_cast<const float4*>(acc + e);
+    const float4 y = *reinterpret_cast<const float4*>(acc + e + 4);
+    uint4 o;
+    o.x = pack_16x2<kBf16>(x.x * scale, x.y * scale);
+    o.y = pack_16x2<kBf16>(x.z * scale, x.w * scale);
+    o.z = pack_16x2<kBf16>(y.x * scale, y.y * scale);
+    o.w = pack_16x2<kBf16>(y.z * scale, y.w * scale);
+    *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(dq) + b * sb + q * sr + h * sh + dd) = o;
+  }
+}
+
+// fp32 (nb,nh,nr,nk) contiguous -> strided 16-bit dbias
+template <bool kBf16>
+__global__ void bwd_convert_dbias_kernel(const float* __restrict__ acc, void* __restrict__ out, int nb, int nh,
+                                         int nr, int nk, int64_t sb, int64_t sh, int64_t sr) {
+  const int64_t n = static_cast<int64_t>(nb) * nh * nr * nk;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int kk = static_cast<int>(i % nk);
+    const int rr = static_cast<int>((i / nk) % nr);
+    const int hh = static_cast<int>((i / (static_cast<int64_t>(nk) * nr)) % nh);
+    const int bb = static_cast<int>(i / (static_cast<int64_t>(nk) * nr * nh));
+    const uint32_t pk = pack_16x2<kBf16>(acc[i], 0.f);
+    reinterpret_cast<uint16_t*>(out)[bb * sb + hh * sh + rr * sr + kk] = static_cast<uint16_t>(pk & 0xFFFFu);
+  }
+}
+
+template <bool kBf16>
+__device__ __forceinline__ float raw16_to_float(uint16_t u) {
+  if (kBf16) return __uint_as_float(static_cast<uint32_t>(u) << 16);
+  return __half2float(__ushort_as_half(u));
+}
+template <bool kBf16>
+__device__ __forceinline__ uint16_t float_to_raw16(float x) {
+  return static_cast<uint16_t>(pack_16x2<kBf16>(x, 0.f) & 0xFFFFu);
+}
+
+template <bool kBf16, bool kBcast>
+__global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant__ BwdKernelParams p) {
+  using L = SmemB;
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) &
+                                                         ~static_cast<uintptr_t>(1023));
+  unsigned char* s_k = smem + L::kKOff;
+  unsigned char* s_v = smem + L::kVOff;
+  unsigned char* s_qdo = smem + L::kQdoOff;
+  unsigned char* s_ds = smem + L::kDsOff;
+  uint8_t* s_act = smem + L::kActOff;
+  float* s_red = reinterpret_cast<float*>(smem + L::kRedOff);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+  uint64_t* bar_kv = bars;
+  uint64_t* bar_qdo_full = bars + 1;
+  uint64_t* bar_qdo_empty = bar_qdo_full + kQStages;
+  uint64_t* bar_s_full = bar_qdo_empty + kQStages;  // [2]
+  uint64_t* bar_dp_full = bar_s_full + 2;
+  uint64_t* bar_pds = bar_dp_full + 1;
+  uint64_t* bar_dq_full = bar_pds + 1;
+  uint64_t* bar_dq_empty = bar_dq_full + 1;
+  uint64_t* bar_ds_empty = bar_dq_empty + 1;        // [2]
+  uint64_t* bar_final = bar_ds_empty + 2;
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + L::kMiscOff);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(smem + L::kMiscOff + 4);
+  int* s_nsteps = reinterpret_cast<int*>(smem + L::kMiscOff + 8);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n = blockIdx.x;  // key tile
+  const int hk = blockIdx.y, b = blockIdx.z;
+  const int G = p.h / p.h_k;
+  const int Sq = p.seqlen_q, Sk = p.seqlen_k;
+  const int off = Sk - Sq;
+  const int M64 = (Sq + kBM - 1) / kBM;
+  const int MT = (Sq + 127) / 128;
+  const int NT = (Sk + kBN - 1) / kBN;
+  const bool causal = p.is_causal != 0;
+  const int act_g = (p.h_mask == p.h && G > 1) ? G : 1;  // activity differs per query head only for per-head masks
+  int m_start = 0;
+  if (causal) m_start = max(0, (n * kBN - off) / kBM);    // first query tile with a row that sees key n*128
+  const WaitCtl ctl{s_abort, p.status};
+
+  // ---------------- set-up ----------------
+  if (tid == 0) {
+    *s_abort = 0;
+    mbar_init(bar_kv, 1);
+    for (int i = 0; i < kQStages; ++i) {
+      mbar_init(bar_qdo_full + i, 1);
+      mbar_init(bar_qdo_empty + i, 1);
+    }
+    mbar_init(bar_s_full + 0, 1);
+    mbar_init(bar_s_full + 1, 1);
+    mbar_init(bar_dp_full, 1);
+    mbar_init(bar_pds, 256);
+    mbar_init(bar_dq_full, 1);
+    mbar_init(bar_dq_empty, 128);
+    mbar_init(bar_ds_empty + 0, 1);
+    mbar_init(bar_ds_empty + 1, 1);
+    mbar_init(bar_final, 1);
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(s_tmem, 512);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    prefetch_tmap(&p.tm_q);
+    prefetch_tmap(&p.tm_do);
+    prefetch_tmap(&p.tm_k);
+    prefetch_tmap(&p.tm_v);
+  }
+  // activity table: s_act[ga * MT + mt] != 0 iff (128-row query tile mt, this key tile) holds a kept element
+  for (int idx = tid; idx < act_g * MT; idx += kThreads) {
+    const int ga = idx / MT, mt = idx % MT;
+    const int hq = hk * G + (act_g > 1 ? ga : 0);
+    const int hm = hq / (p.h / p.h_mask);
+    uint8_t a = 1;
+    if (p.mask) {
+      if (kBcast || p.mask_row_stride == 0) {
+        const uint8_t* mrow = p.mask + b * p.mask_batch_stride + hm * p.mask_head_stride + n * kBN;
+        uint32_t accw = 0;
+#pragma unroll
+        for (int i = 0; i < kBN / 16; ++i) {
+          const uint4 v = *reinterpret_cast<const uint4*>(mrow + i * 16);
+          uint32_t w[4] = {v.x, v.y, v.z, v.w};
+          if (n * kBN + i * 16 + 16 > Sk) {
+#pragma unroll
+            for (int e = 0; e < 16; ++e)
+              if (n * kBN + i * 16 + e >= Sk) w[e >> 2] &= ~(0xFFu << ((e & 3) * 8));
+          }
+          accw |= w[0] | w[1] | w[2] | w[3];
+        }
+        a = accw != 0;
+      } else if (p.act) {
+        a = p.act[((static_cast<int64_t>(b) * p.h_mask + hm) * MT + mt) * NT + n];
+      }
+    }
+    s_act[idx] = a;
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (warp == 1) {
+    int cnt = 0;
+    for (int m = m_start + lane; m < M64; m += 32)
+      for (int g = 0; g < G; ++g) cnt += s_act[(act_g > 1 ? g : 0) * MT + (m >> 1)] ? 1 : 0;
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, s);
+    if (lane == 0) *s_nsteps = cnt;
+  }
+  __syncthreads();
+  const uint32_t tmem_base = *s_tmem;
+  const int n_steps = *s_nsteps;
+  constexpr uint32_t kColSt = 0, kColDp = 128, kColDq = 192, kColDv = 256, kColDk = 384;
+
+  if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    if (warp == 0) {
+      // ---------------- TMA producer ----------------
+      if (lane == 0 && n_steps > 0) {
+        mbar_arrive_expect_tx(bar_kv, 2 * kBN * kD * 2);
+#pragma unroll
+        for (int kb = 0; kb < 2; ++kb) {
+          tma_load_4d(s_k + kb * (kBN * 128), &p.tm_k, bar_kv, kb * 64, hk, n * kBN, b);
+          tma_load_4d(s_v + kb * (kBN * 128), &p.tm_v, bar_kv, kb * 64, hk, n * kBN, b);
+        }
+        int i = 0;
+        bool ok = true;
+        for (int m = m_start; m < M64 && ok; ++m) {
+          for (int g = 0; g < G; ++g) {
+            if (!s_act[(act_g > 1 ? g : 0) * MT + (m >> 1)]) continue;
+            const int stage = i % kQStages;
+            ok = mbar_wait(bar_qdo_empty + stage, ((i / kQStages) & 1) ^ 1, ctl, kWaitQdoEmpty);
+            if (!ok) break;
+            mbar_arrive_expect_tx(bar_qdo_full + stage, L::kStageBytes);
+            unsigned char* dst = s_qdo + stage * L::kStageBytes;
+            const int h = hk * G + g;
+#pragma unroll
+            for (int kb = 0; kb < 2; ++kb) {
+              tma_load_4d(dst + kb * (kBM * 128), &p.tm_q, bar_qdo_full + stage, kb * 64, h, m * kBM, b);
+              tma_load_4d(dst + L::kQBytes + kb * (kBM * 128), &p.tm_do, bar_qdo_full + stage, kb * 64, h, m * kBM, b);
+            }
+            ++i;
+          }
+        }
+      }
+    } else if (warp == 1) {
+      // ---------------- MMA issuer ----------------
+      if (lane == 0 && n_steps > 0) {
+        constexpr uint32_t idesc_s = umma_idesc(kBN, kBM, kBf16, false, false);  // St/dPt: 128 x 64, K-major
+        constexpr uint32_t idesc_g = umma_idesc(kBN, kD, kBf16, false, true);    // dV/dK: A from TMEM, B MN-major
+        constexpr uint32_t idesc_q = umma_idesc(kD, kBM, kBf16, true, true);     // dQ^T: both MN-major
+        const uint32_t k_addr = smem_u32(s_k), v_addr = smem_u32(s_v), qdo_addr = smem_u32(s_qdo),
+                       ds_addr = smem_u32(s_ds);
+        auto issue_st = [&](int step) {  // St[step & 1] = K Q^T
+          const uint32_t qa = qdo_addr + (step % kQStages) * L::kStageBytes;
+#pragma unroll
+          for (int kk = 0; kk < kD / 16; ++kk) {
+            const uint32_t ko = (kk >> 2) * (kBN * 128) + (kk & 3) * 32;
+            const uint32_t qo = (kk >> 2) * (kBM * 128) + (kk & 3) * 32;
+            umma_ss(tmem_base + kColSt + (step & 1) * kBM, umma_desc_sw128(k_addr + ko, 16, 1024),
+                    umma_desc_sw128(qa + qo, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+          }
+          umma_commit(bar_s_full + (step & 1));
+        };
+        auto issue_dp = [&](int step) {  // dPt = V dO^T
+          const uint32_t ga = qdo_addr + (step % kQStages) * L::kStageBytes + L::kQBytes;
+#pragma unroll
+          for (int kk = 0; kk < kD / 16; ++kk) {
+            const uint32_t ko = (kk >> 2) * (kBN * 128) + (kk & 3) * 32;
+            const uint32_t qo = (kk >> 2) * (kBM * 128) + (kk & 3) * 32;
+            umma_ss(tmem_base + kColDp, umma_desc_sw128(v_addr + ko, 16, 1024), umma_desc_sw128(ga + qo, 16, 1024),
+                    idesc_s, kk > 0 ? 1u : 0u);
+          }
+          umma_commit(bar_dp_full);
+        };
+        bool ok = mbar_wait(bar_kv, 0, ctl, kWaitKv);
+        if (ok) ok = mbar_wait(bar_qdo_full + 0, 0, ctl, kWaitQdoFull);
+        if (ok) {
+          tc_fence_after_sync();
+          issue_st(0);
+          issue_dp(0);
+        }
+        if (ok && n_steps > 1) {
+          ok = mbar_wait(bar_qdo_full + 1, 0, ctl, kWaitQdoFull);
+          if (ok) {
+            tc_fence_after_sync();
+            issue_st(1);
+          }
+        }
+        for (int i = 0; i < n_steps && ok; ++i) {
+          ok = mbar_wait(bar_pds, i & 1, ctl, kWaitPds);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t stage_addr = qdo_addr + (i % kQStages) * L::kStageBytes;
+          const uint32_t acc = i > 0 ? 1u : 0u;
+          // dV += P^T dO, dK += dS^T Q : 4 k-steps of 16 queries; query columns 0-31 live in TMEM columns
+          // [0,16) of the St / dPt block and queries 32-63 in columns [32,48)
+#pragma unroll
+          for (int s = 0; s < 4; ++s) {
+            const uint32_t a_col = (s < 2 ? s * 8 : 32 + (s - 2) * 8);
+            umma_ts(tmem_base + kColDv, tmem_base + kColSt + (i & 1) * kBM + a_col,
+                    umma_desc_sw128(stage_addr + L::kQBytes + s * 2048, kBM * 128, 1024), idesc_g,
+                    (acc || s > 0) ? 1u : 0u);
+          }
+#pragma unroll
+          for (int s = 0; s < 4; ++s) {
+            const uint32_t a_col = (s < 2 ? s * 8 : 32 + (s - 2) * 8);
+            umma_ts(tmem_base + kColDk, tmem_base + kColDp + a_col,
+                    umma_desc_sw128(stage_addr + s * 2048, kBM * 128, 1024), idesc_g, (acc || s > 0) ? 1u : 0u);
+          }
+          if (i > 0) {
+            ok = mbar_wait(bar_dq_empty, (i - 1) & 1, ctl, kWaitDqEmpty);
+            if (!ok) break;
+            tc_fence_after_sync();
+          }
+          // dQ^T = K^T dS^T : 8 k-steps of 16 keys
+#pragma unroll
+          for (int s = 0; s < kBN / 16; ++s) {
+            umma_ss(tmem_base + kColDq, umma_desc_sw128(k_addr + s * 2048, kBN * 128, 1024),
+                    umma_desc_sw128(ds_addr + (i & 1) * L::kDsBytes + s * 2048, 16, 1024), idesc_q, s > 0 ? 1u : 0u);
+          }
+          umma_commit(bar_dq_full);
+          umma_commit(bar_qdo_empty + (i % kQStages));
+          umma_commit(bar_ds_empty + (i & 1));
+          if (i + 1 < n_steps) issue_dp(i + 1);
+          if (i + 2 < n_steps) {
+            ok = mbar_wait(bar_qdo_full + ((i + 2) % kQStages), ((i + 2) / kQStages) & 1, ctl, kWaitQdoFull);
+            if (!ok) break;
+            tc_fence_after_sync();
+            issue_st(i + 2);
+          }
+        }
+        umma_commit(bar_final);
+      }
+    }
+  } else if (warp < 12) {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 176;");
+    // ---------------- softmax warpgroups: thread = key, half = which 32 query columns ----------------
+    const int half = (warp - 4) >> 2;
+    const int krow = (warp & 3) * 32 + lane;  // key inside the tile == TMEM lane
+    const int key = n * kBN + krow;
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const bool key_ok = key < Sk;
+    const int mode = p.dbias_mode;
+    float colsum = 0.f;       // column-sum mode
+    float dacc[32];           // direct mode with dbias_h == h_k: sum over the head group
+#pragma unroll
+    for (int j = 0; j < 32; ++j) dacc[j] = 0.f;
+    const bool direct_group = mode == kDbDirect && p.dbias_h != p.h;  // one dbias head per kv head
+    uint16_t* dbias16 = reinterpret_cast<uint16_t*>(p.dbias);
+    int i = 0;
+    bool ok = true;
+    const int m_first = (mode == kDbDirect) ? 0 : m_start;  // direct mode also zero-fills tiles it skips
+    for (int m = m_first; m < M64 && ok; ++m) {
+      const int q0 = m * kBM + half * 32;
+      bool group_touched = false;
+      for (int g = 0; g < G && ok; ++g) {
+        const int h = hk * G + g;
+        const bool active = m >= m_start && s_act[(act_g > 1 ? g : 0) * MT + (m >> 1)] != 0;
+        if (!active) {
+          if (mode == kDbDirect && !direct_group && key < p.dbias_keys) {
+            uint16_t* dst = dbias16 + b * p.dbias_batch_stride + h * p.dbias_head_stride + key;
+            for (int j = 0; j < 32; ++j)
+              if (q0 + j < Sq) dst[static_cast<int64_t>(q0 + j) * p.dbias_row_stride] = 0;
+          }
+          continue;
+        }
+        group_touched = true;
+        const int hm = h / (p.h / p.h_mask), hb = h / (p.h / p.h_bias);
+        // ---- bias / mask for this thread's key and 32 queries ----
+        float bias2[32];
+        uint32_t keep = 0;  // bit j: element (q0 + j, key) is kept
+        if (kBcast) {
+          float bv = 0.f;
+          if (p.bias)
+            bv = raw16_to_float<kBf16>(reinterpret_cast<const uint16_t*>(p.bias)[b * p.bias_batch_stride +
+                                                                              hb * p.bias_head_stride + key]) * kLog2e;
+          bool kp = key_ok;
+          if (p.mask && kp) kp = p.mask[b * p.mask_batch_stride + hm * p.mask_head_stride + key] != 0;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) bias2[j] = bv;
+          keep = kp ? 0xFFFFFFFFu : 0u;
+        } else {
+          const uint16_t* bcol = p.bias ? reinterpret_cast<const uint16_t*>(p.bias) + b * p.bias_batch_stride +
+                                              hb * p.bias_head_stride + key
+                                        : nullptr;
+          const uint8_t* mcol = p.mask ? p.mask + b * p.mask_batch_stride + hm * p.mask_head_stride + key : nullptr;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int qq = min(q0 + j, Sq - 1);
+            bias2[j] = bcol ? raw16_to_float<kBf16>(bcol[static_cast<int64_t>(qq) * p.bias_row_stride]) * kLog2e : 0.f;
+            const bool kp = key_ok && (!mcol || mcol[static_cast<int64_t>(qq) * p.mask_row_stride] != 0);
+            keep |= (kp ? 1u : 0u) << j;
+          }
+        }
+        if (causal && key > q0 + off) {  // some of this thread's queries cannot see its key
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (key > q0 + j + off) keep &= ~(1u << j);
+        }
+        const float* lrow = p.lse2 + (static_cast<int64_t>(b) * p.h + h) * p.sq_r + q0;
+        const float* drow = p.dsum + (static_cast<int64_t>(b) * p.h + h) * p.sq_r + q0;
+
+        // ---- P^T ----
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_s_full + (i & 1), (i >> 1) & 1, ctl, kWaitSFull));
+        if (!ok) break;
+        tc_fence_after_sync();
+        float pv[32];
+        {
+          uint32_t r[32];
+          tmem_ld_x32(tmem_base + lane_addr + kColSt + (i & 1) * kBM + half * 32, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j4 = 0; j4 < 8; ++j4) {
+            const float4 l4 = __ldg(reinterpret_cast<const float4*>(lrow) + j4);
+            const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int j = j4 * 4 + e;
+              const float x = fmaf(__uint_as_float(r[j]), p.scale_log2, bias2[j]) - lv[e];
+              pv[j] = ((keep >> j) & 1u) ? fast_exp2(x) : 0.f;
+            }
+          }
+          uint32_t pk[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) pk[j] = pack_16x2<kBf16>(pv[2 * j], pv[2 * j + 1]);
+          tmem_st_x16(tmem_base + lane_addr + kColSt + (i & 1) * kBM + half * 32, pk);
+        }
+        // ---- dS^T ----
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_dp_full, i & 1, ctl, kWaitDpFull));
+        if (!ok) break;
+        tc_fence_after_sync();
+        uint32_t dsk[16];
+        {
+          uint32_t r[32];
+          tmem_ld_x32(tmem_base + lane_addr + kColDp + half * 32, r);
+          tmem_wait_ld();
+          float step_sum = 0.f;
+#pragma unroll
+          for (int j4 = 0; j4 < 8; ++j4) {
+            const float4 d4 = __ldg(reinterpret_cast<const float4*>(drow) + j4);
+            const float dv4[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int j = j4 * 4 + e;
+              const float ds = pv[j] * (__uint_as_float(r[j]) - dv4[e]);
+              pv[j] = ds;
+              step_sum += ds;
+            }
+          }
+          if (mode == kDbColsum) {
+            colsum += step_sum;
+          } else if (mode == kDbDirect) {
+            if (direct_group) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) dacc[j] += pv[j];
+            } else if (key < p.dbias_keys) {
+              uint16_t* dst = dbias16 + b * p.dbias_batch_stride + h * p.dbias_head_stride + key;
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (q0 + j < Sq) dst[static_cast<int64_t>(q0 + j) * p.dbias_row_stride] = float_to_raw16<kBf16>(pv[j]);
+            }
+          } else if (mode == kDbAtomic && key_ok) {
+            const int b2 = p.dbias_b == 1 ? 0 : b;
+            const int h2 = h / (p.h / p.dbias_h);
+            float* base = p.dbias_acc + (static_cast<int64_t>(b2) * p.dbias_h + h2) * p.dbias_rows * p.dbias_keys + key;
+            if (p.dbias_rows == 1) {
+              atomicAdd(base, step_sum);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (q0 + j < Sq && pv[j] != 0.f) atomicAdd(base + static_cast<int64_t>(q0 + j) * p.dbias_keys, pv[j]);
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) dsk[j] = pack_16x2<kBf16>(pv[2 * j], pv[2 * j + 1]);
+          tmem_st_x16(tmem_base + lane_addr + kColDp + half * 32, dsk);
+        }
+        // ---- dS^T tile to shared memory for the dQ MMA: row = key, 64 queries x 2 B = 128 B, 128-byte swizzle ----
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_ds_empty + (i & 1), ((i >> 1) & 1) ^ 1, ctl, kWaitDsEmpty));
+        if (!ok) break;
+        {
+          unsigned char* rowp = s_ds + (i & 1) * L::kDsBytes + krow * 128;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int chunk = (half * 4 + c) ^ (krow & 7);
+            *reinterpret_cast<uint4*>(rowp + chunk * 16) = make_uint4(dsk[c * 4], dsk[c * 4 + 1], dsk[c * 4 + 2], dsk[c * 4 + 3]);
+          }
+        }
+        tmem_wait_st();
+        fence_proxy_async_smem();
+        tc_fence_before_sync();
+        mbar_arrive(bar_pds);
+        ++i;
+      }
+      if (direct_group && ok && key < p.dbias_keys) {  // one store per (query, key) after the whole head group
+        uint16_t* dst = dbias16 + b * p.dbias_batch_stride + hk * p.dbias_head_stride + key;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          if (q0 + j < Sq)
+            dst[static_cast<int64_t>(q0 + j) * p.dbias_row_stride] = float_to_raw16<kBf16>(group_touched ? dacc[j] : 0.f);
+          dacc[j] = 0.f;
+        }
+      }
+    }
+    // ---------------- epilogue: dV (half 0) and dK (half 1), column-sum dBias ----------------
+    if (mode == kDbColsum) {
+      if (half == 1) s_red[krow] = colsum;
+      named_bar_sync(1, 256);
+      if (half == 0 && key < p.dbias_keys) {
+        // dbias_h == h_k: this CTA saw every query head of the group. dbias_h == h with a group of one: same.
+        const float tot = colsum + s_red[krow];
+        dbias16[b * p.dbias_batch_stride + hk * p.dbias_head_stride + key] = float_to_raw16<kBf16>(key_ok ? tot : 0.f);
+      }
+    }
+    if (ok && n_steps > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar_final, 0, ctl, kWaitFinal));
+    tc_fence_after_sync();
+    if (ok) {
+      const uint32_t col = half == 0 ? kColDv : kColDk;
+      const float mul = half == 0 ? 1.f : p.scale;
+      uint16_t* dst = half == 0
+                          ? reinterpret_cast<uint16_t*>(p.dv) + b * p.dv_batch_stride + hk * p.dv_head_stride +
+                                static_cast<int64_t>(min(key, Sk - 1)) * p.dv_row_stride
+                          : reinterpret_cast<uint16_t*>(p.dk) + b * p.dk_batch_stride + hk * p.dk_head_stride +
+                                static_cast<int64_t>(min(key, Sk - 1)) * p.dk_row_stride;
+#pragma unroll
+      for (int c = 0; c < kD / 32; ++c) {
+        uint32_t r[32];
+        if (n_steps > 0) {
+          tmem_ld_x32(tmem_base + lane_addr + col + c * 32, r);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = 0u;
+        }
+        if (key_ok) {
+#pragma unroll
+          for (int v4 = 0; v4 < 4; ++v4) {
+            uint4 o;
+            o.x = pack_16x2<kBf16>(__uint_as_float(r[v4 * 8 + 0]) * mul, __uint_as_float(r[v4 * 8 + 1]) * mul);
+            o.y = pack_16x2<kBf16>(__uint_as_float(r[v4 * 8 + 2]) * mul, __uint_as_float(r[v4 * 8 + 3]) * mul);
+            o.z = pack_16x2<kBf16>(__uint_as_float(r[v4 * 8 + 4]) * mul, __uint_as_float(r[v4 * 8 + 5]) * mul);
+            o.w = pack_16x2<kBf16>(__uint_as_float(r[v4 * 8 + 6]) * mul, __uint_as_float(r[v4 * 8 + 7]) * mul);
+            *reinterpret_cast<uint4*>(dst + c * 32 + v4 * 8) = o;
+          }
+        }
+      }
+    }
+  } else {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
+    // ---------------- dQ writer: thread = head-dim index (row of dQ^T) ----------------
+    const int dl = (warp & 3) * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    int i = 0;
+    bool ok = true;
+    for (int m = m_start; m < M64 && ok; ++m) {
+      for (int g = 0; g < G && ok; ++g) {
+        if (!s_act[(act_g > 1 ? g : 0) * MT + (m >> 1)]) continue;
+        const int h = hk * G + g;
+        ok = __all_sync(0xffffffffu, mbar_wait(bar_dq_full, i & 1, ctl, kWaitDqFull));
+        if (!ok) break;
+        tc_fence_after_sync();
+        float* base = p.dq_acc + ((static_cast<int64_t>(b) * Sq + m * kBM) * p.h + h) * kD + dl;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t r[32];
+          tmem_ld_x32(tmem_base + lane_addr + kColDq + c * 32, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int q = m * kBM + c * 32 + j;
+            if (q < Sq) atomicAdd(base + static_cast<int64_t>(c * 32 + j) * p.h * kD, __uint_as_float(r[j]));
+          }
+        }
+        tc_fence_before_sync();
+        mbar_arrive(bar_dq_empty);
+        ++i;
+      }
+    }
+  }
+
+  // ---------------- tear-down ----------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+struct BwdPlan {
+  bool bcast;
+  bool needs_act;
+  int dbias_mode;
+  int sq_r;
+  size_t lse2_off, dsum_off, dq_off, act_off, dbias_off, total;
+};
+
+BwdPlan plan(const fdma_bwd_params& bp) {
+  const fdma_fwd_params& p = bp.f;
+  BwdPlan pl;
+  const bool mask_b = !p.mask || p.mask_row_stride == 0 || p.seqlen_q == 1;
+  const bool bias_b = !p.bias || p.bias_row_stride == 0 || p.seqlen_q == 1;
+  pl.bcast = mask_b && bias_b;
+  pl.needs_act = p.mask != nullptr && !mask_b;
+  pl.sq_r = static_cast<int>(round_up(p.seqlen_q, kBM));
+  const int G = p.h / p.h_k;
+  if (!bp.dbias) {
+    pl.dbias_mode = kDbNone;
+  } else if (bp.dbias_b == p.b && bp.dbias_rows == 1 && p.seqlen_q >= 1 &&
+             (bp.dbias_h == p.h_k || (bp.dbias_h == p.h && G == 1))) {
+    pl.dbias_mode = kDbColsum;
+  } else if (bp.dbias_b == p.b && bp.dbias_rows == p.seqlen_q && (bp.dbias_h == p.h_k || bp.dbias_h == p.h)) {
+    pl.dbias_mode = kDbDirect;
+  } else {
+    pl.dbias_mode = kDbAtomic;
+  }
+  size_t o = 0;
+  const size_t rows = static_cast<size_t>(p.b) * p.h * pl.sq_r;
+  pl.lse2_off = o; o += align256(rows * 4);
+  pl.dsum_off = o; o += align256(rows * 4);
+  pl.dq_off = o;   o += align256(static_cast<size_t>(p.b) * p.seqlen_q * p.h * kD * 4);
+  pl.act_off = o;
+  if (pl.needs_act)
+    o += align256(static_cast<size_t>(p.b) * p.h_mask * ((p.seqlen_q + 127) / 128) * ((p.seqlen_k + 127) / 128));
+  pl.dbias_off = o;
+  if (pl.dbias_mode == kDbAtomic)
+    o += align256(static_cast<size_t>(bp.dbias_b) * bp.dbias_h * bp.dbias_rows * bp.dbias_keys * 4);
+  pl.total = o;
+  return pl;
+}
+
+bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; }
+
+template <bool kBf16>
+int launch(const fdma_bwd_params& bp, const BwdPlan& pl, cudaStream_t stream) {
+  const fdma_fwd_params& p = bp.f;
+  if (!p.workspace || p.workspace_bytes < pl.total) return FDMA_ERR_WORKSPACE;
+  char* ws = static_cast<char*>(p.workspace);
+  BwdKernelParams kp;
+  auto encode = [&](CUtensorMap* tm, const void* base, int heads, int rows, int box_rows, int64_t sb, int64_t sr,
+                    int64_t sh) {
+    if (heads == 1) sh = p.d;
+    if (rows == 1) sr = static_cast<int64_t>(heads) * p.d;
+    if (p.b == 1) sb = static_cast<int64_t>(rows) * heads * p.d;
+    const uint64_t dims[4] = {static_cast<uint64_t>(p.d), static_cast<uint64_t>(heads), static_cast<uint64_t>(rows),
+                              static_cast<uint64_t>(p.b)};
+    const uint64_t str[3] = {static_cast<uint64_t>(sh) * 2, static_cast<uint64_t>(sr) * 2,
+                             static_cast<uint64_t>(sb) * 2};
+    const uint32_t box[4] = {64, 1, static_cast<uint32_t>(box_rows), 1};
+    return encode_tmap_4d(tm, base, 2, dims, str, box);
+  };
+  int st = encode(&kp.tm_q, p.q, p.h, p.seqlen_q, kBM, p.q_batch_stride, p.q_row_stride, p.q_head_stride);
+  if (st) return st;
+  st = encode(&kp.tm_do, bp.dout, p.h, p.seqlen_q, kBM, bp.do_batch_stride, bp.do_row_stride, bp.do_head_stride);
+  if (st) return st;
+  st = encode(&kp.tm_k, p.k, p.h_k, p.seqlen_k, kBN, p.k_batch_stride, p.k_row_stride, p.k_head_stride);
+  if (st) return st;
+  st = encode(&kp.tm_v, p.v, p.h_k, p.seqlen_k, kBN, p.v_batch_stride, p.v_row_stride, p.v_head_stride);
+  if (st) return st;
+
+  float* lse2 = reinterpret_cast<float*>(ws + pl.lse2_off);
+  float* dsum = reinterpret_cast<float*>(ws + pl.dsum_off);
+  float* dq_acc = reinterpret_cast<float*>(ws + pl.dq_off);
+  const size_t dq_bytes = static_cast<size_t>(p.b) * p.seqlen_q * p.h * kD * 4;
+  cudaError_t e = cudaMemsetAsync(dq_acc, 0, dq_bytes, stream);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  {
+    const int64_t warps = static_cast<int64_t>(p.b) * p.h * pl.sq_r;
+    const int64_t blocks = (warps * 32 + 255) / 256;
+    bwd_prep_kernel<kBf16><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+        p.out, bp.dout, p.lse, lse2, dsum, p.b, p.h, p.seqlen_q, pl.sq_r, p.d, p.o_batch_stride, p.o_row_stride,
+        p.o_head_stride, bp.do_batch_stride, bp.do_row_stride, bp.do_head_stride);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  kp.act = nullptr;
+  if (pl.needs_act) {
+    uint8_t* act = reinterpret_cast<uint8_t*>(ws + pl.act_off);
+    st = launch_tile_activity(p, act, stream);
+    if (st) return st;
+    kp.act = act;
+  }
+  kp.dbias_acc = nullptr;
+  if (pl.dbias_mode == kDbAtomic) {
+    kp.dbias_acc = reinterpret_cast<float*>(ws + pl.dbias_off);
+    e = cudaMemsetAsync(kp.dbias_acc, 0,
+                        static_cast<size_t>(bp.dbias_b) * bp.dbias_h * bp.dbias_rows * bp.dbias_keys * 4, stream);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  kp.mask = static_cast<const uint8_t*>(p.mask);
+  kp.bias = p.bias;
+  kp.lse2 = lse2;
+  kp.dsum = dsum;
+  kp.dq_acc = dq_acc;
+  kp.dk = bp.dk;
+  kp.dv = bp.dv;
+  kp.dbias = bp.dbias;
+  kp.status = kernel_status_ptr();
+  if (!kp.status) return FDMA_ERR_DRIVER;
+  kp.mask_batch_stride = p.mask_batch_stride; kp.mask_head_stride = p.mask_head_stride;
+  kp.mask_row_stride = p.seqlen_q == 1 ? 0 : p.mask_row_stride;
+  kp.bias_batch_stride = p.bias_batch_stride; kp.bias_head_stride = p.bias_head_stride;
+  kp.bias_row_stride = p.seqlen_q == 1 ? 0 : p.bias_row_stride;
+  kp.dk_batch_stride = bp.dk_batch_stride; kp.dk_row_stride = bp.dk_row_stride; kp.dk_head_stride = bp.dk_head_stride;
+  kp.dv_batch_stride = bp.dv_batch_stride; kp.dv_row_stride = bp.dv_row_stride; kp.dv_head_stride = bp.dv_head_stride;
+  kp.dbias_batch_stride = bp.dbias_batch_stride; kp.dbias_head_stride = bp.dbias_head_stride;
+  kp.dbias_row_stride = bp.dbias_row_stride;
+  kp.b = p.b; kp.seqlen_q = p.seqlen_q; kp.seqlen_k = p.seqlen_k; kp.sq_r = pl.sq_r; kp.h = p.h; kp.h_k = p.h_k;
+  kp.h_mask = p.h_mask; kp.h_bias = p.h_bias;
+  kp.dbias_b = bp.dbias_b; kp.dbias_h = bp.dbias_h; kp.dbias_rows = bp.dbias_rows; kp.dbias_keys = bp.dbias_keys;
+  kp.dbias_mode = pl.dbias_mode;
+  kp.is_causal = p.is_causal;
+  kp.scale_log2 = p.softmax_scale * kLog2e;
+  kp.scale = p.softmax_scale;
+
+  auto kern = pl.bcast ? bwd_kernel<kBf16, true> : bwd_kernel<kBf16, false>;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemB::kAlloc);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  dim3 grid((p.seqlen_k + kBN - 1) / kBN, p.h_k, p.b);
+  kern<<<grid, kThreads, SmemB::kAlloc, stream>>>(kp);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return static_cast<int>(e);
+
+  {
+    const int64_t n_vec = static_cast<int64_t>(p.b) * p.seqlen_q * p.h * kD / 8;
+    const unsigned g = static_cast<unsigned>(std::min<int64_t>((n_vec + 255) / 256, 148 * 32));
+    bwd_convert_dq_kernel<kBf16><<<g, 256, 0, stream>>>(dq_acc, bp.dq, n_vec, p.seqlen_q, p.h, bp.dq_batch_stride,
+                                                        bp.dq_row_stride, bp.dq_head_stride, p.softmax_scale);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  if (pl.dbias_mode == kDbAtomic) {
+    const int64_t ndb = static_cast<int64_t>(bp.dbias_b) * bp.dbias_h * bp.dbias_rows * bp.dbias_keys;
+    const unsigned g = static_cast<unsigned>(std::min<int64_t>((ndb + 255) / 256, 148 * 32));
+    bwd_convert_dbias_kernel<kBf16><<<g, 256, 0, stream>>>(kp.dbias_acc, bp.dbias, bp.dbias_b, bp.dbias_h,
+                                                           bp.dbias_rows, bp.dbias_keys, bp.dbias_batch_stride,
+                                                           bp.dbias_head_stride, bp.dbias_row_stride);
+    e = cudaGetLastError();
+  }
+  return static_cast<int>(e);
+}
+
+}  // namespace
+
+bool tc_bwd_supported(const fdma_bwd_params& bp) {
+  const fdma_fwd_params& p = bp.f;
+  if (!tc_fwd_supported(p)) return false;
+  if (p.d != kD) return false;
+  if (p.h_k > 65535) return false;
+  const int G = p.h / p.h_k;
+  const int act_g = (p.mask && p.h_mask == p.h && G > 1) ? G : 1;
+  if (static_cast<int64_t>(act_g) * ((p.seqlen_q + 127) / 128) > kMaxAct) return false;
+  const void* ptrs[4] = {bp.dout, bp.dq, bp.dk, bp.dv};
+  for (const void* x : ptrs)
+    if (!aligned16(x)) return false;
+  const int64_t strides[12] = {bp.do_batch_stride, bp.do_row_stride, bp.do_head_stride, bp.dq_batch_stride,
+                               bp.dq_row_stride,   bp.dq_head_stride, bp.dk_batch_stride, bp.dk_row_stride,
+                               bp.dk_head_stride,  bp.dv_batch_stride, bp.dv_row_stride,  bp.dv_head_stride};
+  for (int64_t s : strides)
+    if (s % 8 != 0 || s < 0) return false;
+  if (p.seqlen_q > 1 && bp.do_row_stride == 0) return false;
+  if (bp.dbias && bp.dbias_keys > round_up(p.seqlen_k, kBN)) return false;
+  return true;
+}
+
+size_t tc_bwd_workspace_bytes(const fdma_bwd_params& p) { return plan(p).total; }
+
+int tc_bwd(const fdma_bwd_params& p, cudaStream_t stream) {
+  const BwdPlan pl = plan(p);
+  return p.f.dtype == FDMA_BF16 ? launch<true>(p, pl, stream) : launch<false>(p, pl, stream);
+}
+
 }  // namespace fdma

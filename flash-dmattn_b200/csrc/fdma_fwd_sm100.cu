@@ -612,14 +612,8 @@ int launch(const fdma_fwd_params& p, const FwdPlan& pl, cudaStream_t stream) {
   if (pl.needs_act) {
     if (!p.workspace || p.workspace_bytes < pl.act_bytes) return FDMA_ERR_WORKSPACE;
     uint8_t* act = static_cast<uint8_t*>(p.workspace);
-    const int64_t tiles = static_cast<int64_t>(p.b) * p.h_mask * ((p.seqlen_q + kBM - 1) / kBM) *
-                          ((p.seqlen_k + kBN - 1) / kBN);
-    const int64_t blocks = (tiles * 32 + 255) / 256;
-    tile_activity_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
-        kp.mask, p.mask_batch_stride, p.mask_head_stride, p.mask_row_stride, p.b, p.h_mask, p.seqlen_q, p.seqlen_k,
-        p.is_causal, act);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return static_cast<int>(e);
+    st = launch_tile_activity(p, act, stream);
+    if (st) return st;
     kp.act = act;
   }
 
@@ -644,6 +638,16 @@ int launch_d(const fdma_fwd_params& p, const FwdPlan& pl, cudaStream_t stream) {
 }
 
 }  // namespace
+
+int launch_tile_activity(const fdma_fwd_params& p, uint8_t* act, cudaStream_t stream) {
+  const int64_t tiles = static_cast<int64_t>(p.b) * p.h_mask * ((p.seqlen_q + kBM - 1) / kBM) *
+                        ((p.seqlen_k + kBN - 1) / kBN);
+  const int64_t blocks = (tiles * 32 + 255) / 256;
+  tile_activity_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+      static_cast<const uint8_t*>(p.mask), p.mask_batch_stride, p.mask_head_stride,
+      p.seqlen_q == 1 ? 0 : p.mask_row_stride, p.b, p.h_mask, p.seqlen_q, p.seqlen_k, p.is_causal, act);
+  return static_cast<int>(cudaGetLastError());
+}
 
 bool tc_fwd_supported(const fdma_fwd_params& p) {
   if (p.d != 64 && p.d != 128) return false;

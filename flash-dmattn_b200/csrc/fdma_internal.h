@@ -22,6 +22,9 @@ bool tc_fwd_supported(const fdma_fwd_params& p);
 size_t tc_fwd_workspace_bytes(const fdma_fwd_params& p);
 int tc_fwd(const fdma_fwd_params& p, cudaStream_t stream);
 
+// Per-tile mask activity map for per-query masks: act[b][h_mask][ceil(Sq/128)][ceil(Sk/128)] bytes.
+int launch_tile_activity(const fdma_fwd_params& p, uint8_t* act, cudaStream_t stream);
+
 bool tc_bwd_supported(const fdma_bwd_params& p);
 size_t tc_bwd_workspace_bytes(const fdma_bwd_params& p);
 int tc_bwd(const fdma_bwd_params& p, cudaStream_t stream);

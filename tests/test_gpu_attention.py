@@ -61,6 +61,9 @@ def build_case(dev, B, Sq, Sk, H, Hk, d, bias_kind, mask_kind, window, dtype, se
             mask[b, h, 0, start : start + window] = True
     elif mask_kind == "randq":
         mask = torch.rand((B, 1, Sq, Sk), generator=g) < 0.3
+    elif mask_kind == "randqh":  # per query head, with whole 128x128 tiles emptied for some heads
+        mask = torch.rand((B, H, Sq, Sk), generator=g) < 0.3
+        mask[:, ::2, : Sq // 2, Sk // 2 :] = False
     else:
         raise ValueError(mask_kind)
     to = lambda t: None if t is None else t.to(dev)
@@ -154,6 +157,43 @@ def test_tcgen05_forward(dev, kernel_path, geom, bias_kind, mask_kind, window, c
     kernel_path("tcgen05")
     case = build_case(dev, *geom, bias_kind, mask_kind, window, torch.bfloat16)
     compare_all(case, causal, torch.bfloat16, fwd_only=True)
+
+
+TC_BWD_CASES = [
+    ((1, 256, 256, 2, 1, 128), "bcast", "topk", 128, True),     # column-sum dBias over a head group
+    ((2, 512, 512, 4, 2, 128), "bcast", "topk", 200, True),
+    ((1, 384, 640, 2, 2, 128), "bcast", "block", 128, True),    # key tiles without any kept key
+    ((1, 300, 300, 2, 1, 128), "bcast", "topk", 77, True),      # ragged
+    ((2, 640, 128, 2, 2, 128), "none", "none", 0, True),        # Sq > Sk
+    ((1, 200, 520, 2, 1, 128), "none", "topk", 130, False),     # mask only, no dBias
+    ((1, 256, 256, 4, 2, 128), "perq", "randq", 0, True),       # per-query dBias summed over the head group
+    ((1, 300, 420, 4, 4, 128), "perhead", "randq", 0, True),    # per-head per-query dBias
+    ((1, 256, 512, 2, 1, 128), "bcast", "randq", 0, True),      # broadcast bias, per-query mask
+    ((1, 256, 384, 4, 2, 128), "b1h1", "topk", 100, True),      # bias shared by all heads: fp32 atomics
+    ((2, 256, 256, 2, 2, 128), "b1h1", "none", 0, False),       # bias shared by the batch
+    ((1, 512, 512, 4, 2, 128), "perq", "randqh", 0, False),     # per-query-head mask, tiles empty for some heads
+    ((1, 1, 700, 8, 2, 128), "bcast", "topk", 100, False),      # single query row
+]
+
+
+@pytest.mark.parametrize("geom,bias_kind,mask_kind,window,causal", TC_BWD_CASES)
+def test_tcgen05_forward_backward(dev, kernel_path, geom, bias_kind, mask_kind, window, causal):
+    kernel_path("tcgen05")
+    case = build_case(dev, *geom, bias_kind, mask_kind, window, torch.bfloat16)
+    compare_all(case, causal, torch.bfloat16)
+
+
+def test_tcgen05_backward_fp16_and_run_to_run_spread(dev, kernel_path):
+    kernel_path("tcgen05")
+    case = build_case(dev, 1, 384, 384, 4, 2, 128, "bcast", "topk", 100, torch.float16)
+    compare_all(case, True, torch.float16)
+    # dQ goes through fp32 atomics: two runs may differ by accumulation order, but only at fp32 round-off
+    q, k, v, mask, bias, dout = case
+    a = run_ours(q, k, v, mask, bias, dout, True)
+    b = run_ours(q, k, v, mask, bias, dout, True)
+    for x, y in zip(a, b):
+        assert (x.float() - y.float()).abs().max() <= 1e-2 * max(1.0, x.float().abs().max().item())
+    assert torch.equal(a[2], b[2]) and torch.equal(a[3], b[3])  # dK, dV have a fixed accumulation order
 
 
 def test_tcgen05_forward_fp16(dev, kernel_path):
