@@ -1,0 +1,402 @@
+"""Headline benchmark: forward+backward dynamic-mask attention, TFLOP/s on kept blocks.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--batch-per-gpu B]
+
+Workload (BASELINE.json configs[2], the shape its metric is quoted on): S = Sq = Sk = 32768, top-2048 mask per
+(batch, kv head) from a query-broadcast bias (B,Hkv,1,Sk) ~ N(0,1), causal, Hq = 32, Hkv = 8, d = 128, bf16,
+dOut ~ N(0,1), seeded synthetic data. One batch element per GPU (8 independent (batch, kv-head) units); with N GPUs
+the global batch is N, sharded over ranks with no collective in the data path (weak scaling).
+
+A step = one forward + one backward through the C ABI (fdma_fwd, fdma_bwd); create_mask is outside the timed
+region, as in the reference's benchmarks (benchmarks/forward_performance.py:185-204). FLOPs are counted only on
+kept tiles of the tile shape each kernel really uses, from the actual mask (4*d*BM*BN per forward tile, 10*d*BM*BN
+per backward tile). `value` has inputs resident in HBM; `e2e` goes through flash_sparse_attn_func with pinned host
+buffers, copying inputs up and results back inside the timed region.
+
+--impl reference times the reference's eager algorithm (the CPU oracle port, oracle/oracle.py) on the host cores
+on a bounded sample of the same workload.
+"""
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "flash-dmattn_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+
+S, HQ, HKV, D, WINDOW = 32768, 32, 8, 128, 2048
+WORKLOAD = "S=32768 W=2048 d=128 Hq=32 Hkv=8 causal, bias (B,Hkv,1,Sk), B=1 per GPU"
+
+
+def set_geometry(seq_len: int, window: int):
+    """Smaller sequence lengths exist for profiler captures only; the reported benchmark uses the defaults."""
+    global S, WINDOW, WORKLOAD
+    S, WINDOW = seq_len, window
+    WORKLOAD = f"S={S} W={WINDOW} d=128 Hq=32 Hkv=8 causal, bias (B,Hkv,1,Sk), B=1 per GPU"
+
+
+FWD_TILE, BWD_TILE = (128, 128), (64, 128)
+NOMINAL_TFLOPS = 2250.0
+
+
+# ------------------------------------------------------------------------------------------------------------
+# FLOP accounting on kept tiles (host side, from the actual mask)
+# ------------------------------------------------------------------------------------------------------------
+def kept_tiles_rowbcast(mask_row: torch.Tensor, Sq: int, Sk: int, bm: int, bn: int, causal: bool) -> int:
+    """Number of (bm x bn) tiles holding at least one kept, causally visible element, for a mask that is the
+    same for every query row. mask_row: bool (Sk,)."""
+    nt = (Sk + bn - 1) // bn
+    mt = (Sq + bm - 1) // bm
+    idx = torch.arange(Sk, device=mask_row.device)
+    big = Sk + Sq + 1
+    first = torch.where(mask_row[:Sk], idx, torch.full_like(idx, big))
+    pad = nt * bn - Sk
+    if pad:
+        first = torch.cat([first, torch.full((pad,), big, device=first.device, dtype=first.dtype)])
+    kmin = first.view(nt, bn).amin(dim=1)                       # first kept key of each key tile
+    last_row = torch.clamp((torch.arange(mt, device=mask_row.device) + 1) * bm - 1, max=Sq - 1)
+    limit = last_row + (Sk - Sq) if causal else torch.full_like(last_row, big - 1)
+    return int((kmin.view(1, nt) <= limit.view(mt, 1)).sum().item())
+
+
+def count_flops(mask: torch.Tensor, B: int, Sq: int, Sk: int, H: int, Hk: int, d: int, causal: bool) -> dict:
+    """mask (B,Hk,1,Sk) bool. Returns FLOPs per pass under the accounting rules of the metric."""
+    G = H // Hk
+    kept_f = kept_b = kept_c = 0
+    for b in range(B):
+        for hk in range(Hk):
+            row = mask[b, hk, 0]
+            kept_f += G * kept_tiles_rowbcast(row, Sq, Sk, *FWD_TILE, causal)
+            kept_b += G * kept_tiles_rowbcast(row, Sq, Sk, *BWD_TILE, causal)
+            kept_c += G * kept_tiles_rowbcast(row, Sq, Sk, 128, 128, causal)
+    mt, nt = (Sq + 127) // 128, (Sk + 127) // 128
+    causal_tiles = sum(min(nt, max(0, ((i + 1) * 128 + Sk - Sq + 127) // 128)) for i in range(mt)) if causal else mt * nt
+    fwd = 4 * d * FWD_TILE[0] * FWD_TILE[1] * kept_f
+    bwd = 10 * d * BWD_TILE[0] * BWD_TILE[1] * kept_b
+    return {
+        "fwd": fwd, "bwd": bwd, "total": fwd + bwd,
+        "canonical_128x128": 14 * d * 128 * 128 * kept_c,
+        "causal_dense": 14 * d * 128 * 128 * causal_tiles * B * H,
+    }
+
+
+# ------------------------------------------------------------------------------------------------------------
+# clocks sampler
+# ------------------------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {
+            "sm_mhz": statistics.median(sm) if sm else None,
+            "sm_max_mhz": max(smax) if smax else None,
+            "samples": len(sm),
+            "reasons": sorted(reasons),
+        }
+
+
+# ------------------------------------------------------------------------------------------------------------
+# CPU legs (oracle port of the reference's eager path)
+# ------------------------------------------------------------------------------------------------------------
+CPU_ROWS = 1024  # query rows of the bounded CPU sample (the last rows of the sequence: full causal extent)
+
+
+def cpu_sample(steps: int, warmup: int) -> dict:
+    """Eager fp32 forward+backward of ONE kv head (its 4 query heads) x the last CPU_ROWS query rows against
+    all 32768 keys, timed on the host cores; FLOPs counted on that slice's kept 128x128 tiles."""
+    from oracle import oracle
+
+    G = HQ // HKV
+    q, k, v, bias, dout = oracle.make_inputs(1, CPU_ROWS, S, G, 1, D, (1, 1, 1, S), seed=0, dtype=torch.bfloat16)
+    mask = oracle.create_mask(bias, None, 1, CPU_ROWS, S, WINDOW, torch.finfo(torch.bfloat16).min)
+    flops = count_flops(mask, 1, CPU_ROWS, S, G, 1, D, True)
+    times = []
+    for it in range(warmup + steps):
+        t0 = time.perf_counter()
+        oracle.attention_forward_backward(q, k, v, mask, bias, dout, None, True)
+        if it >= warmup:
+            times.append(time.perf_counter() - t0)
+    sec = sum(times) / len(times)
+    flop_ref = flops["canonical_128x128"]
+    return {
+        "value": flop_ref / sec / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+        "sample": f"1 kv head x {G} query heads x last {CPU_ROWS} query rows x {S} keys, fp32 eager, "
+                  f"{sec * 1e3:.0f} ms per fwd+bwd, kept-tile FLOPs at 128x128",
+        "ms_per_step": sec * 1e3,
+    }
+
+
+def run_reference(args, rank: int, world: int):
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 10))  # ~4 s of host work per step: keeps the arm within a few minutes
+    cb = cpu_sample(steps, min(args.warmup, 1))
+    line = {
+        "impl": "reference", "metric": "fwd+bwd TFLOP/s on kept blocks", "value": cb["value"], "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": cb["ms_per_step"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "note": "reference eager algorithm (CPU oracle port), bounded sample per step"},
+        "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": cb["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------------------------
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            pk = json.load(f)
+        return float(pk.get("bf16_tflops_sustained", pk.get("bf16_tflops"))), "measured (cuBLAS bf16, sustained)"
+    return 1400.0, "fallback (sustained)"
+
+
+def run_ours(args, rank: int, world: int, local_rank: int):
+    import torch.distributed as dist
+
+    from flash_sparse_attn import _lib, flash_sparse_attn_func
+    from flash_sparse_attn import flash_sparse_attn_interface as iface
+    from flash_sparse_attn.utils.mask import create_mask
+
+    dev = torch.device(f"cuda:{local_rank}")
+    torch.cuda.set_device(dev)
+    lib = _lib.load()
+    B = args.batch_per_gpu
+    # seeded synthetic inputs: Q, K, V, bias, dOut ~ N(0,1) drawn in fp32 then cast to bf16; seed differs per rank
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    rnd = lambda *shape: torch.randn(shape, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    q, k, v = rnd(B, S, HQ, D), rnd(B, S, HKV, D), rnd(B, S, HKV, D)
+    bias, dout = rnd(B, HKV, 1, S), rnd(B, S, HQ, D)
+    mask = create_mask(bias, None, B, S, S, WINDOW, torch.finfo(torch.bfloat16).min)
+    flops = count_flops(mask.cpu(), B, S, S, HQ, HKV, D, True)  # on the host: keeps the launch list clean
+
+    out = torch.empty_like(q)
+    lse = torch.empty((B, HQ, S), dtype=torch.float32, device=dev)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    dbias = torch.empty_like(bias)
+    fp = _lib.FwdParams()
+    iface._fill_fwd(fp, q, k, v, mask, bias, out, lse, D ** -0.5, True)
+    bp = _lib.BwdParams()
+    iface._fill_fwd(bp.f, q, k, v, mask, bias, out, lse, D ** -0.5, True)
+    bp.dout = dout.data_ptr()
+    bp.do_batch_stride, bp.do_row_stride, bp.do_head_stride = iface._bsh(dout)
+    bp.dq, bp.dk, bp.dv, bp.dbias = dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dbias.data_ptr()
+    bp.dq_batch_stride, bp.dq_row_stride, bp.dq_head_stride = iface._bsh(dq)
+    bp.dk_batch_stride, bp.dk_row_stride, bp.dk_head_stride = iface._bsh(dk)
+    bp.dv_batch_stride, bp.dv_row_stride, bp.dv_head_stride = iface._bsh(dv)
+    bp.dbias_batch_stride, bp.dbias_head_stride, bp.dbias_row_stride = dbias.stride()[:3]
+    bp.dbias_b, bp.dbias_h, bp.dbias_rows, bp.dbias_keys = dbias.shape
+    ws_f = lib.fdma_fwd_workspace_bytes(ctypes.byref(fp))
+    ws_b = lib.fdma_bwd_workspace_bytes(ctypes.byref(bp))
+    ws = torch.empty(max(ws_f, ws_b, 1), dtype=torch.uint8, device=dev)
+    fp.workspace, fp.workspace_bytes = ws.data_ptr(), ws_f
+    bp.f.workspace, bp.f.workspace_bytes = ws.data_ptr(), ws_b
+    stream = torch.cuda.current_stream(dev)
+
+    def step(ev=None):
+        if ev is not None:
+            lib.fdma_time_next_kernel(ev[0].cuda_event, ev[1].cuda_event)
+        _lib.check(lib.fdma_fwd(ctypes.byref(fp), stream.cuda_stream), "fdma_fwd")
+        if ev is not None:
+            lib.fdma_time_next_kernel(ev[2].cuda_event, ev[3].cuda_event)
+        _lib.check(lib.fdma_bwd(ctypes.byref(bp), stream.cuda_stream), "fdma_bwd")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    # ---- device-resident timing ----
+    for _ in range(args.warmup):
+        step()
+    kernel_events = []
+    for _ in range(args.steps):
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        for e in evs:
+            e.record(stream)  # materialises the underlying cudaEvent_t
+        kernel_events.append(evs)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    t_start, t_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t_start.record(stream)
+    for i in range(args.steps):
+        step(kernel_events[i])
+    t_stop.record(stream)
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms_total = t_start.elapsed_time(t_stop)
+    fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in kernel_events)
+    bwd_ms = statistics.mean(e[2].elapsed_time(e[3]) for e in kernel_events)
+    _lib.check(lib.fdma_last_kernel_status(stream.cuda_stream, None), "kernel status")
+
+    # ---- end to end through the public API with pinned host buffers ----
+    host_in = {n: t.detach().cpu().pin_memory() for n, t in (("q", q), ("k", k), ("v", v), ("bias", bias),
+                                                              ("dout", dout), ("mask", mask))}
+    host_out = {n: torch.empty(t.shape, dtype=t.dtype).pin_memory()
+                for n, t in (("out", out), ("dq", dq), ("dk", dk), ("dv", dv), ("dbias", dbias))}
+    h2d = sum(t.numel() * t.element_size() for t in host_in.values())
+    d2h = sum(t.numel() * t.element_size() for t in host_out.values())
+
+    def e2e_step():
+        dq_, dk_, dv_, db_ = (host_in[n].to(dev, non_blocking=True).requires_grad_(True) for n in ("q", "k", "v", "bias"))
+        do_ = host_in["dout"].to(dev, non_blocking=True)
+        m_ = host_in["mask"].to(dev, non_blocking=True)
+        o = flash_sparse_attn_func(dq_, dk_, dv_, attn_mask=m_, attn_bias=db_, is_causal=True)
+        o.backward(do_)
+        host_out["out"].copy_(o.detach(), non_blocking=True)
+        host_out["dq"].copy_(dq_.grad, non_blocking=True)
+        host_out["dk"].copy_(dk_.grad, non_blocking=True)
+        host_out["dv"].copy_(dv_.grad, non_blocking=True)
+        host_out["dbias"].copy_(db_.grad, non_blocking=True)
+
+    e2e_ms = float("nan")
+    if not args.no_e2e:
+        e2e_steps = max(1, min(args.steps, 5))
+        e2e_step()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(e2e_steps):
+            e2e_step()
+        e1.record(stream)
+        barrier()
+        e2e_ms = e0.elapsed_time(e1) / e2e_steps
+
+    # ---- max over ranks ----
+    vals = torch.tensor([ms_total, e2e_ms, fwd_ms, bwd_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+    ms_total, e2e_ms, fwd_ms, bwd_ms = vals.tolist()
+    flop_sum = torch.tensor([float(flops["total"]), float(flops["canonical_128x128"]), float(flops["causal_dense"]),
+                             float(flops["bwd"]), float(flops["fwd"])], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(flop_sum, op=dist.ReduceOp.SUM)
+    if rank != 0:
+        return
+    tot, canon, dense, bwd_fl, fwd_fl = flop_sum.tolist()
+    ms_per_step = ms_total / args.steps
+    value = tot / (ms_per_step * 1e-3) / 1e12
+    peak, peak_src = load_peaks()
+    bwd_tflops = (bwd_fl / world) / (bwd_ms * 1e-3) / 1e12  # per launch, per GPU
+    cpu = cpu_sample(1, 1) if world == 1 and not args.no_cpu else None
+    line = {
+        "metric": "fwd+bwd TFLOP/s on kept blocks", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "global_batch": B * world, "seq_len": S, "window": WINDOW,
+                   "parallelism": f"(batch x kv-head) units sharded over {world} GPU(s), no collective",
+                   "l2": "inputs larger than L2 (Q alone is 256 MiB per batch element)",
+                   "tiles": {"fwd": list(FWD_TILE), "bwd": list(BWD_TILE)}},
+        "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
+        "tflops_canonical_128x128_tiles": canon / (ms_per_step * 1e-3) / 1e12,
+        "tflops_causal_dense": dense / (ms_per_step * 1e-3) / 1e12,
+        "utilisation_of_nominal_2250": value / world / NOMINAL_TFLOPS,
+        "roofline": {"bound": "tensor", "kernel": "bwd_kernel", "achieved": bwd_tflops, "peak": peak,
+                     "unit": "TFLOP/s", "frac": bwd_tflops / peak, "peak_source": "of " + peak_src,
+                     "traffic": None, "fwd_kernel_achieved": (fwd_fl / world) / (fwd_ms * 1e-3) / 1e12},
+        "e2e": {"value": tot / (e2e_ms * 1e-3) / 1e12 if e2e_ms == e2e_ms else None, "unit": "TFLOP/s",
+                "ms_per_step": e2e_ms if e2e_ms == e2e_ms else None,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": args.steps * 4,  # fwd_kernel + bwd_prep_kernel + bwd_kernel + bwd_convert_dq_kernel
+        "clocks": clocks,
+    }
+    if cpu is not None:
+        line["cpu_baseline"] = {k_: cpu[k_] for k_ in ("value", "unit", "cores", "kind", "sample")}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch-per-gpu", type=int, default=1)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg (profiling runs)")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
+    ap.add_argument("--seq-len", type=int, default=S, help="profiling only: shorter sequence")
+    ap.add_argument("--window", type=int, default=WINDOW, help="profiling only: window for --seq-len")
+    args = ap.parse_args()
+    if args.impl == "ours":
+        args.warmup = max(args.warmup, 3)
+    if args.seq_len != S or args.window != WINDOW:
+        set_geometry(args.seq_len, args.window)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if world > 1:
+        import torch.distributed as dist
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
+    try:
+        run_ours(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

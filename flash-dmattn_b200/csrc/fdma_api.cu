@@ -96,6 +96,18 @@ int encode_tmap_4d(void* out_map, const void* base, int elem_bytes, const uint64
   return r == CUDA_SUCCESS ? 0 : FDMA_ERR_DRIVER;
 }
 
+namespace {
+thread_local cudaEvent_t t_ev_start = nullptr;
+thread_local cudaEvent_t t_ev_stop = nullptr;
+}  // namespace
+
+void take_timing_events(cudaEvent_t* start, cudaEvent_t* stop) {
+  *start = t_ev_start;
+  *stop = t_ev_stop;
+  t_ev_start = nullptr;
+  t_ev_stop = nullptr;
+}
+
 int* kernel_status_ptr() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
@@ -186,6 +198,11 @@ int fdma_create_mask(const fdma_mask_params* p, void* stream_) {
     return n ? static_cast<int>(cudaMemsetAsync(p->out, 0, n, stream)) : 0;
   }
   return create_mask(*p, stream);
+}
+
+void fdma_time_next_kernel(void* start_event, void* stop_event) {
+  t_ev_start = static_cast<cudaEvent_t>(start_event);
+  t_ev_stop = static_cast<cudaEvent_t>(stop_event);
 }
 
 int fdma_last_kernel_status(void* stream_, int32_t* detail) {

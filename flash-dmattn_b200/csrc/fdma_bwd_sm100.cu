@@ -11,8 +11,8 @@
 //   St  = K Q^T        (128 keys x 64 queries, SS MMA)        dPt = V dO^T        (SS MMA)
 //   P^T, dS^T          written back into the St / dPt columns as 16-bit, used as the A operand (from TMEM) of
 //   dV += P^T dO,  dK += dS^T Q   (B = dO / Q tiles read MN-major from the same shared-memory copy)
-//   dQ^T = K^T dS^T    (A = K MN-major, B = dS^T staged in shared memory), added to an fp32 dQ buffer with
-//                      red.global.add by a dedicated warpgroup (lane = head-dim index -> 128-byte coalesced)
+//   dQ^T = K^T dS^T    (A = K MN-major, B = dS^T staged in shared memory), added to an fp32 dQ buffer by a
+//                      dedicated warpgroup: transpose through shared memory, one bulk reduce-add per 32 queries
 // Query-broadcast bias gives dBias = column sums of dS: one fp32 register per softmax thread for the whole CTA.
 //
 // Warps: 0 TMA producer | 1 MMA issuer | 4-7, 8-11 softmax (query columns 0-31 / 32-63) | 12-15 dQ writer.
@@ -50,7 +50,7 @@ struct BwdKernelParams {
   const void* bias;
   const float* lse2;   // (B,H,Sq_r) LSE * log2(e); +inf for empty and padded rows
   const float* dsum;   // (B,H,Sq_r) D = rowsum(dO o O)
-  float* dq_acc;       // (B,Sq,H,128) fp32, zeroed by the launcher
+  float* dq_acc;       // (B,H,Sq,128) fp32, zeroed by the launcher
   void* dk;
   void* dv;
   void* dbias;         // direct / column-sum modes: the output tensor
@@ -77,7 +77,10 @@ struct SmemB {
   static constexpr int kDsOff = kQdoOff + kQStages * kStageBytes;  // 160 KB
   static constexpr int kDsBytes = kBN * kBM * 2;                   // 16 KB
   static constexpr int kActOff = kDsOff + 2 * kDsBytes;            // 192 KB
-  static constexpr int kRedOff = kActOff + kMaxAct;
+  static constexpr int kLdOff = kActOff + kMaxAct;                 // per stage: 64 x LSE*log2e, 64 x D (fp32)
+  static constexpr int kLdBytes = 2 * kBM * 4;
+  static constexpr int kDqOff = kLdOff + kQStages * kLdBytes;      // [32 q][128 d] fp32 staging tile of the dQ writer
+  static constexpr int kRedOff = kDqOff + 32 * kD * 4;
   static constexpr int kBarOff = kRedOff + kBN * 4;
   static constexpr int kNumBars = 1 + 2 * kQStages + 2 + 1 + 1 + 1 + 1 + 2 + 1;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
@@ -136,7 +139,7 @@ __global__ void bwd_prep_kernel(const void* __restrict__ out, const void* __rest
   }
 }
 
-// fp32 dQ accumulator (B,Sq,H,128) * scale -> dq (strided, 16-bit)
+// fp32 dQ accumulator (B,H,Sq,128) * scale -> dq (B,Sq,H,128 strided, 16-bit)
 template <bool kBf16>
 __global__ void bwd_convert_dq_kernel(const float* __restrict__ acc, void* __restrict__ dq, int64_t n_vec, int Sq,
                                       int H, int64_t sb, int64_t sr, int64_t sh, float scale) {
@@ -144,9 +147,9 @@ __global__ void bwd_convert_dq_kernel(const float* __restrict__ acc, void* __res
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const int64_t e = i * 8;
     const int dd = static_cast<int>(e % kD);
-    const int h = static_cast<int>((e / kD) % H);
-    const int q = static_cast<int>((e / (static_cast<int64_t>(kD) * H)) % Sq);
-    const int b = static_cast<int>(e / (static_cast<int64_t>(kD) * H * Sq));
+    const int q = static_cast<int>((e / kD) % Sq);
+    const int h = static_cast<int>((e / (static_cast<int64_t>(kD) * Sq)) % H);
+    const int b = static_cast<int>(e / (static_cast<int64_t>(kD) * Sq * H));
     const float4 x = *reinterpret_cast<const float4*>(acc + e);
     const float4 y = *reinterpret_cast<const float4*>(acc + e + 4);
     uint4 o;
@@ -195,6 +198,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
   unsigned char* s_qdo = smem + L::kQdoOff;
   unsigned char* s_ds = smem + L::kDsOff;
   uint8_t* s_act = smem + L::kActOff;
+  float* s_ld = reinterpret_cast<float*>(smem + L::kLdOff);
   float* s_red = reinterpret_cast<float*>(smem + L::kRedOff);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
   uint64_t* bar_kv = bars;
@@ -304,6 +308,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
     if (warp == 0) {
       // ---------------- TMA producer ----------------
       if (lane == 0 && n_steps > 0) {
+        FDMA_PROF_BEGIN();
         mbar_arrive_expect_tx(bar_kv, 2 * kBN * kD * 2);
 #pragma unroll
         for (int kb = 0; kb < 2; ++kb) {
@@ -316,11 +321,14 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
           for (int g = 0; g < G; ++g) {
             if (!s_act[(act_g > 1 ? g : 0) * MT + (m >> 1)]) continue;
             const int stage = i % kQStages;
-            ok = mbar_wait(bar_qdo_empty + stage, ((i / kQStages) & 1) ^ 1, ctl, kWaitQdoEmpty);
+            ok = FDMA_PROF_WAIT(0, mbar_wait(bar_qdo_empty + stage, ((i / kQStages) & 1) ^ 1, ctl, kWaitQdoEmpty));
             if (!ok) break;
-            mbar_arrive_expect_tx(bar_qdo_full + stage, L::kStageBytes);
+            mbar_arrive_expect_tx(bar_qdo_full + stage, L::kStageBytes + L::kLdBytes);
             unsigned char* dst = s_qdo + stage * L::kStageBytes;
             const int h = hk * G + g;
+            const int64_t row0 = (static_cast<int64_t>(b) * p.h + h) * p.sq_r + m * kBM;
+            bulk_load_1d(s_ld + stage * (2 * kBM), p.lse2 + row0, kBM * 4, bar_qdo_full + stage);
+            bulk_load_1d(s_ld + stage * (2 * kBM) + kBM, p.dsum + row0, kBM * 4, bar_qdo_full + stage);
 #pragma unroll
             for (int kb = 0; kb < 2; ++kb) {
               tma_load_4d(dst + kb * (kBM * 128), &p.tm_q, bar_qdo_full + stage, kb * 64, h, m * kBM, b);
@@ -329,10 +337,11 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
             ++i;
           }
         }
+        FDMA_PROF_END(0, true);
       }
     } else if (warp == 1) {
-      // ---------------- MMA issuer ----------------
-      if (lane == 0 && n_steps > 0) {
+      // ---------------- MMA issuer (whole warp, uniform control flow; the issue wrappers elect one lane) -------
+      if (n_steps > 0) {
         constexpr uint32_t idesc_s = umma_idesc(kBN, kBM, kBf16, false, false);  // St/dPt: 128 x 64, K-major
         constexpr uint32_t idesc_g = umma_idesc(kBN, kD, kBf16, false, true);    // dV/dK: A from TMEM, B MN-major
         constexpr uint32_t idesc_q = umma_idesc(kD, kBM, kBf16, true, true);     // dQ^T: both MN-major
@@ -360,28 +369,38 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
           }
           umma_commit(bar_dp_full);
         };
-        bool ok = mbar_wait(bar_kv, 0, ctl, kWaitKv);
-        if (ok) ok = mbar_wait(bar_qdo_full + 0, 0, ctl, kWaitQdoFull);
+        FDMA_PROF_BEGIN();
+        bool ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(0, mbar_wait(bar_kv, 0, ctl, kWaitKv)));
+        if (ok) ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(1, mbar_wait(bar_qdo_full + 0, 0, ctl, kWaitQdoFull)));
         if (ok) {
           tc_fence_after_sync();
           issue_st(0);
           issue_dp(0);
         }
         if (ok && n_steps > 1) {
-          ok = mbar_wait(bar_qdo_full + 1, 0, ctl, kWaitQdoFull);
+          ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(1, mbar_wait(bar_qdo_full + 1, 0, ctl, kWaitQdoFull)));
           if (ok) {
             tc_fence_after_sync();
             issue_st(1);
           }
         }
         for (int i = 0; i < n_steps && ok; ++i) {
-          ok = mbar_wait(bar_pds, i & 1, ctl, kWaitPds);
+          ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(2, mbar_wait(bar_pds, i & 1, ctl, kWaitPds)));
           if (!ok) break;
           tc_fence_after_sync();
           const uint32_t stage_addr = qdo_addr + (i % kQStages) * L::kStageBytes;
           const uint32_t acc = i > 0 ? 1u : 0u;
-          // dV += P^T dO, dK += dS^T Q : 4 k-steps of 16 queries; query columns 0-31 live in TMEM columns
-          // [0,16) of the St / dPt block and queries 32-63 in columns [32,48)
+          // A operands from TMEM: queries 0-31 sit in columns [0,16) of the St / dPt block, queries 32-63 in
+          // columns [32,48) (each softmax warpgroup writes back into the columns it read).
+          // Order: dK first, because it frees the dPt columns for the next step's dP -- the product the softmax
+          // threads wait for next; dV, dQ and the S of step i+2 follow behind it.
+#pragma unroll
+          for (int s = 0; s < 4; ++s) {
+            const uint32_t a_col = (s < 2 ? s * 8 : 32 + (s - 2) * 8);
+            umma_ts(tmem_base + kColDk, tmem_base + kColDp + a_col,
+                    umma_desc_sw128(stage_addr + s * 2048, kBM * 128, 1024), idesc_g, (acc || s > 0) ? 1u : 0u);
+          }
+          if (i + 1 < n_steps) issue_dp(i + 1);
 #pragma unroll
           for (int s = 0; s < 4; ++s) {
             const uint32_t a_col = (s < 2 ? s * 8 : 32 + (s - 2) * 8);
@@ -389,14 +408,8 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
                     umma_desc_sw128(stage_addr + L::kQBytes + s * 2048, kBM * 128, 1024), idesc_g,
                     (acc || s > 0) ? 1u : 0u);
           }
-#pragma unroll
-          for (int s = 0; s < 4; ++s) {
-            const uint32_t a_col = (s < 2 ? s * 8 : 32 + (s - 2) * 8);
-            umma_ts(tmem_base + kColDk, tmem_base + kColDp + a_col,
-                    umma_desc_sw128(stage_addr + s * 2048, kBM * 128, 1024), idesc_g, (acc || s > 0) ? 1u : 0u);
-          }
           if (i > 0) {
-            ok = mbar_wait(bar_dq_empty, (i - 1) & 1, ctl, kWaitDqEmpty);
+            ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(3, mbar_wait(bar_dq_empty, (i - 1) & 1, ctl, kWaitDqEmpty)));
             if (!ok) break;
             tc_fence_after_sync();
           }
@@ -409,15 +422,16 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
           umma_commit(bar_dq_full);
           umma_commit(bar_qdo_empty + (i % kQStages));
           umma_commit(bar_ds_empty + (i & 1));
-          if (i + 1 < n_steps) issue_dp(i + 1);
           if (i + 2 < n_steps) {
-            ok = mbar_wait(bar_qdo_full + ((i + 2) % kQStages), ((i + 2) / kQStages) & 1, ctl, kWaitQdoFull);
+            ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(1, mbar_wait(bar_qdo_full + ((i + 2) % kQStages),
+                                                                     ((i + 2) / kQStages) & 1, ctl, kWaitQdoFull)));
             if (!ok) break;
             tc_fence_after_sync();
             issue_st(i + 2);
           }
         }
         umma_commit(bar_final);
+        FDMA_PROF_END(8, lane == 0);
       }
     }
   } else if (warp < 12) {
@@ -435,8 +449,21 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
     for (int j = 0; j < 32; ++j) dacc[j] = 0.f;
     const bool direct_group = mode == kDbDirect && p.dbias_h != p.h;  // one dbias head per kv head
     uint16_t* dbias16 = reinterpret_cast<uint16_t*>(p.dbias);
+    // Row-broadcast bias / mask that do not depend on the query head: one value per thread for the whole CTA.
+    const bool hoist = kBcast && (G == 1 || ((!p.bias || p.h_bias != p.h) && (!p.mask || p.h_mask != p.h)));
+    float bv_h = 0.f;
+    bool kp_h = key_ok;
+    if (hoist) {
+      const int hq0 = hk * G;
+      const int hm0 = hq0 / (p.h / p.h_mask), hb0 = hq0 / (p.h / p.h_bias);
+      if (p.bias)
+        bv_h = raw16_to_float<kBf16>(reinterpret_cast<const uint16_t*>(p.bias)[b * p.bias_batch_stride +
+                                                                            hb0 * p.bias_head_stride + key]) * kLog2e;
+      if (p.mask && kp_h) kp_h = p.mask[b * p.mask_batch_stride + hm0 * p.mask_head_stride + key] != 0;
+    }
     int i = 0;
     bool ok = true;
+    FDMA_PROF_BEGIN();
     const int m_first = (mode == kDbDirect) ? 0 : m_start;  // direct mode also zero-fills tiles it skips
     for (int m = m_first; m < M64 && ok; ++m) {
       const int q0 = m * kBM + half * 32;
@@ -458,12 +485,14 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         float bias2[32];
         uint32_t keep = 0;  // bit j: element (q0 + j, key) is kept
         if (kBcast) {
-          float bv = 0.f;
-          if (p.bias)
-            bv = raw16_to_float<kBf16>(reinterpret_cast<const uint16_t*>(p.bias)[b * p.bias_batch_stride +
-                                                                              hb * p.bias_head_stride + key]) * kLog2e;
-          bool kp = key_ok;
-          if (p.mask && kp) kp = p.mask[b * p.mask_batch_stride + hm * p.mask_head_stride + key] != 0;
+          float bv = bv_h;
+          bool kp = kp_h;
+          if (!hoist) {
+            if (p.bias)
+              bv = raw16_to_float<kBf16>(reinterpret_cast<const uint16_t*>(p.bias)[b * p.bias_batch_stride +
+                                                                                hb * p.bias_head_stride + key]) * kLog2e;
+            if (p.mask && kp) kp = p.mask[b * p.mask_batch_stride + hm * p.mask_head_stride + key] != 0;
+          }
 #pragma unroll
           for (int j = 0; j < 32; ++j) bias2[j] = bv;
           keep = kp ? 0xFFFFFFFFu : 0u;
@@ -485,56 +514,55 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
           for (int j = 0; j < 32; ++j)
             if (key > q0 + j + off) keep &= ~(1u << j);
         }
-        const float* lrow = p.lse2 + (static_cast<int64_t>(b) * p.h + h) * p.sq_r + q0;
-        const float* drow = p.dsum + (static_cast<int64_t>(b) * p.h + h) * p.sq_r + q0;
+        // LSE*log2e and D of the step's 64 queries arrive in shared memory with the Q/dO stage
+        const float* lrow = s_ld + (i % kQStages) * (2 * kBM) + half * 32;
+        const float* drow = lrow + kBM;
 
-        // ---- P^T ----
-        ok = __all_sync(0xffffffffu, mbar_wait(bar_s_full + (i & 1), (i >> 1) & 1, ctl, kWaitSFull));
+        // ---- P^T and dS^T in one pass: both accumulators are loaded together ----
+        // (the stage barrier has long completed when S arrives; waiting on it makes the bulk-copied LSE / D
+        // values visible to this thread)
+        ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(0, mbar_wait(bar_qdo_full + (i % kQStages), (i / kQStages) & 1,
+                                                                   ctl, kWaitQdoFull)));
         if (!ok) break;
-        tc_fence_after_sync();
-        float pv[32];
-        {
-          uint32_t r[32];
-          tmem_ld_x32(tmem_base + lane_addr + kColSt + (i & 1) * kBM + half * 32, r);
-          tmem_wait_ld();
-#pragma unroll
-          for (int j4 = 0; j4 < 8; ++j4) {
-            const float4 l4 = __ldg(reinterpret_cast<const float4*>(lrow) + j4);
-            const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int j = j4 * 4 + e;
-              const float x = fmaf(__uint_as_float(r[j]), p.scale_log2, bias2[j]) - lv[e];
-              pv[j] = ((keep >> j) & 1u) ? fast_exp2(x) : 0.f;
-            }
-          }
-          uint32_t pk[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) pk[j] = pack_16x2<kBf16>(pv[2 * j], pv[2 * j + 1]);
-          tmem_st_x16(tmem_base + lane_addr + kColSt + (i & 1) * kBM + half * 32, pk);
-        }
-        // ---- dS^T ----
-        ok = __all_sync(0xffffffffu, mbar_wait(bar_dp_full, i & 1, ctl, kWaitDpFull));
+        ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(1, mbar_wait(bar_s_full + (i & 1), (i >> 1) & 1, ctl, kWaitSFull)));
+        if (!ok) break;
+        ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(2, mbar_wait(bar_dp_full, i & 1, ctl, kWaitDpFull)));
         if (!ok) break;
         tc_fence_after_sync();
         uint32_t dsk[16];
         {
-          uint32_t r[32];
-          tmem_ld_x32(tmem_base + lane_addr + kColDp + half * 32, r);
+          uint32_t rs[32], rp[32];
+          tmem_ld_x32(tmem_base + lane_addr + kColSt + (i & 1) * kBM + half * 32, rs);
+          tmem_ld_x32(tmem_base + lane_addr + kColDp + half * 32, rp);
           tmem_wait_ld();
-          float step_sum = 0.f;
+          float pv[32];
+          float part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
           for (int j4 = 0; j4 < 8; ++j4) {
-            const float4 d4 = __ldg(reinterpret_cast<const float4*>(drow) + j4);
+            const float4 l4 = reinterpret_cast<const float4*>(lrow)[j4];
+            const float4 d4 = reinterpret_cast<const float4*>(drow)[j4];
+            const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
             const float dv4[4] = {d4.x, d4.y, d4.z, d4.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const int j = j4 * 4 + e;
-              const float ds = pv[j] * (__uint_as_float(r[j]) - dv4[e]);
+              const float x = fmaf(__uint_as_float(rs[j]), p.scale_log2, bias2[j]) - lv[e];
+              const float pj = ((keep >> j) & 1u) ? fast_exp2(x) : 0.f;
+              const float ds = pj * (__uint_as_float(rp[j]) - dv4[e]);
+              rs[j] = __float_as_uint(pj);
               pv[j] = ds;
-              step_sum += ds;
+              part[e] += ds;
             }
           }
+          uint32_t pk[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            pk[j] = pack_16x2<kBf16>(__uint_as_float(rs[2 * j]), __uint_as_float(rs[2 * j + 1]));
+            dsk[j] = pack_16x2<kBf16>(pv[2 * j], pv[2 * j + 1]);
+          }
+          tmem_st_x16(tmem_base + lane_addr + kColSt + (i & 1) * kBM + half * 32, pk);
+          tmem_st_x16(tmem_base + lane_addr + kColDp + half * 32, dsk);
+          const float step_sum = (part[0] + part[1]) + (part[2] + part[3]);
           if (mode == kDbColsum) {
             colsum += step_sum;
           } else if (mode == kDbDirect) {
@@ -559,12 +587,10 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
                 if (q0 + j < Sq && pv[j] != 0.f) atomicAdd(base + static_cast<int64_t>(q0 + j) * p.dbias_keys, pv[j]);
             }
           }
-#pragma unroll
-          for (int j = 0; j < 16; ++j) dsk[j] = pack_16x2<kBf16>(pv[2 * j], pv[2 * j + 1]);
-          tmem_st_x16(tmem_base + lane_addr + kColDp + half * 32, dsk);
         }
         // ---- dS^T tile to shared memory for the dQ MMA: row = key, 64 queries x 2 B = 128 B, 128-byte swizzle ----
-        ok = __all_sync(0xffffffffu, mbar_wait(bar_ds_empty + (i & 1), ((i >> 1) & 1) ^ 1, ctl, kWaitDsEmpty));
+        ok = __all_sync(0xffffffffu,
+                        FDMA_PROF_WAIT(3, mbar_wait(bar_ds_empty + (i & 1), ((i >> 1) & 1) ^ 1, ctl, kWaitDsEmpty)));
         if (!ok) break;
         {
           unsigned char* rowp = s_ds + (i & 1) * L::kDsBytes + krow * 128;
@@ -590,6 +616,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         }
       }
     }
+    FDMA_PROF_END(16, tid == 128);
     // ---------------- epilogue: dV (half 0) and dK (half 1), column-sum dBias ----------------
     if (mode == kDbColsum) {
       if (half == 1) s_red[krow] = colsum;
@@ -634,36 +661,56 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
       }
     }
   } else {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
     // ---------------- dQ writer: thread = head-dim index (row of dQ^T) ----------------
+    // dQ^T (128 d x 64 q, fp32) leaves TMEM in two halves of 32 queries: transposed into a [32 q][128 d] fp32
+    // staging tile in shared memory, then ONE bulk reduce-add (cp.reduce.async.bulk ... add.f32) per half into
+    // the fp32 dQ buffer, whose (B,H,Sq,128) layout makes the 32 rows contiguous.
     const int dl = (warp & 3) * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    float* s_dq = reinterpret_cast<float*>(smem + L::kDqOff);
     int i = 0;
     bool ok = true;
+    FDMA_PROF_BEGIN();
     for (int m = m_start; m < M64 && ok; ++m) {
       for (int g = 0; g < G && ok; ++g) {
         if (!s_act[(act_g > 1 ? g : 0) * MT + (m >> 1)]) continue;
         const int h = hk * G + g;
-        ok = __all_sync(0xffffffffu, mbar_wait(bar_dq_full, i & 1, ctl, kWaitDqFull));
+        ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(0, mbar_wait(bar_dq_full, i & 1, ctl, kWaitDqFull)));
         if (!ok) break;
         tc_fence_after_sync();
-        float* base = p.dq_acc + ((static_cast<int64_t>(b) * Sq + m * kBM) * p.h + h) * kD + dl;
+        uint32_t r0[32], r1[32];
+        tmem_ld_x32(tmem_base + lane_addr + kColDq, r0);
+        tmem_ld_x32(tmem_base + lane_addr + kColDq + 32, r1);
+        tmem_wait_ld();
+        tc_fence_before_sync();
+        mbar_arrive(bar_dq_empty);  // dQ^T columns may be overwritten by the next step from here on
+        float* gdst = p.dq_acc + ((static_cast<int64_t>(b) * p.h + h) * Sq + m * kBM) * kD;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
-          uint32_t r[32];
-          tmem_ld_x32(tmem_base + lane_addr + kColDq + c * 32, r);
-          tmem_wait_ld();
+          if (tid == 384) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // staging tile free again
+          named_bar_sync(2, 128);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int q = m * kBM + c * 32 + j;
-            if (q < Sq) atomicAdd(base + static_cast<int64_t>(c * 32 + j) * p.h * kD, __uint_as_float(r[j]));
+          for (int j = 0; j < 32; ++j) s_dq[j * kD + dl] = __uint_as_float(c == 0 ? r0[j] : r1[j]);
+          fence_proxy_async_smem();
+          named_bar_sync(3, 128);
+          if (tid == 384) {
+            const int rows = min(32, Sq - (m * kBM + c * 32));
+            if (rows > 0) {
+              asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;"
+                           :
+                           : "l"(reinterpret_cast<uint64_t>(gdst + c * 32 * kD)), "r"(smem_u32(s_dq)),
+                             "r"(static_cast<uint32_t>(rows * kD * 4))
+                           : "memory");
+            }
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           }
         }
-        tc_fence_before_sync();
-        mbar_arrive(bar_dq_empty);
         ++i;
       }
     }
+    if (tid == 384) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    FDMA_PROF_END(24, tid == 384);
   }
 
   // ---------------- tear-down ----------------
@@ -805,7 +852,11 @@ int launch(const fdma_bwd_params& bp, const BwdPlan& pl, cudaStream_t stream) {
   e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemB::kAlloc);
   if (e != cudaSuccess) return static_cast<int>(e);
   dim3 grid((p.seqlen_k + kBN - 1) / kBN, p.h_k, p.b);
+  cudaEvent_t ev0, ev1;
+  take_timing_events(&ev0, &ev1);
+  if (ev0) cudaEventRecord(ev0, stream);
   kern<<<grid, kThreads, SmemB::kAlloc, stream>>>(kp);
+  if (ev1) cudaEventRecord(ev1, stream);
   e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
 
@@ -859,3 +910,17 @@ int tc_bwd(const fdma_bwd_params& p, cudaStream_t stream) {
 }
 
 }  // namespace fdma
+
+#ifdef FDMA_PROF
+// Tracing build only: copies the backward kernel's 64 wait-cycle counters to `out` and clears them.
+// Slots: [0,8) producer, [8,16) MMA issuer, [16,24) one softmax thread, [24,32) one dQ-writer thread; slot 7 of
+// each group is the role's lifetime in cycles, the others are per-wait totals in the order of the source.
+extern "C" int fdma_prof_read_bwd(unsigned long long* out) {
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  e = cudaMemcpyFromSymbol(out, fdma::g_prof, sizeof(unsigned long long) * 64);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  static const unsigned long long zeros[64] = {};
+  return static_cast<int>(cudaMemcpyToSymbol(fdma::g_prof, zeros, sizeof(zeros)));
+}
+#endif

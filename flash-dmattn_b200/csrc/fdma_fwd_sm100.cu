@@ -239,6 +239,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
   asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
   if (warp == 0) {
     if (lane == 0 && nT > 0) {
+      FDMA_PROF_BEGIN();
       // Q tiles (rows beyond Sq are zero-filled by TMA)
       mbar_arrive_expect_tx(bar_q, kNQ * L::kQBytes);
 #pragma unroll
@@ -253,7 +254,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
 #pragma unroll
         for (int kv = 0; kv < 2; ++kv) {
           const int slot = it % kStages;
-          ok = mbar_wait(bar_kv_empty + slot, ((it / kStages) & 1) ^ 1, ctl, kWaitKvEmpty);
+          ok = FDMA_PROF_WAIT(0, mbar_wait(bar_kv_empty + slot, ((it / kStages) & 1) ^ 1, ctl, kWaitKvEmpty));
           if (!ok) break;
           mbar_arrive_expect_tx(bar_kv_full + slot, L::kKvBytes);
           const CUtensorMap* tm = kv == 0 ? &p.tm_k : &p.tm_v;
@@ -263,13 +264,15 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
           ++it;
         }
       }
+      FDMA_PROF_END(0, true);
     }
   } else if (warp == 1) {
-    if (lane == 0 && nT > 0) {
+    if (nT > 0) {  // whole warp, uniform control flow; the issue wrappers elect one lane
       constexpr uint32_t idesc_qk = umma_idesc(kBM, kBN, kBf16, false, false);
       constexpr uint32_t idesc_pv = umma_idesc(kBM, D, kBf16, false, true);
       const uint32_t q_addr = smem_u32(s_q), kv_addr = smem_u32(s_kv);
-      bool ok = mbar_wait(bar_q, 0, ctl, kWaitQ);
+      FDMA_PROF_BEGIN();
+      bool ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(0, mbar_wait(bar_q, 0, ctl, kWaitQ)));
       tc_fence_after_sync();
       int a = 0;            // index of the current kept tile; its K is ring item 2a, its V item 2a+1
       int prev_j = -1;      // previous kept tile (its PV is still to be issued)
@@ -281,11 +284,13 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
         const uint8_t pfl = prev_j >= 0 ? s_flags[prev_j] : 0;
         const int k_it = 2 * a, v_it = 2 * (a - 1) + 1;
         if (!last) {
-          ok = mbar_wait(bar_kv_full + (k_it % kStages), (k_it / kStages) & 1, ctl, kWaitKvFullK);
+          ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(1, mbar_wait(bar_kv_full + (k_it % kStages), (k_it / kStages) & 1,
+                                                                     ctl, kWaitKvFullK)));
           if (!ok) break;
         }
         if (prev_j >= 0) {
-          ok = mbar_wait(bar_kv_full + (v_it % kStages), (v_it / kStages) & 1, ctl, kWaitKvFullV);
+          ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(2, mbar_wait(bar_kv_full + (v_it % kStages), (v_it / kStages) & 1,
+                                                                     ctl, kWaitKvFullV)));
           if (!ok) break;
         }
         tc_fence_after_sync();
@@ -293,7 +298,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
         for (int t = 0; t < kNQ; ++t) {
           const uint32_t s_col = tmem_base + t * kBN;
           if (pfl & (1 << t)) {
-            ok = mbar_wait(bar_p_full + t, pcnt[t] & 1, ctl, kWaitP);
+            ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(3 + t, mbar_wait(bar_p_full + t, pcnt[t] & 1, ctl, kWaitP)));
             if (!ok) break;
             tc_fence_after_sync();
             const uint32_t o_col = tmem_base + 2 * kBN + t * 128;
@@ -326,6 +331,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
         }
       }
       umma_commit(bar_o_done);
+      FDMA_PROF_END(8, lane == 0);
     }
   } else if (warp == 2) {
     if (kBcast) {
@@ -383,6 +389,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
                qclamp * p.bias_row_stride;
     }
     float m_ref = -CUDART_INF_F, l = 0.f;
+    FDMA_PROF_BEGIN();
     uint32_t scnt = 0;
     int bi = 0;
     bool ok = true;
@@ -391,11 +398,11 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
       if (fl == 0) continue;
       const int slot = bi % kBmSlots;
       if (kBcast) {
-        ok = __all_sync(0xffffffffu, mbar_wait(bar_bm_full + slot, (bi / kBmSlots) & 1, ctl, kWaitBmFull));
+        ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(0, mbar_wait(bar_bm_full + slot, (bi / kBmSlots) & 1, ctl, kWaitBmFull)));
         if (!ok) break;
       }
       if (fl & (1 << t)) {
-        ok = __all_sync(0xffffffffu, mbar_wait(bar_s_full + t, scnt & 1, ctl, kWaitS));
+        ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(1, mbar_wait(bar_s_full + t, scnt & 1, ctl, kWaitS)));
         if (!ok) break;
         tc_fence_after_sync();
         float s[kBN];
@@ -456,9 +463,18 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
               if (kbase + i >= klim) s[i] = -CUDART_INF_F;
           }
         }
-        float m_tile = -CUDART_INF_F;
+        float m_tile;
+        {  // four independent chains instead of one 128-long dependent chain
+          float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
-        for (int i = 0; i < kBN; ++i) m_tile = fmaxf(m_tile, s[i]);
+          for (int i = 0; i < kBN; i += 4) {
+            mx[0] = fmaxf(mx[0], s[i]);
+            mx[1] = fmaxf(mx[1], s[i + 1]);
+            mx[2] = fmaxf(mx[2], s[i + 2]);
+            mx[3] = fmaxf(mx[3], s[i + 3]);
+          }
+          m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+        }
         const bool need = m_tile > m_ref + kRescaleThreshold || (m_ref == -CUDART_INF_F && m_tile > m_ref);
         if (__any_sync(0xffffffffu, need)) {
           const float m_new = need ? fmaxf(m_ref, m_tile) : m_ref;
@@ -479,7 +495,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
           m_ref = m_new;
         }
         const float m_use = (m_ref == -CUDART_INF_F) ? 0.f : m_ref;
-        float lsum = 0.f;
+        float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int c = 0; c < kBN / 32; ++c) {
           uint32_t pk[16];
@@ -487,12 +503,12 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
           for (int i = 0; i < 16; ++i) {
             const float p0 = fast_exp2(s[c * 32 + 2 * i] - m_use);
             const float p1 = fast_exp2(s[c * 32 + 2 * i + 1] - m_use);
-            lsum += p0 + p1;
+            ls[i & 3] += p0 + p1;
             pk[i] = pack_16x2<kBf16>(p0, p1);
           }
           tmem_st_x16(s_taddr + c * 16, pk);
         }
-        l += lsum;
+        l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
         tmem_wait_st();
         tc_fence_before_sync();
         mbar_arrive(bar_p_full + t);
@@ -505,7 +521,9 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
       ++bi;
     }
     // ---------------- epilogue ----------------
-    if (ok && nT > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar_o_done, 0, ctl, kWaitO));
+    if (ok && nT > 0) ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(2, mbar_wait(bar_o_done, 0, ctl, kWaitO)));
+    FDMA_PROF_END(16, tid == 128);
+    FDMA_PROF_END(24, tid == 256);
     tc_fence_after_sync();
     if (ok) {
       const bool in_range = qrow < Sq;  // TMEM loads below are warp-collective: every lane runs them
@@ -625,7 +643,11 @@ int launch(const fdma_fwd_params& p, const FwdPlan& pl, cudaStream_t stream) {
     attr_set = true;
   }
   dim3 grid((p.seqlen_q + kNQ * kBM - 1) / (kNQ * kBM), p.h, p.b);
+  cudaEvent_t ev0, ev1;
+  take_timing_events(&ev0, &ev1);
+  if (ev0) cudaEventRecord(ev0, stream);
   kern<<<grid, kThreads, L::kAlloc, stream>>>(kp);
+  if (ev1) cudaEventRecord(ev1, stream);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -688,3 +710,16 @@ int tc_fwd(const fdma_fwd_params& p, cudaStream_t stream) {
 }
 
 }  // namespace fdma
+
+#ifdef FDMA_PROF
+// Tracing build only: forward kernel's wait-cycle counters. Slots: [0,8) producer, [8,16) MMA issuer,
+// [16,24) one softmax thread of query tile 0, [24,32) one of query tile 1; slot 7 of each group is the lifetime.
+extern "C" int fdma_prof_read_fwd(unsigned long long* out) {
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return static_cast<int>(e);
+  e = cudaMemcpyFromSymbol(out, fdma::g_prof, sizeof(unsigned long long) * 64);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  static const unsigned long long zeros[64] = {};
+  return static_cast<int>(cudaMemcpyToSymbol(fdma::g_prof, zeros, sizeof(zeros)));
+}
+#endif

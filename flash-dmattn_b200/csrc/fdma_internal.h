@@ -36,6 +36,9 @@ int create_mask(const fdma_mask_params& p, cudaStream_t stream);
 // Device address of the current device's kernel status word (written by bounded waits that give up).
 int* kernel_status_ptr();
 
+// Events registered by fdma_time_next_kernel for this host thread (both null when none); take_* clears them.
+void take_timing_events(cudaEvent_t* start, cudaEvent_t* stop);
+
 // Encodes a 4-D tiled tensor map (dims innermost first) with 128-byte swizzle; returns 0 or a status.
 int encode_tmap_4d(void* out_map, const void* base, int elem_bytes, const uint64_t dims[4],
                    const uint64_t strides_bytes[3], const uint32_t box[4]);

@@ -92,6 +92,31 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
 }
 
 // ---------------------------------------------------------------------------------------------
+// Optional wait-time tracing (-DFDMA_PROF): each role adds the SM clock cycles it spends inside every kind of
+// wait, and its total lifetime, to a small global table that fdma_prof_read() copies out. Off by default; the
+// macros then cost nothing.
+// ---------------------------------------------------------------------------------------------
+#ifdef FDMA_PROF
+static __device__ unsigned long long g_prof[64];  // one table per translation unit
+#define FDMA_PROF_BEGIN() \
+  unsigned long long prof_acc_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; \
+  const long long prof_t0_ = clock64()
+#define FDMA_PROF_WAIT(slot, expr) \
+  ([&]() { const long long t_ = clock64(); const bool r_ = (expr); prof_acc_[slot] += clock64() - t_; return r_; }())
+#define FDMA_PROF_END(base, active) \
+  do { \
+    if (active) { \
+      prof_acc_[7] = clock64() - prof_t0_; \
+      for (int i_ = 0; i_ < 8; ++i_) atomicAdd(&g_prof[(base) + i_], prof_acc_[i_]); \
+    } \
+  } while (0)
+#else
+#define FDMA_PROF_BEGIN() do {} while (0)
+#define FDMA_PROF_WAIT(slot, expr) (expr)
+#define FDMA_PROF_END(base, active) do {} while (0)
+#endif
+
+// ---------------------------------------------------------------------------------------------
 // Proxy / tcgen05 fences
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() {
@@ -120,6 +145,14 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m
       : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1),
         "r"(c2), "r"(c3)
       : "memory");
+}
+
+// Untiled bulk copy global -> shared (both addresses 16-byte aligned, size a multiple of 16 bytes).
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               :
+               : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gmem_src)), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -166,9 +199,13 @@ __host__ __device__ constexpr uint32_t umma_idesc(int m, int n, bool is_bf16, bo
          (static_cast<uint32_t>(m >> 4) << 24);
 }
 
-// D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.
+// The three issue wrappers below are called by ALL lanes of a converged warp with warp-uniform arguments; one
+// elected lane issues. Keeping the surrounding control flow uniform lets the compiler hold descriptors in
+// uniform registers instead of moving them there one by one for every instruction.
+// D[tmem] (+)= A[smem] * B[smem]
 __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                         uint32_t accumulate) {
+  if (elect_one())
   asm volatile(
       "{\n\t"
       ".reg .pred p;\n\t"
@@ -182,6 +219,7 @@ __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64
 // D[tmem] (+)= A[tmem] * B[smem]; A holds 16-bit values packed two per 32-bit column (lane = M row).
 __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
                                         uint32_t accumulate) {
+  if (elect_one())
   asm volatile(
       "{\n\t"
       ".reg .pred p;\n\t"
@@ -192,8 +230,10 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
       : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-// The mbarrier receives one arrival once every tcgen05.mma issued so far by this thread has completed.
+// The mbarrier receives one arrival once every tcgen05.mma issued so far by the electing warp has completed
+// (elect.sync picks the same lane every time for a full, converged warp).
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  if (elect_one())
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
 }

@@ -57,6 +57,7 @@ EXPORTED_SYMBOLS = (
     "fdma_bwd",
     "fdma_create_mask",
     "fdma_last_kernel_status",
+    "fdma_time_next_kernel",
 )
 
 _lib = None
@@ -88,6 +89,8 @@ def load():
     lib.fdma_create_mask.argtypes = [POINTER(MaskParams), c_void_p]
     lib.fdma_last_kernel_status.restype = c_int
     lib.fdma_last_kernel_status.argtypes = [c_void_p, POINTER(c_int32)]
+    lib.fdma_time_next_kernel.restype = None
+    lib.fdma_time_next_kernel.argtypes = [c_void_p, c_void_p]
     _lib = lib
     return lib
 

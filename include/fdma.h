@@ -161,6 +161,15 @@ int fdma_version(void);
  */
 int fdma_last_kernel_status(void* stream, int32_t* detail);
 
+/*
+ * Measurement hook (no counterpart in the reference, which is timed from Python with wall clocks,
+ * benchmarks/forward_performance.py:388-399). The NEXT fdma_fwd or fdma_bwd call made by this host thread
+ * records `start_event` immediately before and `stop_event` immediately after its main attention kernel
+ * (not the small pre/post kernels), on the stream given to that call, then forgets both. Events are
+ * cudaEvent_t handles created by the caller with timing enabled. Pass NULLs to cancel.
+ */
+void fdma_time_next_kernel(void* start_event, void* stop_event);
+
 #ifdef __cplusplus
 }
 #endif
