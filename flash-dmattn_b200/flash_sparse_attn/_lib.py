@@ -58,6 +58,8 @@ EXPORTED_SYMBOLS = (
     "fdma_create_mask",
     "fdma_last_kernel_status",
     "fdma_time_next_kernel",
+    "fdma_fwd_static_scratch",
+    "fdma_static_scratch_limit",
 )
 
 _lib = None
@@ -89,6 +91,9 @@ def load():
     lib.fdma_create_mask.argtypes = [POINTER(MaskParams), c_void_p]
     lib.fdma_last_kernel_status.restype = c_int
     lib.fdma_last_kernel_status.argtypes = [c_void_p, POINTER(c_int32)]
+    lib.fdma_fwd_static_scratch.restype = c_int
+    lib.fdma_fwd_static_scratch.argtypes = [POINTER(FwdParams), c_void_p]
+    lib.fdma_static_scratch_limit.restype = c_size_t
     lib.fdma_time_next_kernel.restype = None
     lib.fdma_time_next_kernel.argtypes = [c_void_p, c_void_p]
     _lib = lib

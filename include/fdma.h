@@ -162,6 +162,21 @@ int fdma_version(void);
 int fdma_last_kernel_status(void* stream, int32_t* detail);
 
 /*
+ * Forward pass with library-owned scratch. It has no counterpart in the reference (whose C++ side allocates
+ * its own temporaries with torch::empty). Same arguments, results and status codes as fdma_fwd, except that
+ * p->workspace / p->workspace_bytes are ignored: the per-tile activity bytes that a per-query mask needs live in
+ * a fixed 1 MiB array inside the library (fdma_static_scratch_limit() returns that size). It exists for hosts
+ * that cannot supply scratch at call time -- engines that partition device memory once at start-up and give
+ * their operators no allocator, or loops where a device allocation is not acceptable. It allocates and frees
+ * nothing. A problem needing more than the limit (B * h_mask * ceil(Sq/128) * ceil(Sk/128) bytes) returns
+ * FDMA_ERR_TOO_LARGE and launches nothing. The first call on each device resolves the array's address: issue it
+ * outside any stream capture. Calls share the array; calls whose GPU work overlaps in time race and must be
+ * serialised by the caller.
+ */
+int fdma_fwd_static_scratch(const fdma_fwd_params* p, void* stream);
+size_t fdma_static_scratch_limit(void);
+
+/*
  * Measurement hook (no counterpart in the reference, which is timed from Python with wall clocks,
  * benchmarks/forward_performance.py:388-399). The NEXT fdma_fwd or fdma_bwd call made by this host thread
  * records `start_event` immediately before and `stop_event` immediately after its main attention kernel
