@@ -451,15 +451,18 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
     uint16_t* dbias16 = reinterpret_cast<uint16_t*>(p.dbias);
     // Row-broadcast bias / mask that do not depend on the query head: one value per thread for the whole CTA.
     const bool hoist = kBcast && (G == 1 || ((!p.bias || p.h_bias != p.h) && (!p.mask || p.h_mask != p.h)));
-    float bv_h = 0.f;
-    bool kp_h = key_ok;
+    // mask / bias head of query head h, without integer division (extents are 1, h_k or h)
+    auto hm_of = [&](int h) { return p.h_mask == p.h ? h : (p.h_mask == p.h_k ? hk : 0); };
+    auto hb_of = [&](int h) { return p.h_bias == p.h ? h : (p.h_bias == p.h_k ? hk : 0); };
+    float bv_h = -CUDART_INF_F;  // bias*log2e of this key, or -inf when the key is masked out
     if (hoist) {
-      const int hq0 = hk * G;
-      const int hm0 = hq0 / (p.h / p.h_mask), hb0 = hq0 / (p.h / p.h_bias);
-      if (p.bias)
-        bv_h = raw16_to_float<kBf16>(reinterpret_cast<const uint16_t*>(p.bias)[b * p.bias_batch_stride +
-                                                                            hb0 * p.bias_head_stride + key]) * kLog2e;
-      if (p.mask && kp_h) kp_h = p.mask[b * p.mask_batch_stride + hm0 * p.mask_head_stride + key] != 0;
+      const int hm0 = hm_of(hk * G), hb0 = hb_of(hk * G);
+      bool kp = key_ok;
+      if (p.mask && kp) kp = p.mask[b * p.mask_batch_stride + hm0 * p.mask_head_stride + key] != 0;
+      if (kp)
+        bv_h = p.bias ? raw16_to_float<kBf16>(reinterpret_cast<const uint16_t*>(
+                            p.bias)[b * p.bias_batch_stride + hb0 * p.bias_head_stride + key]) * kLog2e
+                      : 0.f;
     }
     int i = 0;
     bool ok = true;
@@ -480,23 +483,25 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
           continue;
         }
         group_touched = true;
-        const int hm = h / (p.h / p.h_mask), hb = h / (p.h / p.h_bias);
-        // ---- bias / mask for this thread's key and 32 queries ----
+        // ---- bias (log2 units) for this thread's key and 32 queries; masked elements get -inf, which turns
+        //      into P = exp2(-inf) = 0 without any per-element select ----
         float bias2[32];
-        uint32_t keep = 0;  // bit j: element (q0 + j, key) is kept
         if (kBcast) {
           float bv = bv_h;
-          bool kp = kp_h;
           if (!hoist) {
-            if (p.bias)
-              bv = raw16_to_float<kBf16>(reinterpret_cast<const uint16_t*>(p.bias)[b * p.bias_batch_stride +
-                                                                                hb * p.bias_head_stride + key]) * kLog2e;
+            const int hm = hm_of(h), hb = hb_of(h);
+            bool kp = key_ok;
             if (p.mask && kp) kp = p.mask[b * p.mask_batch_stride + hm * p.mask_head_stride + key] != 0;
+            bv = -CUDART_INF_F;
+            if (kp)
+              bv = p.bias ? raw16_to_float<kBf16>(reinterpret_cast<const uint16_t*>(
+                                p.bias)[b * p.bias_batch_stride + hb * p.bias_head_stride + key]) * kLog2e
+                          : 0.f;
           }
 #pragma unroll
           for (int j = 0; j < 32; ++j) bias2[j] = bv;
-          keep = kp ? 0xFFFFFFFFu : 0u;
         } else {
+          const int hm = hm_of(h), hb = hb_of(h);
           const uint16_t* bcol = p.bias ? reinterpret_cast<const uint16_t*>(p.bias) + b * p.bias_batch_stride +
                                               hb * p.bias_head_stride + key
                                         : nullptr;
@@ -504,27 +509,27 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const int qq = min(q0 + j, Sq - 1);
-            bias2[j] = bcol ? raw16_to_float<kBf16>(bcol[static_cast<int64_t>(qq) * p.bias_row_stride]) * kLog2e : 0.f;
+            const float bj = bcol ? raw16_to_float<kBf16>(bcol[static_cast<int64_t>(qq) * p.bias_row_stride]) * kLog2e : 0.f;
             const bool kp = key_ok && (!mcol || mcol[static_cast<int64_t>(qq) * p.mask_row_stride] != 0);
-            keep |= (kp ? 1u : 0u) << j;
+            bias2[j] = kp ? bj : -CUDART_INF_F;
           }
         }
-        if (causal && key > q0 + off) {  // some of this thread's queries cannot see its key
+        // causal limit: only the tiles on the diagonal contain (query, key) pairs that fail it
+        if (causal && n * kBN + (warp & 3) * 32 + 31 > q0 + off) {
 #pragma unroll
           for (int j = 0; j < 32; ++j)
-            if (key > q0 + j + off) keep &= ~(1u << j);
+            if (key > q0 + j + off) bias2[j] = -CUDART_INF_F;
         }
         // LSE*log2e and D of the step's 64 queries arrive in shared memory with the Q/dO stage
         const float* lrow = s_ld + (i % kQStages) * (2 * kBM) + half * 32;
         const float* drow = lrow + kBM;
 
         // ---- P^T and dS^T in one pass: both accumulators are loaded together ----
-        // (the stage barrier has long completed when S arrives; waiting on it makes the bulk-copied LSE / D
-        // values visible to this thread)
+        // The stage barrier completed long ago (the MMA warp waited on it before issuing S); waiting on it here
+        // makes the bulk-copied LSE / D values visible to this thread. dP of step i is committed after S of
+        // step i was issued, so its barrier covers both accumulators.
         ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(0, mbar_wait(bar_qdo_full + (i % kQStages), (i / kQStages) & 1,
                                                                    ctl, kWaitQdoFull)));
-        if (!ok) break;
-        ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(1, mbar_wait(bar_s_full + (i & 1), (i >> 1) & 1, ctl, kWaitSFull)));
         if (!ok) break;
         ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(2, mbar_wait(bar_dp_full, i & 1, ctl, kWaitDpFull)));
         if (!ok) break;
@@ -546,8 +551,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const int j = j4 * 4 + e;
-              const float x = fmaf(__uint_as_float(rs[j]), p.scale_log2, bias2[j]) - lv[e];
-              const float pj = ((keep >> j) & 1u) ? fast_exp2(x) : 0.f;
+              const float pj = fast_exp2(fmaf(__uint_as_float(rs[j]), p.scale_log2, bias2[j] - lv[e]));
               const float ds = pj * (__uint_as_float(rp[j]) - dv4[e]);
               rs[j] = __float_as_uint(pj);
               pv[j] = ds;
