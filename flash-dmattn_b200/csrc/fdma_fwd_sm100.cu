@@ -405,28 +405,30 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
         ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(1, mbar_wait(bar_s_full + t, scnt & 1, ctl, kWaitS)));
         if (!ok) break;
         tc_fence_after_sync();
-        float s[kBN];
+        // Scores are kept as 64 register pairs so that the scale/bias FMA, the max-subtraction and the row sum run
+        // as packed fp32x2 instructions (half the issue slots of scalar code).
+        float2 s2[kBN / 2];
         {
           uint32_t su[kBN];
 #pragma unroll
           for (int c = 0; c < 4; ++c) tmem_ld_x32(s_taddr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&su[c * 32]));
           tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < kBN; ++i) s[i] = __uint_as_float(su[i]);
+          for (int i = 0; i < kBN / 2; ++i) s2[i] = make_float2(__uint_as_float(su[2 * i]), __uint_as_float(su[2 * i + 1]));
         }
         const int kbase = j * kBN;
+        const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
         // scores in log2 units with bias and mask folded in
         if (kBcast) {
           const float4* bm4 = reinterpret_cast<const float4*>(s_bm + slot * kBN);
 #pragma unroll
           for (int i = 0; i < kBN / 4; ++i) {
             const float4 a4 = bm4[i];
-            s[4 * i + 0] = fmaf(s[4 * i + 0], p.scale_log2, a4.x);
-            s[4 * i + 1] = fmaf(s[4 * i + 1], p.scale_log2, a4.y);
-            s[4 * i + 2] = fmaf(s[4 * i + 2], p.scale_log2, a4.z);
-            s[4 * i + 3] = fmaf(s[4 * i + 3], p.scale_log2, a4.w);
+            s2[2 * i] = __ffma2_rn(s2[2 * i], sc2, make_float2(a4.x, a4.y));
+            s2[2 * i + 1] = __ffma2_rn(s2[2 * i + 1], sc2, make_float2(a4.z, a4.w));
           }
         } else {
+          const float2 l2e2 = make_float2(kLog2e, kLog2e);
 #pragma unroll
           for (int c = 0; c < kBN / 16; ++c) {
             uint4 mb = make_uint4(0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u);
@@ -439,14 +441,19 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
             const uint32_t mw[4] = {mb.x, mb.y, mb.z, mb.w};
             const uint32_t bw[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const uint32_t raw = (i & 1) ? (bw[i >> 1] >> 16) : (bw[i >> 1] & 0xFFFFu);
-              float bf;
-              if (kBf16) bf = __uint_as_float(raw << 16);
-              else bf = __half2float(__ushort_as_half(static_cast<uint16_t>(raw)));
-              const bool keep = ((mw[i >> 2] >> ((i & 3) * 8)) & 0xFFu) != 0;
-              const float v = fmaf(s[c * 16 + i], p.scale_log2, bf * kLog2e);
-              s[c * 16 + i] = keep ? v : -CUDART_INF_F;
+            for (int i = 0; i < 8; ++i) {  // pair i of this 16-key chunk
+              float2 bf;
+              if (kBf16) {
+                bf = make_float2(__uint_as_float(bw[i] << 16), __uint_as_float(bw[i] & 0xFFFF0000u));
+              } else {
+                const __half2 hh = *reinterpret_cast<const __half2*>(&bw[i]);
+                bf = make_float2(__low2float(hh), __high2float(hh));
+              }
+              float2 add = __fmul2_rn(bf, l2e2);
+              const uint32_t mpair = mw[i >> 1] >> ((i & 1) * 16);
+              if ((mpair & 0xFFu) == 0) add.x = -CUDART_INF_F;
+              if ((mpair & 0xFF00u) == 0) add.y = -CUDART_INF_F;
+              s2[c * 8 + i] = __ffma2_rn(s2[c * 8 + i], sc2, add);
             }
           }
         }
@@ -459,19 +466,21 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
           if (causal) wlim = min(wlim, warp_q0 + off + 1);
           if (kbase + kBN > wlim) {
 #pragma unroll
-            for (int i = 0; i < kBN; ++i)
-              if (kbase + i >= klim) s[i] = -CUDART_INF_F;
+            for (int i = 0; i < kBN / 2; ++i) {
+              if (kbase + 2 * i >= klim) s2[i].x = -CUDART_INF_F;
+              if (kbase + 2 * i + 1 >= klim) s2[i].y = -CUDART_INF_F;
+            }
           }
         }
         float m_tile;
-        {  // four independent chains instead of one 128-long dependent chain
+        {  // four independent chains of three-input max
           float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
-          for (int i = 0; i < kBN; i += 4) {
-            mx[0] = fmaxf(mx[0], s[i]);
-            mx[1] = fmaxf(mx[1], s[i + 1]);
-            mx[2] = fmaxf(mx[2], s[i + 2]);
-            mx[3] = fmaxf(mx[3], s[i + 3]);
+          for (int i = 0; i < kBN / 2; i += 4) {
+            mx[0] = fmax3(mx[0], s2[i].x, s2[i].y);
+            mx[1] = fmax3(mx[1], s2[i + 1].x, s2[i + 1].y);
+            mx[2] = fmax3(mx[2], s2[i + 2].x, s2[i + 2].y);
+            mx[3] = fmax3(mx[3], s2[i + 3].x, s2[i + 3].y);
           }
           m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
         }
@@ -495,20 +504,25 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
           m_ref = m_new;
         }
         const float m_use = (m_ref == -CUDART_INF_F) ? 0.f : m_ref;
-        float ls[4] = {0.f, 0.f, 0.f, 0.f};
+        float2 ls[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+        const float2 nm2 = make_float2(-m_use, -m_use);
 #pragma unroll
         for (int c = 0; c < kBN / 32; ++c) {
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            const float p0 = fast_exp2(s[c * 32 + 2 * i] - m_use);
-            const float p1 = fast_exp2(s[c * 32 + 2 * i + 1] - m_use);
-            ls[i & 3] += p0 + p1;
-            pk[i] = pack_16x2<kBf16>(p0, p1);
+            const float2 x = __fadd2_rn(s2[c * 16 + i], nm2);
+            const float2 pp = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+            ls[i & 3] = __fadd2_rn(ls[i & 3], pp);
+            pk[i] = pack_16x2<kBf16>(pp.x, pp.y);
           }
           tmem_st_x16(s_taddr + c * 16, pk);
         }
-        l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+        {
+          const float2 t01 = __fadd2_rn(ls[0], ls[1]), t23 = __fadd2_rn(ls[2], ls[3]);
+          const float2 tt = __fadd2_rn(t01, t23);
+          l += tt.x + tt.y;
+        }
         tmem_wait_st();
         tc_fence_before_sync();
         mbar_arrive(bar_p_full + t);
