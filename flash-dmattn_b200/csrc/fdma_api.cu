@@ -147,7 +147,8 @@ const char* fdma_strerror(int status) {
 size_t fdma_fwd_workspace_bytes(const fdma_fwd_params* pp) {
   if (!pp || validate_fwd(*pp)) return 0;
   const fdma_fwd_params p = normalise(*pp);
-  if (p.path != FDMA_PATH_SIMT && tc_fwd_supported(p)) return tc_fwd_workspace_bytes(p);
+  if ((p.path == FDMA_PATH_AUTO || p.path == FDMA_PATH_DECODE) && decode_supported(p)) return decode_workspace_bytes(p);
+  if (p.path != FDMA_PATH_SIMT && p.path != FDMA_PATH_DECODE && tc_fwd_supported(p)) return tc_fwd_workspace_bytes(p);
   return 0;
 }
 
@@ -159,6 +160,10 @@ int fdma_fwd(const fdma_fwd_params* pp, void* stream_) {
   if (st) return st;
   const fdma_fwd_params p = normalise(*pp);
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (p.path == FDMA_PATH_AUTO || p.path == FDMA_PATH_DECODE) {
+    if (decode_supported(p)) return decode_fwd(p, stream);
+    if (p.path == FDMA_PATH_DECODE) return FDMA_ERR_UNSUPPORTED;
+  }
   const bool tc_ok = tc_fwd_supported(p);
   if (p.path == FDMA_PATH_TCGEN05 && !tc_ok) return FDMA_ERR_UNSUPPORTED;
   if (p.path != FDMA_PATH_SIMT && tc_ok) return tc_fwd(p, stream);

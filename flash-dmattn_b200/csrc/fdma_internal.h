@@ -29,6 +29,11 @@ bool tc_bwd_supported(const fdma_bwd_params& p);
 size_t tc_bwd_workspace_bytes(const fdma_bwd_params& p);
 int tc_bwd(const fdma_bwd_params& p, cudaStream_t stream);
 
+// ---- single-query (decode) forward: row-granular skipping, split over keys + merge -------------
+bool decode_supported(const fdma_fwd_params& p);
+size_t decode_workspace_bytes(const fdma_fwd_params& p);
+int decode_fwd(const fdma_fwd_params& p, cudaStream_t stream);
+
 // ---- create_mask -------------------------------------------------------------------------------
 int create_mask(const fdma_mask_params& p, cudaStream_t stream);
 

@@ -11,7 +11,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("FDMA_LIB", os.path.join(_HERE, "lib", "libfdma_sm100.so"))
 
 FDMA_BF16, FDMA_FP16, FDMA_FP32 = 0, 1, 2
-PATH_AUTO, PATH_SIMT, PATH_TCGEN05 = 0, 1, 2
+PATH_AUTO, PATH_SIMT, PATH_TCGEN05, PATH_DECODE = 0, 1, 2, 3
 MASK_TOPK, MASK_RELU = 0, 1
 
 

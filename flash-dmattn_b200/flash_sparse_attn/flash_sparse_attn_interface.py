@@ -20,9 +20,10 @@ _kernel_path = _lib.PATH_AUTO
 
 
 def set_kernel_path(path: str) -> None:
-    """Selects the kernel family: "auto" (default), "simt" (CUDA-core kernels) or "tcgen05". Used by tests."""
+    """Selects the kernel family: "auto" (default), "simt" (CUDA-core kernels), "tcgen05" or "decode". Used by tests."""
     global _kernel_path
-    _kernel_path = {"auto": _lib.PATH_AUTO, "simt": _lib.PATH_SIMT, "tcgen05": _lib.PATH_TCGEN05}[path]
+    _kernel_path = {"auto": _lib.PATH_AUTO, "simt": _lib.PATH_SIMT, "tcgen05": _lib.PATH_TCGEN05,
+                    "decode": _lib.PATH_DECODE}[path]
 
 
 def round_multiple(x: int, m: int) -> int:

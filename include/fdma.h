@@ -42,10 +42,11 @@ enum fdma_status {
   FDMA_ERR_TOO_LARGE = -7      /* static-scratch variant: problem exceeds the compiled-in limit  */
 };
 
-/* Which kernel family the launcher picks. AUTO: tcgen05/TMA kernels where shape and alignment
- * allow, the CUDA-core kernels otherwise. The other two values force one family (tests use them);
- * forcing TCGEN05 on an unsupported shape returns FDMA_ERR_UNSUPPORTED. */
-enum fdma_path { FDMA_PATH_AUTO = 0, FDMA_PATH_SIMT = 1, FDMA_PATH_TCGEN05 = 2 };
+/* Which kernel family the launcher picks. AUTO: the row-gather decode kernel for single-query calls
+ * (seqlen_q == 1, head dim 64/128/256), tcgen05/TMA kernels where shape and alignment allow, the
+ * CUDA-core kernels otherwise. The other values force one family (tests use them); forcing a family
+ * on a shape it does not handle returns FDMA_ERR_UNSUPPORTED. */
+enum fdma_path { FDMA_PATH_AUTO = 0, FDMA_PATH_SIMT = 1, FDMA_PATH_TCGEN05 = 2, FDMA_PATH_DECODE = 3 };
 
 /*
  * Forward: O = softmax(scale * Q K^T + bias, masked) V, LSE = logsumexp of the masked scores.

@@ -196,6 +196,37 @@ def test_tcgen05_backward_fp16_and_run_to_run_spread(dev, kernel_path):
     assert torch.equal(a[2], b[2]) and torch.equal(a[3], b[3])  # dK, dV have a fixed accumulation order
 
 
+DECODE_CASES = [
+    ((1, 1, 700, 8, 2, 128), "bcast", "topk", 100, "decode"),     # GQA group of 4 shares K/V rows
+    ((2, 1, 5000, 4, 4, 64), "b1h1", "block", 300, "decode"),     # MHA, fully broadcast bias, long runs of skipped keys
+    ((3, 1, 4096, 6, 2, 128), "perhead", "randqh", 0, "decode"),  # per-head mask/bias: one head per CTA
+    ((1, 1, 333, 16, 2, 256), "bcast", "none", 0, "auto"),        # group of 8 at d=256: falls back to other kernels
+    ((2, 1, 9000, 8, 1, 256), "bcast", "topk", 64, "auto"),       # MQA, d=256, group of 8 -> fallback, very sparse
+    ((2, 1, 2048, 8, 4, 256), "bcast", "topk", 700, "decode"),    # d=256, group of 2
+    ((1, 1, 40, 2, 2, 128), "none", "none", 0, "decode"),         # shorter than one chunk per warp
+]
+
+
+@pytest.mark.parametrize("geom,bias_kind,mask_kind,window,path", DECODE_CASES)
+def test_decode_forward_backward(dev, kernel_path, geom, bias_kind, mask_kind, window, path):
+    kernel_path(path)
+    case = build_case(dev, *geom, bias_kind, mask_kind, window, torch.bfloat16)
+    compare_all(case, False, torch.bfloat16)
+
+
+def test_decode_all_keys_masked_and_fp16(dev, kernel_path):
+    from flash_sparse_attn import flash_sparse_attn_func
+
+    kernel_path("decode")
+    q, k, v, mask, bias, dout = build_case(dev, 2, 1, 512, 4, 2, 128, "bcast", "topk", 50, torch.float16)
+    mask = mask.clone()
+    mask[1] = False  # batch element 1 sees nothing: output 0
+    out = flash_sparse_attn_func(q, k, v, attn_mask=mask, attn_bias=bias)
+    ref, _ = oracle.attention_forward(q, k, v, mask, bias, None, False)
+    check("out", out, ref, torch.float16)
+    assert (out[1] == 0).all()
+
+
 def test_tcgen05_forward_fp16(dev, kernel_path):
     kernel_path("tcgen05")
     case = build_case(dev, 1, 256, 256, 2, 1, 128, "bcast", "topk", 100, torch.float16)
