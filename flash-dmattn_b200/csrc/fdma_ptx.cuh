@@ -1,6 +1,6 @@
 // Thin inline-PTX wrappers for the sm_100a features the kernels use: mbarrier, TMA tiled copies,
 // tcgen05 (TMEM allocation, UMMA issue, commit, TMEM load/store) and the shared-memory / instruction
-// descriptors that tcgen05.mma consumes. Everything is cta_group::1 and there is no multicast anywhere.
+// descriptors that tcgen05.mma consumes. Everything is cta_group::1; every TMA copy targets the issuing CTA only.
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
@@ -130,7 +130,7 @@ __device__ __forceinline__ void tc_fence_after_sync() {
 }
 
 // ---------------------------------------------------------------------------------------------
-// TMA (tiled, no multicast). The destination is this CTA's shared memory; completion is signalled as
+// TMA (tiled, single-CTA). The destination is this CTA's shared memory; completion is signalled as
 // transaction bytes on an mbarrier of the same CTA.
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
