@@ -483,11 +483,14 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
           continue;
         }
         group_touched = true;
-        // ---- bias (log2 units) for this thread's key and 32 queries; masked elements get -inf, which turns
-        //      into P = exp2(-inf) = 0 without any per-element select ----
-        float bias2[32];
+        // ---- bias (log2 units) for this thread's key; masked elements get -inf, which turns into
+        //      P = exp2(-inf) = 0 without any per-element select. Row-broadcast bias: one scalar per thread; the
+        //      per-element array is only filled for per-query bias/mask and on tiles that cross the causal limit ----
+        const bool diag = causal && n * kBN + (warp & 3) * 32 + 31 > q0 + off;  // warp-uniform
+        const bool per_elem = !kBcast || diag;
+        float bv = bv_h;
+        float2 bias2[16];
         if (kBcast) {
-          float bv = bv_h;
           if (!hoist) {
             const int hm = hm_of(h), hb = hb_of(h);
             bool kp = key_ok;
@@ -498,8 +501,12 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
                                 p.bias)[b * p.bias_batch_stride + hb * p.bias_head_stride + key]) * kLog2e
                           : 0.f;
           }
+          if (diag) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) bias2[j] = bv;
+            for (int j = 0; j < 16; ++j)
+              bias2[j] = make_float2(key > q0 + 2 * j + off ? -CUDART_INF_F : bv,
+                                     key > q0 + 2 * j + 1 + off ? -CUDART_INF_F : bv);
+          }
         } else {
           const int hm = hm_of(h), hb = hb_of(h);
           const uint16_t* bcol = p.bias ? reinterpret_cast<const uint16_t*>(p.bias) + b * p.bias_batch_stride +
@@ -507,18 +514,24 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
                                         : nullptr;
           const uint8_t* mcol = p.mask ? p.mask + b * p.mask_batch_stride + hm * p.mask_head_stride + key : nullptr;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int qq = min(q0 + j, Sq - 1);
-            const float bj = bcol ? raw16_to_float<kBf16>(bcol[static_cast<int64_t>(qq) * p.bias_row_stride]) * kLog2e : 0.f;
-            const bool kp = key_ok && (!mcol || mcol[static_cast<int64_t>(qq) * p.mask_row_stride] != 0);
-            bias2[j] = kp ? bj : -CUDART_INF_F;
-          }
-        }
-        // causal limit: only the tiles on the diagonal contain (query, key) pairs that fail it
-        if (causal && n * kBN + (warp & 3) * 32 + 31 > q0 + off) {
+          for (int j = 0; j < 16; ++j) {
+            float two[2];
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (key > q0 + j + off) bias2[j] = -CUDART_INF_F;
+            for (int e = 0; e < 2; ++e) {
+              const int qq = min(q0 + 2 * j + e, Sq - 1);
+              const float bj = bcol ? raw16_to_float<kBf16>(bcol[static_cast<int64_t>(qq) * p.bias_row_stride]) * kLog2e : 0.f;
+              const bool kp = key_ok && (!mcol || mcol[static_cast<int64_t>(qq) * p.mask_row_stride] != 0);
+              two[e] = kp ? bj : -CUDART_INF_F;
+            }
+            bias2[j] = make_float2(two[0], two[1]);
+          }
+          if (diag) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              if (key > q0 + 2 * j + off) bias2[j].x = -CUDART_INF_F;
+              if (key > q0 + 2 * j + 1 + off) bias2[j].y = -CUDART_INF_F;
+            }
+          }
         }
         // LSE*log2e and D of the step's 64 queries arrive in shared memory with the Q/dO stage
         const float* lrow = s_ld + (i % kQStages) * (2 * kBM) + half * 32;
@@ -540,24 +553,41 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
           tmem_ld_x32(tmem_base + lane_addr + kColSt + (i & 1) * kBM + half * 32, rs);
           tmem_ld_x32(tmem_base + lane_addr + kColDp + half * 32, rp);
           tmem_wait_ld();
-          float pv[32];
-          float part[4] = {0.f, 0.f, 0.f, 0.f};
+          // packed fp32x2 arithmetic: two queries per instruction
+          float2 pp[16], dd[16];
+          float2 part[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+          const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
+          const float2 bv2 = make_float2(bv, bv);
+          const float2 neg1 = make_float2(-1.f, -1.f);
 #pragma unroll
           for (int j4 = 0; j4 < 8; ++j4) {
             const float4 l4 = reinterpret_cast<const float4*>(lrow)[j4];
             const float4 d4 = reinterpret_cast<const float4*>(drow)[j4];
-            const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
-            const float dv4[4] = {d4.x, d4.y, d4.z, d4.w};
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int j = j4 * 4 + e;
-              const float pj = fast_exp2(fmaf(__uint_as_float(rs[j]), p.scale_log2, bias2[j] - lv[e]));
-              const float ds = pj * (__uint_as_float(rp[j]) - dv4[e]);
-              rs[j] = __float_as_uint(pj);
-              pv[j] = ds;
-              part[e] += ds;
+            for (int e = 0; e < 2; ++e) {
+              const int j = j4 * 2 + e;  // pair index
+              const float2 lv = e == 0 ? make_float2(l4.x, l4.y) : make_float2(l4.z, l4.w);
+              const float2 dv = e == 0 ? make_float2(d4.x, d4.y) : make_float2(d4.z, d4.w);
+              const float2 addend = __ffma2_rn(lv, neg1, per_elem ? bias2[j] : bv2);       // bias - LSE
+              const float2 x = __ffma2_rn(make_float2(__uint_as_float(rs[2 * j]), __uint_as_float(rs[2 * j + 1])), sc2,
+                                          addend);
+              const float2 pj = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+              const float2 dpd = __ffma2_rn(dv, neg1, make_float2(__uint_as_float(rp[2 * j]), __uint_as_float(rp[2 * j + 1])));
+              const float2 ds = __fmul2_rn(pj, dpd);
+              pp[j] = pj;
+              dd[j] = ds;
+              part[e] = __fadd2_rn(part[e], ds);
             }
           }
+          float pv[32];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            rs[2 * j] = __float_as_uint(pp[j].x);
+            rs[2 * j + 1] = __float_as_uint(pp[j].y);
+            pv[2 * j] = dd[j].x;
+            pv[2 * j + 1] = dd[j].y;
+          }
+          const float step_sum_packed = (part[0].x + part[0].y) + (part[1].x + part[1].y);
           uint32_t pk[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
@@ -566,7 +596,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
           }
           tmem_st_x16(tmem_base + lane_addr + kColSt + (i & 1) * kBM + half * 32, pk);
           tmem_st_x16(tmem_base + lane_addr + kColDp + half * 32, dsk);
-          const float step_sum = (part[0] + part[1]) + (part[2] + part[3]);
+          const float step_sum = step_sum_packed;
           if (mode == kDbColsum) {
             colsum += step_sum;
           } else if (mode == kDbDirect) {
