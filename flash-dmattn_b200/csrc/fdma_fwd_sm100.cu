@@ -72,7 +72,7 @@ struct Smem {
   static constexpr int kBmOff = kKvOff + kStages * kKvBytes;
   static constexpr int kFlagsOff = kBmOff + kBmSlots * kBN * 4;
   static constexpr int kBarOff = kFlagsOff + kMaxTiles;
-  static constexpr int kNumBars = 1 + 2 * kStages + 2 + 2 + 1 + 2 * kBmSlots;
+  static constexpr int kNumBars = 1 + 2 * kStages + 2 + 2 + 1 + 2 * kBmSlots + 1;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kTotal = kMiscOff + 16;
   static constexpr int kAlloc = kTotal + 1024;  // slack to align the base to 1024 B
@@ -135,6 +135,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
   uint64_t* bar_o_done = bar_p_full + 2;
   uint64_t* bar_bm_full = bar_o_done + 1;
   uint64_t* bar_bm_empty = bar_bm_full + kBmSlots;
+  uint64_t* bar_stagger = bar_bm_empty + kBmSlots;  // warpgroup 0 -> warpgroup 1, once
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + L::kMiscOff);
   volatile int* s_abort = reinterpret_cast<volatile int*>(smem + L::kMiscOff + 4);
 
@@ -174,6 +175,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
       mbar_init(bar_p_full + t, kBM);
     }
     mbar_init(bar_o_done, 1);
+    mbar_init(bar_stagger, kBM);
     for (int i = 0; i < kBmSlots; ++i) {
       mbar_init(bar_bm_full + i, 1);
       mbar_init(bar_bm_empty + i, 8);  // one arrival per softmax warp
@@ -393,6 +395,11 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
     uint32_t scnt = 0;
     int bi = 0;
     bool ok = true;
+    // The two warpgroups share the transcendental unit; running their exp2 phases at the same time doubles the
+    // length of both. Warpgroup 1 therefore starts only when warpgroup 0 reaches the exp2 phase of its first
+    // tile, which keeps the two loops roughly half a period apart.
+    bool stagger_sent = false;
+    if (t == 1) ok = __all_sync(0xffffffffu, mbar_wait(bar_stagger, 0, ctl, kWaitS));
     for (int j = 0; j < nT && ok; ++j) {
       const uint8_t fl = s_flags[j];
       if (fl == 0) continue;
@@ -503,6 +510,10 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
           l *= alpha;
           m_ref = m_new;
         }
+        if (t == 0 && !stagger_sent) {
+          mbar_arrive(bar_stagger);
+          stagger_sent = true;
+        }
         const float m_use = (m_ref == -CUDART_INF_F) ? 0.f : m_ref;
         float2 ls[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
         const float2 nm2 = make_float2(-m_use, -m_use);
@@ -534,6 +545,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
       }
       ++bi;
     }
+    if (t == 0 && !stagger_sent) mbar_arrive(bar_stagger);  // no tile processed: release warpgroup 1 anyway
     // ---------------- epilogue ----------------
     if (ok && nT > 0) ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(2, mbar_wait(bar_o_done, 0, ctl, kWaitO)));
     FDMA_PROF_END(16, tid == 128);
