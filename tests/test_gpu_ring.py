@@ -1,0 +1,57 @@
+"""KV-ring context parallelism on real GPUs (needs at least two): NCCL ranks as child processes, tcgen05 kernels
+underneath, compared with the fp32 oracle on the full sequence."""
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, causal):
+    import torch.distributed as dist
+
+    from flash_sparse_attn import ring
+    from oracle import oracle
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dev = torch.device(f"cuda:{rank}")
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        B, H, Hk, d = 1, 4, 1, 128
+        S = 2 * world * 256
+        q, k, v, bias, dout = oracle.make_inputs(B, S, S, H, Hk, d, (B, Hk, 1, S), seed=5, dtype=torch.bfloat16)
+        mask = oracle.create_mask(bias, None, B, S, S, S // 4, torch.finfo(torch.bfloat16).min)
+        want = oracle.attention_forward_backward(q, k, v, mask, bias, dout, None, causal)
+        loc = lambda t, dim: ring.zigzag_split(t, dim, rank, world).contiguous().to(dev)
+        ql, kl, vl = (loc(t, 1).requires_grad_(True) for t in (q, k, v))
+        bl = loc(bias, 3).requires_grad_(True)
+        out = ring.ring_flash_sparse_attn_func(ql, kl, vl, loc(mask, 3), bl, None, causal)
+        out.backward(loc(dout, 1))
+
+        def gather(t, dim):
+            parts = [torch.empty_like(t) for _ in range(world)]
+            dist.all_gather(parts, t.contiguous())
+            return ring.zigzag_merge(parts, dim).float().cpu()
+
+        for name, got, ref, dim in (("out", out, want[0], 1), ("dq", ql.grad, want[2], 1), ("dk", kl.grad, want[3], 1),
+                                    ("dv", vl.grad, want[4], 1), ("dbias", bl.grad, want[5], 3)):
+            r = oracle.error_report(name, gather(got, dim), ref)
+            assert r["max_abs"] <= 2e-2 + 3 * r["floor_max_abs"] and r["mean_abs"] <= 2e-3 + 2 * r["floor_mean_abs"], r
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_ring_two_gpus(causal):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_worker, args=(2, port, causal), nprocs=2, join=True)
