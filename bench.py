@@ -362,6 +362,59 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     print(json.dumps(line), flush=True)
 
 
+def run_ring(args, rank: int, world: int, local_rank: int):
+    """Secondary workload (not the headline line): one long sequence, KV-ring context parallel over all ranks.
+    BASELINE config-5 geometry with head dim 128 instead of 256 (the tcgen05 kernels cover 64 and 128):
+    B=1, S=131072, Hq=16, Hkv=1, top-1024 query-broadcast mask, causal, fwd+bwd with dBias."""
+    import torch.distributed as dist
+
+    from flash_sparse_attn import ring
+    from flash_sparse_attn.utils.mask import create_mask
+
+    dev = torch.device(f"cuda:{local_rank}")
+    torch.cuda.set_device(dev)
+    B, Sr, H, Hk, d, w = 1, args.ring_seq_len, 16, 1, 128, 1024
+    g = torch.Generator(device="cpu").manual_seed(7)
+    bias_full = torch.randn((B, Hk, 1, Sr), generator=g).to(torch.bfloat16)
+    mask_full = create_mask(bias_full.to(dev), None, B, Sr, Sr, w, torch.finfo(torch.bfloat16).min).cpu()
+    gl = torch.Generator(device=dev).manual_seed(100 + rank)
+    S2 = Sr // world
+    rnd = lambda *shape: torch.randn(shape, generator=gl, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    q, k, v, dout = rnd(B, S2, H, d), rnd(B, S2, Hk, d), rnd(B, S2, Hk, d), rnd(B, S2, H, d)
+    q.requires_grad_(True); k.requires_grad_(True); v.requires_grad_(True)
+    bias = ring.zigzag_split(bias_full, 3, rank, world).contiguous().to(dev).requires_grad_(True)
+    mask = ring.zigzag_split(mask_full, 3, rank, world).contiguous().to(dev)
+
+    def step():
+        out = ring.ring_flash_sparse_attn_func(q, k, v, mask, bias, None, True)
+        out.backward(dout)
+        q.grad = k.grad = v.grad = bias.grad = None
+
+    for _ in range(args.warmup):
+        step()
+    dist.barrier(); torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    dist.barrier(); torch.cuda.synchronize(dev)
+    ms = torch.tensor([e0.elapsed_time(e1) / args.steps], dtype=torch.float64, device=dev)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    if rank != 0:
+        return
+    fl = count_flops(mask_full, B, Sr, Sr, H, Hk, d, True)
+    line = {
+        "metric": "fwd+bwd TFLOP/s on kept blocks (KV-ring context parallel)", "value": fl["canonical_128x128"] / (ms.item() * 1e-3) / 1e12,
+        "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms.item(),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"ring: B=1 S={Sr} Hq=16 Hkv=1 d=128 W=1024 causal, bias (1,1,1,S)",
+                   "parallelism": f"KV ring over {world} ranks, zig-zag chunks of {Sr // (2 * world)} tokens",
+                   "flops": "kept 128x128 tiles of the global mask"},
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -373,6 +426,9 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     ap.add_argument("--seq-len", type=int, default=S, help="profiling only: shorter sequence")
     ap.add_argument("--window", type=int, default=WINDOW, help="profiling only: window for --seq-len")
+    ap.add_argument("--workload", default="sharded", choices=["sharded", "ring"],
+                    help="sharded = the headline benchmark; ring = single long sequence over a KV ring (needs >= 2 ranks)")
+    ap.add_argument("--ring-seq-len", type=int, default=131072)
     args = ap.parse_args()
     if args.impl == "ours":
         args.warmup = max(args.warmup, 3)
@@ -390,7 +446,10 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
     try:
-        run_ours(args, rank, world, local_rank)
+        if args.workload == "ring":
+            run_ring(args, rank, world, local_rank)
+        else:
+            run_ours(args, rank, world, local_rank)
     finally:
         if world > 1:
             import torch.distributed as dist
