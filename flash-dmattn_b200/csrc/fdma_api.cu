@@ -51,6 +51,7 @@ int validate_fwd(const fdma_fwd_params& p) {
   if (p.dtype != FDMA_BF16 && p.dtype != FDMA_FP16) return FDMA_ERR_UNSUPPORTED;
   if (p.mask && !(p.h_mask == 1 || p.h_mask == p.h_k || p.h_mask == p.h)) return FDMA_ERR_BAD_ARG;
   if (p.bias && !(p.h_bias == 1 || p.h_bias == p.h_k || p.h_bias == p.h)) return FDMA_ERR_BAD_ARG;
+  if (p.key_pos && !(p.h_pos == 1 || p.h_pos == p.h_k || p.h_pos == p.h)) return FDMA_ERR_BAD_ARG;
   return 0;
 }
 
@@ -75,6 +76,10 @@ fdma_fwd_params normalise(const fdma_fwd_params& in) {
   if (!p.mask) p.h_mask = 1;
   if (!p.bias) p.h_bias = 1;
   if (p.seqlen_q == 1) p.is_causal = 0;
+  if (!p.key_pos || !p.is_causal) {
+    p.key_pos = nullptr;
+    p.h_pos = 1;
+  }
   return p;
 }
 

@@ -22,6 +22,7 @@
 #include <math_constants.h>
 
 #include <algorithm>
+#include <cstdlib>
 
 #include "fdma_internal.h"
 #include "fdma_ptx.cuh"
@@ -55,6 +56,9 @@ struct BwdKernelParams {
   void* dv;
   void* dbias;         // direct / column-sum modes: the output tensor
   float* dbias_acc;    // atomic mode: fp32 buffer (dbias_b, dbias_h, dbias_rows, dbias_keys), zeroed
+  float* dkv_part;     // nsplit > 1: fp32 partials [2: dV, dK][nsplit][B][h_k][NT*128][128]
+  float* dbias_part;   // nsplit > 1, column-sum mode: fp32 partials [nsplit][B][h_k][NT*128]
+  int nsplit;          // query-range splits per key tile
   const uint8_t* act;  // per-query mask: activity bytes [B][h_mask][ceil(Sq/128)][ceil(Sk/128)], else null
   int* status;
   int64_t mask_batch_stride, mask_head_stride, mask_row_stride;
@@ -65,6 +69,9 @@ struct BwdKernelParams {
   int b, seqlen_q, seqlen_k, sq_r, h, h_k, h_mask, h_bias;
   int dbias_b, dbias_h, dbias_rows, dbias_keys, dbias_mode;
   int is_causal;
+  const int32_t* key_pos;  // ascending positions of compacted keys, or null
+  int64_t pos_batch_stride, pos_head_stride;
+  int h_pos, causal_shift;
   float scale_log2, scale;
 };
 
@@ -216,18 +223,36 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
   int* s_nsteps = reinterpret_cast<int*>(smem + L::kMiscOff + 8);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int n = blockIdx.x;  // key tile
   const int hk = blockIdx.y, b = blockIdx.z;
   const int G = p.h / p.h_k;
   const int Sq = p.seqlen_q, Sk = p.seqlen_k;
   const int off = Sk - Sq;
-  const int M64 = (Sq + kBM - 1) / kBM;
   const int MT = (Sq + 127) / 128;
   const int NT = (Sk + kBN - 1) / kBN;
+  // blockIdx.x = (query-range split, key tile). With more than one split a CTA covers the 64-row query tiles
+  // [m_lo, M64) of its key tile and leaves fp32 partial dK / dV / column sums for a reduction kernel. The last
+  // query ranges, which causal masking never empties, are scheduled first.
+  const int n = blockIdx.x % NT;  // key tile
+  const int split = p.nsplit - 1 - blockIdx.x / NT;
+  const int M64_all = (Sq + kBM - 1) / kBM;
+  const int m_chunk = (M64_all + p.nsplit - 1) / p.nsplit;
+  const int m_lo = split * m_chunk;
+  const int M64 = min(M64_all, m_lo + m_chunk);  // end of this CTA's query range
   const bool causal = p.is_causal != 0;
   const int act_g = (p.h_mask == p.h && G > 1) ? G : 1;  // activity differs per query head only for per-head masks
+  // Compacted keys carry their original positions (ascending); the causal test then runs on positions.
+  const int32_t* pos_row = nullptr;
+  if (causal && p.key_pos)
+    pos_row = p.key_pos + b * p.pos_batch_stride + (p.h_pos == p.h_k ? hk : 0) * p.pos_head_stride;
+  const int coff = pos_row ? p.causal_shift : off;
   int m_start = 0;
-  if (causal) m_start = max(0, (n * kBN - off) / kBM);    // first query tile with a row that sees key n*128
+  if (pos_row) {
+    const int64_t first = (static_cast<int64_t>(pos_row[n * kBN]) - coff) / kBM;
+    m_start = static_cast<int>(max(static_cast<int64_t>(0), min(first, static_cast<int64_t>(M64))));
+  } else if (causal) {
+    m_start = max(0, (n * kBN - off) / kBM);  // first query tile with a row that sees key n*128
+  }
+  m_start = max(m_start, m_lo);
   const WaitCtl ctl{s_abort, p.status};
 
   // ---------------- set-up ----------------
@@ -442,6 +467,10 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
     const int key = n * kBN + krow;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const bool key_ok = key < Sk;
+    // value compared with q + coff in the causal test: the key's position
+    // (clamped so that ckey - coff cannot overflow; padding slots hold INT_MAX and are masked out anyway)
+    const int ckey = pos_row ? (key_ok ? min(pos_row[key], 0x3FFFFFFF) : 0x3FFFFFFF) : key;
+    const int ckey_wmax = pos_row ? __shfl_sync(0xffffffffu, ckey, 31) : n * kBN + (warp & 3) * 32 + 31;
     const int mode = p.dbias_mode;
     float colsum = 0.f;       // column-sum mode
     float dacc[32];           // direct mode with dbias_h == h_k: sum over the head group
@@ -467,7 +496,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
     int i = 0;
     bool ok = true;
     FDMA_PROF_BEGIN();
-    const int m_first = (mode == kDbDirect) ? 0 : m_start;  // direct mode also zero-fills tiles it skips
+    const int m_first = (mode == kDbDirect) ? m_lo : m_start;  // direct mode also zero-fills tiles it skips
     for (int m = m_first; m < M64 && ok; ++m) {
       const int q0 = m * kBM + half * 32;
       bool group_touched = false;
@@ -486,7 +515,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         // ---- bias (log2 units) for this thread's key; masked elements get -inf, which turns into
         //      P = exp2(-inf) = 0 without any per-element select. Row-broadcast bias: one scalar per thread; the
         //      per-element array is only filled for per-query bias/mask and on tiles that cross the causal limit ----
-        const bool diag = causal && n * kBN + (warp & 3) * 32 + 31 > q0 + off;  // warp-uniform
+        const bool diag = causal && static_cast<int64_t>(ckey_wmax) > static_cast<int64_t>(q0) + coff;  // warp-uniform
         const bool per_elem = !kBcast || diag;
         float bv = bv_h;
         float2 bias2[16];
@@ -504,8 +533,8 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
           if (diag) {
 #pragma unroll
             for (int j = 0; j < 16; ++j)
-              bias2[j] = make_float2(key > q0 + 2 * j + off ? -CUDART_INF_F : bv,
-                                     key > q0 + 2 * j + 1 + off ? -CUDART_INF_F : bv);
+              bias2[j] = make_float2(ckey - coff > q0 + 2 * j ? -CUDART_INF_F : bv,
+                                     ckey - coff > q0 + 2 * j + 1 ? -CUDART_INF_F : bv);
           }
         } else {
           const int hm = hm_of(h), hb = hb_of(h);
@@ -528,8 +557,8 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
           if (diag) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-              if (key > q0 + 2 * j + off) bias2[j].x = -CUDART_INF_F;
-              if (key > q0 + 2 * j + 1 + off) bias2[j].y = -CUDART_INF_F;
+              if (ckey - coff > q0 + 2 * j) bias2[j].x = -CUDART_INF_F;
+              if (ckey - coff > q0 + 2 * j + 1) bias2[j].y = -CUDART_INF_F;
             }
           }
         }
@@ -658,7 +687,10 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
       if (half == 0 && key < p.dbias_keys) {
         // dbias_h == h_k: this CTA saw every query head of the group. dbias_h == h with a group of one: same.
         const float tot = colsum + s_red[krow];
-        dbias16[b * p.dbias_batch_stride + hk * p.dbias_head_stride + key] = float_to_raw16<kBf16>(key_ok ? tot : 0.f);
+        if (p.nsplit > 1)
+          p.dbias_part[((static_cast<int64_t>(split) * p.b + b) * p.h_k + hk) * (NT * kBN) + key] = key_ok ? tot : 0.f;
+        else
+          dbias16[b * p.dbias_batch_stride + hk * p.dbias_head_stride + key] = float_to_raw16<kBf16>(key_ok ? tot : 0.f);
       }
     }
     if (ok && n_steps > 0) ok = __all_sync(0xffffffffu, mbar_wait(bar_final, 0, ctl, kWaitFinal));
@@ -681,7 +713,16 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = 0u;
         }
-        if (key_ok) {
+        if (p.nsplit > 1) {
+          // fp32 partial: part[dv|dk][split][b][hk][key][d]
+          float* part = p.dkv_part + ((((static_cast<int64_t>(half) * p.nsplit + split) * p.b + b) * p.h_k + hk) *
+                                          (NT * kBN) + key) * kD + c * 32;
+#pragma unroll
+          for (int v4 = 0; v4 < 8; ++v4)
+            *reinterpret_cast<float4*>(part + v4 * 4) =
+                make_float4(__uint_as_float(r[v4 * 4 + 0]) * mul, __uint_as_float(r[v4 * 4 + 1]) * mul,
+                            __uint_as_float(r[v4 * 4 + 2]) * mul, __uint_as_float(r[v4 * 4 + 3]) * mul);
+        } else if (key_ok) {
 #pragma unroll
           for (int v4 = 0; v4 < 4; ++v4) {
             uint4 o;
@@ -756,13 +797,75 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
   }
 }
 
+// Sum of the query-range partials of dK or dV: part [nsplit][B][h_k][keys_r][128] fp32 -> 16-bit (B, Sk, h_k, 128).
+template <bool kBf16>
+__global__ void __launch_bounds__(256) bwd_reduce_dkv_kernel(const float* __restrict__ part, void* __restrict__ dst,
+                                                              int nsplit, int B, int Hk, int Sk, int keys_r,
+                                                              int64_t sb, int64_t sr, int64_t sh) {
+  const int64_t n_vec = static_cast<int64_t>(B) * Hk * Sk * (kD / 8);
+  const int64_t split_stride = static_cast<int64_t>(B) * Hk * keys_r * kD;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n_vec;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(i % (kD / 8));
+    const int key = static_cast<int>((i / (kD / 8)) % Sk);
+    const int hk = static_cast<int>((i / (static_cast<int64_t>(kD / 8) * Sk)) % Hk);
+    const int b = static_cast<int>(i / (static_cast<int64_t>(kD / 8) * Sk * Hk));
+    const float* src = part + ((static_cast<int64_t>(b) * Hk + hk) * keys_r + key) * kD + c * 8;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < nsplit; ++s) {
+      const float4 a = *reinterpret_cast<const float4*>(src + s * split_stride);
+      const float4 d = *reinterpret_cast<const float4*>(src + s * split_stride + 4);
+      acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+      acc[4] += d.x; acc[5] += d.y; acc[6] += d.z; acc[7] += d.w;
+    }
+    uint4 o;
+    o.x = pack_16x2<kBf16>(acc[0], acc[1]);
+    o.y = pack_16x2<kBf16>(acc[2], acc[3]);
+    o.z = pack_16x2<kBf16>(acc[4], acc[5]);
+    o.w = pack_16x2<kBf16>(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(dst) + b * sb + static_cast<int64_t>(key) * sr + hk * sh +
+                              c * 8) = o;
+  }
+}
+
+// Sum of the query-range partials of the column-sum dBias: part [nsplit][B][h_k][keys_r] fp32 -> 16-bit
+// (B, h_k, 1, dbias_keys); keys beyond Sk are zero.
+template <bool kBf16>
+__global__ void __launch_bounds__(256) bwd_reduce_dbias_kernel(const float* __restrict__ part, void* __restrict__ dst,
+                                                                int nsplit, int B, int Hk, int dbias_keys, int Sk,
+                                                                int keys_r, int64_t sb, int64_t sh) {
+  const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (i >= static_cast<int64_t>(B) * Hk * dbias_keys) return;
+  const int key = static_cast<int>(i % dbias_keys);
+  const int hk = static_cast<int>((i / dbias_keys) % Hk);
+  const int b = static_cast<int>(i / (static_cast<int64_t>(dbias_keys) * Hk));
+  float acc = 0.f;
+  if (key < Sk)
+    for (int s = 0; s < nsplit; ++s) acc += part[((static_cast<int64_t>(s) * B + b) * Hk + hk) * keys_r + key];
+  reinterpret_cast<uint16_t*>(dst)[b * sb + hk * sh + key] = float_to_raw16<kBf16>(acc);
+}
+
 struct BwdPlan {
   bool bcast;
   bool needs_act;
   int dbias_mode;
   int sq_r;
-  size_t lse2_off, dsum_off, dq_off, act_off, dbias_off, total;
+  int nsplit;
+  size_t lse2_off, dsum_off, dq_off, act_off, dbias_off, part_off, dbpart_off, total;
 };
+
+// Query-range splits per key tile. A grid of (key tiles x kv heads x batch) CTAs that cannot fill the GPU twice is
+// cut along the query dimension until about eight CTAs per SM exist, so that the causal imbalance between key
+// tiles evens out; every split keeps at least 32 steps.
+int pick_nsplit(const fdma_fwd_params& p) {
+  const int64_t ctas = static_cast<int64_t>((p.seqlen_k + kBN - 1) / kBN) * p.h_k * p.b;
+  if (const char* e = getenv("FDMA_BWD_SPLIT_TUNE")) return std::max(1, atoi(e));
+  if (ctas >= 2 * 148) return 1;
+  const int64_t steps = static_cast<int64_t>((p.seqlen_q + kBM - 1) / kBM) * (p.h / p.h_k);
+  const int64_t want = (8 * 148 + ctas - 1) / ctas;
+  const int64_t cap = std::max<int64_t>(1, steps / 32);
+  return static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(std::min(want, cap), 64)));
+}
 
 BwdPlan plan(const fdma_bwd_params& bp) {
   const fdma_fwd_params& p = bp.f;
@@ -794,6 +897,14 @@ BwdPlan plan(const fdma_bwd_params& bp) {
   pl.dbias_off = o;
   if (pl.dbias_mode == kDbAtomic)
     o += align256(static_cast<size_t>(bp.dbias_b) * bp.dbias_h * bp.dbias_rows * bp.dbias_keys * 4);
+  pl.nsplit = pick_nsplit(p);
+  pl.part_off = pl.dbpart_off = o;
+  if (pl.nsplit > 1) {
+    const size_t keys_r = round_up(p.seqlen_k, kBN);
+    o += align256(static_cast<size_t>(2) * pl.nsplit * p.b * p.h_k * keys_r * kD * 4);
+    pl.dbpart_off = o;
+    if (pl.dbias_mode == kDbColsum) o += align256(static_cast<size_t>(pl.nsplit) * p.b * p.h_k * keys_r * 4);
+  }
   pl.total = o;
   return pl;
 }
@@ -856,6 +967,9 @@ int launch(const fdma_bwd_params& bp, const BwdPlan& pl, cudaStream_t stream) {
                         static_cast<size_t>(bp.dbias_b) * bp.dbias_h * bp.dbias_rows * bp.dbias_keys * 4, stream);
     if (e != cudaSuccess) return static_cast<int>(e);
   }
+  kp.nsplit = pl.nsplit;
+  kp.dkv_part = reinterpret_cast<float*>(ws + pl.part_off);
+  kp.dbias_part = reinterpret_cast<float*>(ws + pl.dbpart_off);
   kp.mask = static_cast<const uint8_t*>(p.mask);
   kp.bias = p.bias;
   kp.lse2 = lse2;
@@ -879,13 +993,16 @@ int launch(const fdma_bwd_params& bp, const BwdPlan& pl, cudaStream_t stream) {
   kp.dbias_b = bp.dbias_b; kp.dbias_h = bp.dbias_h; kp.dbias_rows = bp.dbias_rows; kp.dbias_keys = bp.dbias_keys;
   kp.dbias_mode = pl.dbias_mode;
   kp.is_causal = p.is_causal;
+  kp.key_pos = p.key_pos;
+  kp.pos_batch_stride = p.key_pos_batch_stride; kp.pos_head_stride = p.key_pos_head_stride;
+  kp.h_pos = p.h_pos; kp.causal_shift = p.causal_shift;
   kp.scale_log2 = p.softmax_scale * kLog2e;
   kp.scale = p.softmax_scale;
 
   auto kern = pl.bcast ? bwd_kernel<kBf16, true> : bwd_kernel<kBf16, false>;
   e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemB::kAlloc);
   if (e != cudaSuccess) return static_cast<int>(e);
-  dim3 grid((p.seqlen_k + kBN - 1) / kBN, p.h_k, p.b);
+  dim3 grid(((p.seqlen_k + kBN - 1) / kBN) * pl.nsplit, p.h_k, p.b);
   cudaEvent_t ev0, ev1;
   take_timing_events(&ev0, &ev1);
   if (ev0) cudaEventRecord(ev0, stream);
@@ -894,6 +1011,26 @@ int launch(const fdma_bwd_params& bp, const BwdPlan& pl, cudaStream_t stream) {
   e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
 
+  if (pl.nsplit > 1) {
+    const int keys_r = static_cast<int>(round_up(p.seqlen_k, kBN));
+    const int64_t n_vec = static_cast<int64_t>(p.b) * p.h_k * p.seqlen_k * (kD / 8);
+    const unsigned g = static_cast<unsigned>(std::min<int64_t>((n_vec + 255) / 256, 148 * 32));
+    for (int which = 0; which < 2; ++which) {  // 0: dV, 1: dK
+      const float* part = kp.dkv_part + static_cast<size_t>(which) * pl.nsplit * p.b * p.h_k * keys_r * kD;
+      bwd_reduce_dkv_kernel<kBf16><<<g, 256, 0, stream>>>(
+          part, which == 0 ? bp.dv : bp.dk, pl.nsplit, p.b, p.h_k, p.seqlen_k, keys_r,
+          which == 0 ? bp.dv_batch_stride : bp.dk_batch_stride, which == 0 ? bp.dv_row_stride : bp.dk_row_stride,
+          which == 0 ? bp.dv_head_stride : bp.dk_head_stride);
+    }
+    if (pl.dbias_mode == kDbColsum) {
+      const int64_t nk = static_cast<int64_t>(p.b) * p.h_k * bp.dbias_keys;
+      bwd_reduce_dbias_kernel<kBf16><<<static_cast<unsigned>((nk + 255) / 256), 256, 0, stream>>>(
+          kp.dbias_part, bp.dbias, pl.nsplit, p.b, p.h_k, bp.dbias_keys, p.seqlen_k, keys_r, bp.dbias_batch_stride,
+          bp.dbias_head_stride);
+    }
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
   {
     const int64_t n_vec = static_cast<int64_t>(p.b) * p.seqlen_q * p.h * kD / 8;
     const unsigned g = static_cast<unsigned>(std::min<int64_t>((n_vec + 255) / 256, 148 * 32));
@@ -920,6 +1057,7 @@ bool tc_bwd_supported(const fdma_bwd_params& bp) {
   if (!tc_fwd_supported(p)) return false;
   if (p.d != kD) return false;
   if (p.h_k > 65535) return false;
+  if (p.key_pos && p.is_causal && p.h_pos == p.h && p.h != p.h_k) return false;  // positions per kv head at most
   const int G = p.h / p.h_k;
   const int act_g = (p.mask && p.h_mask == p.h && G > 1) ? G : 1;
   if (static_cast<int64_t>(act_g) * ((p.seqlen_q + 127) / 128) > kMaxAct) return false;

@@ -54,6 +54,9 @@ struct FwdKernelParams {
   void* out;
   float* lse;
   const uint8_t* act;  // per-query mode: activity bytes [B][h_mask][ceil(Sq/128)][ceil(Sk/128)], or null
+  const int32_t* key_pos;  // broadcast mode only: ascending key positions of compacted keys, or null
+  int64_t pos_batch_stride, pos_head_stride;
+  int h_pos, causal_shift;
   int* status;
   int64_t o_batch_stride, o_row_stride, o_head_stride;
   int64_t mask_batch_stride, mask_head_stride, mask_row_stride;
@@ -70,7 +73,8 @@ struct Smem {
   static constexpr int kQOff = 0;
   static constexpr int kKvOff = kQOff + kNQ * kQBytes;
   static constexpr int kBmOff = kKvOff + kStages * kKvBytes;
-  static constexpr int kFlagsOff = kBmOff + kBmSlots * kBN * 4;
+  static constexpr int kPosOff = kBmOff + kBmSlots * kBN * 4;
+  static constexpr int kFlagsOff = kPosOff + kBmSlots * kBN * 4;
   static constexpr int kBarOff = kFlagsOff + kMaxTiles;
   static constexpr int kNumBars = 1 + 2 * kStages + 2 + 2 + 1 + 2 * kBmSlots + 1;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
@@ -125,6 +129,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
   unsigned char* s_q = smem + L::kQOff;
   unsigned char* s_kv = smem + L::kKvOff;
   float* s_bm = reinterpret_cast<float*>(smem + L::kBmOff);
+  int* s_pos = reinterpret_cast<int*>(smem + L::kPosOff);
   uint8_t* s_flags = smem + L::kFlagsOff;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
   uint64_t* bar_q = bars;
@@ -149,13 +154,18 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
   const int off = Sk - Sq;
   const int nt_all = (Sk + kBN - 1) / kBN;
   const bool causal = p.is_causal != 0;
+  // Compacted keys: the causal limit is tested on the keys' original positions (ascending along the tile index).
+  const int32_t* pos_row = nullptr;
+  if (kBcast && causal && p.key_pos)
+    pos_row = p.key_pos + b * p.pos_batch_stride +
+              (p.h_pos == p.h ? h : (p.h_pos == p.h_k ? hk : 0)) * p.pos_head_stride;
 
   int n_end[kNQ];
 #pragma unroll
   for (int t = 0; t < kNQ; ++t) {
     const int m0 = (mblk * kNQ + t) * kBM;
     int ne = nt_all;
-    if (causal) ne = min(ne, max(0, (m0 + kBM + off + kBN - 1) / kBN));
+    if (causal && !pos_row) ne = min(ne, max(0, (m0 + kBM + off + kBN - 1) / kBN));
     if (m0 >= Sq) ne = 0;
     n_end[t] = ne;
   }
@@ -215,6 +225,14 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
       if (any) {
         if (j < n_end[0]) f |= 1;
         if (j < n_end[1]) f |= 2;
+        if (pos_row) {  // the tile's smallest position against the last row of each query tile
+          const int64_t pmin = pos_row[j * kBN];
+#pragma unroll
+          for (int t = 0; t < kNQ; ++t) {
+            const int qlast = min((mblk * kNQ + t) * kBM + kBM - 1, Sq - 1);
+            if (pmin > static_cast<int64_t>(qlast) + p.causal_shift) f &= ~(1 << t);
+          }
+        }
       }
     } else {
 #pragma unroll
@@ -365,6 +383,17 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
           v[i] = keep ? bf * kLog2e : -CUDART_INF_F;
         }
         *reinterpret_cast<float4*>(s_bm + slot * kBN + lane * 4) = make_float4(v[0], v[1], v[2], v[3]);
+        if (pos_row) {
+          int4 pv = make_int4(0x7FFFFFFF, 0x7FFFFFFF, 0x7FFFFFFF, 0x7FFFFFFF);
+          if (k0 + 3 < Sk) {
+            pv = *reinterpret_cast<const int4*>(pos_row + k0);
+          } else {
+            if (k0 < Sk) pv.x = pos_row[k0];
+            if (k0 + 1 < Sk) pv.y = pos_row[k0 + 1];
+            if (k0 + 2 < Sk) pv.z = pos_row[k0 + 2];
+          }
+          *reinterpret_cast<int4*>(s_pos + slot * kBN + lane * 4) = pv;
+        }
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_bm_full + slot);
         ++bi;
@@ -467,10 +496,25 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
         // causal / length limit, only on tiles that cross it
         {
           int klim = Sk;  // keys < klim are visible to this row
-          if (causal) klim = min(klim, qrow + off + 1);
           const int warp_q0 = m0 + (warp & 3) * 32;  // smallest query row of this warp
           int wlim = Sk;
-          if (causal) wlim = min(wlim, warp_q0 + off + 1);
+          if (pos_row) {
+            const int* tp = s_pos + slot * kBN;
+            if (static_cast<int64_t>(tp[kBN - 1]) > static_cast<int64_t>(warp_q0) + p.causal_shift) {
+              // positions ascend: the visible keys of this row are a prefix of the tile, found by bisection
+              const int64_t lim = static_cast<int64_t>(qrow) + p.causal_shift;
+              int cnt = 0;
+#pragma unroll
+              for (int step = kBN / 2; step > 0; step >>= 1)
+                if (tp[cnt + step - 1] <= lim) cnt += step;
+              if (cnt == kBN - 1 && tp[kBN - 1] <= lim) cnt = kBN;
+              klim = min(klim, kbase + cnt);
+              wlim = kbase;  // take the per-element path
+            }
+          } else if (causal) {
+            klim = min(klim, qrow + off + 1);
+            wlim = min(wlim, warp_q0 + off + 1);
+          }
           if (kbase + kBN > wlim) {
 #pragma unroll
             for (int i = 0; i < kBN / 2; ++i) {
@@ -651,6 +695,9 @@ int launch(const fdma_fwd_params& p, const FwdPlan& pl, cudaStream_t stream) {
   kp.b = p.b; kp.seqlen_q = p.seqlen_q; kp.seqlen_k = p.seqlen_k; kp.h = p.h; kp.h_k = p.h_k;
   kp.h_mask = p.h_mask; kp.h_bias = p.h_bias;
   kp.is_causal = p.is_causal;
+  kp.key_pos = p.key_pos;
+  kp.pos_batch_stride = p.key_pos_batch_stride; kp.pos_head_stride = p.key_pos_head_stride;
+  kp.h_pos = p.h_pos; kp.causal_shift = p.causal_shift;
   kp.scale_log2 = p.softmax_scale * kLog2e;
 
   if (pl.needs_act) {
@@ -723,6 +770,10 @@ bool tc_fwd_supported(const fdma_fwd_params& p) {
   if (p.mask) {
     if (!aligned16(p.mask)) return false;
     if (p.mask_batch_stride % 16 || p.mask_head_stride % 16 || p.mask_row_stride % 16) return false;
+  }
+  if (p.key_pos && p.is_causal) {  // key positions: broadcast mode only, 16-byte vector loads of int32
+    if (!plan(p).bcast) return false;
+    if (!aligned16(p.key_pos) || p.key_pos_batch_stride % 4 || p.key_pos_head_stride % 4) return false;
   }
   return true;
 }

@@ -55,6 +55,8 @@ struct RowCtx {
   int k_limit;  // keys [0, k_limit) pass the causal / length test
   const uint8_t* mask_row;
   const void* bias_row;
+  const int32_t* pos_row;  // key positions (compacted keys) or null
+  int pos_limit;           // with pos_row and causal: key k is visible iff pos_row[k] <= pos_limit
 };
 
 template <typename T>
@@ -67,7 +69,15 @@ __device__ __forceinline__ bool locate_row(const fdma_fwd_params& p, int64_t row
   c.hk = c.h / (p.h / p.h_k);
   const bool causal = p.is_causal && p.seqlen_q > 1;
   int lim = p.seqlen_k;
-  if (causal) lim = min(lim, c.q + 1 + p.seqlen_k - p.seqlen_q);
+  c.pos_row = nullptr;
+  c.pos_limit = 0x7FFFFFFF;
+  if (causal && p.key_pos) {
+    const int hp = p.h_pos == p.h ? c.h : (p.h_pos == p.h_k ? c.hk : 0);
+    c.pos_row = p.key_pos + c.b * p.key_pos_batch_stride + hp * p.key_pos_head_stride;
+    c.pos_limit = c.q + p.causal_shift;
+  } else if (causal) {
+    lim = min(lim, c.q + 1 + p.seqlen_k - p.seqlen_q);
+  }
   c.k_limit = max(lim, 0);
   c.mask_row = nullptr;
   c.bias_row = nullptr;
@@ -107,6 +117,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) simt_fwd_kernel(const fdm
     const int k = k0 + lane;
     bool valid = k < c.k_limit;
     if (valid && c.mask_row) valid = c.mask_row[k] != 0;
+    if (valid && c.pos_row) valid = c.pos_row[k] <= c.pos_limit;
     if (!__any_sync(0xffffffffu, valid)) continue;  // skipped 32-key granule
     float s = -CUDART_INF_F;
     if (valid) {
@@ -195,6 +206,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
     const int k = k0 + lane;
     bool valid = k < c.k_limit;
     if (valid && c.mask_row) valid = c.mask_row[k] != 0;
+    if (valid && c.pos_row) valid = c.pos_row[k] <= c.pos_limit;
     if (!__any_sync(0xffffffffu, valid)) continue;
     float pr = 0.f, ds = 0.f;
     if (valid) {

@@ -23,6 +23,8 @@ class FwdParams(Structure):
         + [(n, c_int32) for n in ("b", "seqlen_q", "seqlen_k", "h", "h_k", "h_mask", "h_bias", "d")]
         + [("dtype", c_int32), ("is_causal", c_int32), ("softmax_scale", c_float), ("path", c_int32)]
         + [("workspace", c_void_p), ("workspace_bytes", c_size_t)]
+        + [("key_pos", c_void_p), ("key_pos_batch_stride", c_int64), ("key_pos_head_stride", c_int64)]
+        + [("h_pos", c_int32), ("causal_shift", c_int32)]
     )
 
 
@@ -60,7 +62,35 @@ EXPORTED_SYMBOLS = (
     "fdma_time_next_kernel",
     "fdma_fwd_static_scratch",
     "fdma_static_scratch_limit",
+    "fdma_compact_index",
+    "fdma_gather_rows",
+    "fdma_scatter_rows",
 )
+
+
+
+class CompactParams(ctypes.Structure):
+    """fdma_compact_params of include/fdma.h."""
+
+    _fields_ = [
+        ("mask", c_void_p), ("mask_batch_stride", c_int64), ("mask_head_stride", c_int64),
+        ("b_mask", c_int32), ("h_mask", c_int32), ("seqlen_k", c_int32), ("capacity", c_int32),
+        ("key_pos", c_void_p), ("count", c_void_p), ("mask_out", c_void_p),
+    ]
+
+
+class RowsParams(ctypes.Structure):
+    """fdma_rows_params of include/fdma.h."""
+
+    _fields_ = [
+        ("src", c_void_p), ("dst", c_void_p), ("key_pos", c_void_p),
+        ("key_pos_batch_stride", c_int64), ("key_pos_head_stride", c_int64),
+        ("src_batch_stride", c_int64), ("src_row_stride", c_int64), ("src_head_stride", c_int64),
+        ("dst_batch_stride", c_int64), ("dst_row_stride", c_int64), ("dst_head_stride", c_int64),
+        ("b", c_int32), ("heads", c_int32), ("h_pos", c_int32), ("rows_full", c_int32),
+        ("capacity", c_int32), ("row_elems", c_int32), ("dtype", c_int32), ("reserved_", c_int32),
+    ]
+
 
 _lib = None
 
@@ -94,6 +124,12 @@ def load():
     lib.fdma_fwd_static_scratch.restype = c_int
     lib.fdma_fwd_static_scratch.argtypes = [POINTER(FwdParams), c_void_p]
     lib.fdma_static_scratch_limit.restype = c_size_t
+    lib.fdma_compact_index.restype = c_int
+    lib.fdma_compact_index.argtypes = [POINTER(CompactParams), c_void_p]
+    lib.fdma_gather_rows.restype = c_int
+    lib.fdma_gather_rows.argtypes = [POINTER(RowsParams), c_void_p]
+    lib.fdma_scatter_rows.restype = c_int
+    lib.fdma_scatter_rows.argtypes = [POINTER(RowsParams), c_void_p]
     lib.fdma_time_next_kernel.restype = None
     lib.fdma_time_next_kernel.argtypes = [c_void_p, c_void_p]
     _lib = lib

@@ -1,0 +1,231 @@
+"""Key compaction for row-broadcast dynamic masks.
+
+When a mask keeps the same W of Sk keys for every query of a (batch, head) -- the usual shape of a dynamic mask
+built from one importance row per head, ({B|1}, {Hk|1}, 1, Sk) -- the attention over all Sk keys equals the
+attention over the W kept keys, as long as the causal test still sees the keys' original positions. This module
+gathers K, V and the bias of the kept keys into dense (B, Wp, Hk, d) tensors, runs the attention kernels over them
+with the position list, and scatters dK, dV and dBias back to their full shapes. Tiles are then W/128 per query
+block instead of "every 128-key tile that holds at least one kept key", which for scattered keep-sets is the
+difference between W/128 and Sk/128 tiles.
+
+The reference's CUDA backend has no such path; its Triton prototype gathers the top-k keys per head in the same
+way (flash_sparse_attn/flash_dmattn_triton.py:49-211). `flash_sparse_attn_func` takes this route by itself for the
+mask shapes it fits (see `set_compaction`); `flash_sparse_attn_compact_func` asks for it explicitly.
+"""
+from typing import NamedTuple, Optional
+
+import ctypes
+import torch
+
+from . import _lib
+from .flash_sparse_attn_interface import (_bsh, _check_inputs, _dtype_code, _fill_fwd, _stream_ptr, round_multiple)
+
+__all__ = ["CompactKeys", "compact_keys", "flash_sparse_attn_compact_func"]
+
+_TILE = 128
+
+
+class CompactKeys(NamedTuple):
+    key: torch.Tensor          # (B, Wp, Hk, d)
+    value: torch.Tensor        # (B, Wp, Hk, d)
+    mask: torch.Tensor         # bool (Bm, Hm, 1, Wp): slot holds a kept key
+    bias: Optional[torch.Tensor]  # (Bb, Hb, 1, Wp) or None
+    key_pos: torch.Tensor      # int32 (Bm, Hm, Wp): ascending positions, INT32_MAX in unused slots
+    count: torch.Tensor        # int32 (Bm, Hm): kept keys per row
+    seqlen_k: int              # original number of keys
+
+
+def _row_mask(attn_mask: torch.Tensor, B: int, Hk: int, Sk: int) -> torch.Tensor:
+    if attn_mask.dtype != torch.bool or attn_mask.dim() != 4:
+        raise RuntimeError("attn_mask must be a 4-D bool tensor")
+    Bm, Hm, rows, keys = attn_mask.shape
+    if rows != 1:
+        raise RuntimeError("key compaction needs a row-broadcast mask: shape ({B|1}, {Hk|1}, 1, Sk)")
+    if Bm not in (1, B) or Hm not in (1, Hk):
+        raise RuntimeError("key compaction needs mask batch in {1, B} and mask heads in {1, num_heads_k}")
+    if keys < Sk:
+        raise RuntimeError("attn_mask has fewer keys than key")
+    m = attn_mask[:, :, 0, :Sk]
+    return m if m.stride(-1) == 1 else m.contiguous()
+
+
+def _rows_call(fn, src, dst, key_pos, b, heads, rows_full, cap, row_elems, src_strides, dst_strides, device):
+    rp = _lib.RowsParams()
+    rp.src, rp.dst, rp.key_pos = src.data_ptr(), dst.data_ptr(), key_pos.data_ptr()
+    rp.key_pos_batch_stride = 0 if key_pos.shape[0] == 1 else key_pos.stride(0)
+    rp.key_pos_head_stride = key_pos.stride(1)
+    rp.src_batch_stride, rp.src_row_stride, rp.src_head_stride = src_strides
+    rp.dst_batch_stride, rp.dst_row_stride, rp.dst_head_stride = dst_strides
+    rp.b, rp.heads, rp.h_pos, rp.rows_full, rp.capacity, rp.row_elems = b, heads, key_pos.shape[1], rows_full, cap, row_elems
+    rp.dtype = _dtype_code(src)
+    _lib.check(fn(ctypes.byref(rp), _stream_ptr(device)), fn.__name__)
+
+
+def _bias_layout(attn_bias: torch.Tensor, key_pos: torch.Tensor, B: int):
+    """Batch / head extents of the compacted bias: the bias' own, widened to the position list's where that varies."""
+    Bb, Hb = attn_bias.shape[0], attn_bias.shape[1]
+    Bm, Hm = key_pos.shape[0], key_pos.shape[1]
+    if Bb not in (1, B):
+        raise RuntimeError("attn_bias batch dimension must be 1 or batch_size")
+    if attn_bias.shape[2] != 1:
+        raise RuntimeError("key compaction needs a row-broadcast bias: shape ({B|1}, {H|Hk|1}, 1, Sk)")
+    Bc, Hc = max(Bb, Bm), max(Hb, Hm)
+    if Hc % Hm:
+        raise RuntimeError("attn_bias heads must be a multiple of the mask heads")
+    return Bc, Hc
+
+
+def compact_keys(key: torch.Tensor, value: torch.Tensor, attn_mask: torch.Tensor,
+                 attn_bias: Optional[torch.Tensor] = None, capacity: Optional[int] = None,
+                 check_capacity: bool = True) -> CompactKeys:
+    """Gathers the kept keys of a row-broadcast mask. `capacity` is the number of slots per row (rounded up to a
+    multiple of 128); when omitted it is taken from the fullest mask row, which costs one device synchronisation.
+    A row with more kept keys than `capacity` raises; that check reads the counts back (one synchronisation) and is
+    skipped with check_capacity=False, for callers that know the bound holds."""
+    lib = _lib.load()
+    B, Sk, Hk, d = key.shape
+    m = _row_mask(attn_mask, B, Hk, Sk)
+    Bm, Hm = m.shape[0], m.shape[1]
+    dev = key.device
+    with torch.cuda.device(dev):
+        if capacity is None:
+            capacity = int(m.sum(dim=-1, dtype=torch.int32).max().item())
+        cap = max(_TILE, round_multiple(int(capacity), _TILE))
+        key_pos = torch.empty((Bm, Hm, cap), dtype=torch.int32, device=dev)
+        count = torch.empty((Bm, Hm), dtype=torch.int32, device=dev)
+        mask_c = torch.empty((Bm, Hm, 1, cap), dtype=torch.bool, device=dev)
+        cp = _lib.CompactParams()
+        cp.mask = m.data_ptr()
+        cp.mask_batch_stride, cp.mask_head_stride = m.stride(0), m.stride(1)
+        cp.b_mask, cp.h_mask, cp.seqlen_k, cp.capacity = Bm, Hm, Sk, cap
+        cp.key_pos, cp.count, cp.mask_out = key_pos.data_ptr(), count.data_ptr(), mask_c.data_ptr()
+        _lib.check(lib.fdma_compact_index(ctypes.byref(cp), _stream_ptr(dev)), "fdma_compact_index")
+        if check_capacity and int(count.max().item()) > cap:
+            raise RuntimeError(f"a mask row keeps more than capacity={cap} keys")
+        key = key if key.stride(-1) == 1 else key.contiguous()
+        value = value if value.stride(-1) == 1 else value.contiguous()
+        k_c = torch.empty((B, cap, Hk, d), dtype=key.dtype, device=dev)
+        v_c = torch.empty((B, cap, Hk, d), dtype=key.dtype, device=dev)
+        for src, dst in ((key, k_c), (value, v_c)):
+            _rows_call(lib.fdma_gather_rows, src, dst, key_pos, B, Hk, Sk, cap, d, _bsh(src), _bsh(dst), dev)
+        bias_c = None
+        if attn_bias is not None:
+            Bc, Hc = _bias_layout(attn_bias, key_pos, B)
+            bias_c = torch.empty((Bc, Hc, 1, cap), dtype=attn_bias.dtype, device=dev)
+            sb = 0 if attn_bias.shape[0] == 1 else attn_bias.stride(0)
+            sh = 0 if attn_bias.shape[1] == 1 else attn_bias.stride(1)
+            sr = 0 if attn_bias.shape[3] == 1 else attn_bias.stride(3)
+            _rows_call(lib.fdma_gather_rows, attn_bias, bias_c, key_pos, Bc, Hc, Sk, cap, 1, (sb, sr, sh),
+                       (bias_c.stride(0), 1, bias_c.stride(1)), dev)
+    return CompactKeys(k_c, v_c, mask_c, bias_c, key_pos, count, Sk)
+
+
+def _set_positions(p, ck: CompactKeys, seqlen_q: int):
+    p.key_pos = ck.key_pos.data_ptr()
+    p.key_pos_batch_stride = 0 if ck.key_pos.shape[0] == 1 else ck.key_pos.stride(0)
+    p.key_pos_head_stride = ck.key_pos.stride(1)
+    p.h_pos = ck.key_pos.shape[1]
+    p.causal_shift = ck.seqlen_k - seqlen_q
+
+
+class _CompactAttnFunc(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, mask, bias, softmax_scale, is_causal, capacity, trusted):
+        lib = _lib.load()
+        q = q if q.stride(-1) == 1 else q.contiguous()
+        ck = compact_keys(k, v, mask, bias, capacity, check_capacity=not trusted)
+        _check_inputs(q, ck.key, ck.value, ck.mask, ck.bias)
+        B, Sq, H, d = q.shape
+        dev = q.device
+        with torch.cuda.device(dev):
+            out = torch.empty_like(q)
+            lse = torch.empty((B, H, Sq), dtype=torch.float32, device=dev)
+            p = _lib.FwdParams()
+            _fill_fwd(p, q, ck.key, ck.value, ck.mask, ck.bias, out, lse, softmax_scale, is_causal)
+            _set_positions(p, ck, Sq)
+            ws_bytes = lib.fdma_fwd_workspace_bytes(ctypes.byref(p))
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev) if ws_bytes else None
+            if ws is not None:
+                p.workspace, p.workspace_bytes = ws.data_ptr(), ws_bytes
+            _lib.check(lib.fdma_fwd(ctypes.byref(p), _stream_ptr(dev)), "fdma_fwd")
+        saved = [q, ck.key, ck.value, ck.mask, ck.key_pos, out, lse] + ([ck.bias] if ck.bias is not None else [])
+        ctx.save_for_backward(*saved)
+        ctx.has_bias = ck.bias is not None
+        ctx.meta = (softmax_scale, is_causal, ck.seqlen_k, tuple(k.shape), tuple(bias.shape) if bias is not None else None)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        lib = _lib.load()
+        saved = ctx.saved_tensors
+        q, k_c, v_c, mask_c, key_pos, out, lse = saved[:7]
+        bias_c = saved[7] if ctx.has_bias else None
+        softmax_scale, is_causal, Sk, k_shape, bias_shape = ctx.meta
+        B, Sq, H, d = q.shape
+        Hk, cap = k_c.shape[2], k_c.shape[1]
+        dev = q.device
+        dout = dout if dout.stride(-1) == 1 else dout.contiguous()
+        ck = CompactKeys(k_c, v_c, mask_c, bias_c, key_pos, None, Sk)
+        with torch.cuda.device(dev):
+            dq = torch.empty_like(q)
+            dk_c, dv_c = torch.empty_like(k_c), torch.empty_like(v_c)
+            dbias_c = torch.empty_like(bias_c) if bias_c is not None else None
+            bp = _lib.BwdParams()
+            _fill_fwd(bp.f, q, k_c, v_c, mask_c, bias_c, out, lse, softmax_scale, is_causal)
+            _set_positions(bp.f, ck, Sq)
+            bp.dout = dout.data_ptr()
+            bp.do_batch_stride, bp.do_row_stride, bp.do_head_stride = _bsh(dout)
+            bp.dq, bp.dk, bp.dv = dq.data_ptr(), dk_c.data_ptr(), dv_c.data_ptr()
+            bp.dq_batch_stride, bp.dq_row_stride, bp.dq_head_stride = _bsh(dq)
+            bp.dk_batch_stride, bp.dk_row_stride, bp.dk_head_stride = _bsh(dk_c)
+            bp.dv_batch_stride, bp.dv_row_stride, bp.dv_head_stride = _bsh(dv_c)
+            if dbias_c is not None:
+                bp.dbias = dbias_c.data_ptr()
+                bp.dbias_batch_stride, bp.dbias_head_stride, bp.dbias_row_stride = dbias_c.stride()[:3]
+                bp.dbias_b, bp.dbias_h, bp.dbias_rows, bp.dbias_keys = dbias_c.shape
+            ws_bytes = lib.fdma_bwd_workspace_bytes(ctypes.byref(bp))
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev) if ws_bytes else None
+            if ws is not None:
+                bp.f.workspace, bp.f.workspace_bytes = ws.data_ptr(), ws_bytes
+            _lib.check(lib.fdma_bwd(ctypes.byref(bp), _stream_ptr(dev)), "fdma_bwd")
+            dk = torch.empty(k_shape, dtype=q.dtype, device=dev)
+            dv = torch.empty(k_shape, dtype=q.dtype, device=dev)
+            for src, dst in ((dk_c, dk), (dv_c, dv)):
+                _rows_call(lib.fdma_scatter_rows, src, dst, key_pos, B, Hk, Sk, cap, d, _bsh(src), _bsh(dst), dev)
+            dbias = None
+            if dbias_c is not None:
+                Bc, Hc = dbias_c.shape[0], dbias_c.shape[1]
+                full = torch.empty((Bc, Hc, 1, Sk), dtype=q.dtype, device=dev)
+                _rows_call(lib.fdma_scatter_rows, dbias_c, full, key_pos, Bc, Hc, Sk, cap, 1,
+                           (dbias_c.stride(0), 1, dbias_c.stride(1)), (full.stride(0), 1, full.stride(1)), dev)
+                # dimensions the bias broadcast over (and the compaction widened) are summed back
+                for dim in (0, 1, 3):
+                    if bias_shape[dim] == 1 and full.shape[dim] != 1:
+                        full = full.sum(dim=dim, keepdim=True, dtype=torch.float32).to(q.dtype)
+                if bias_shape[3] > Sk:
+                    full = torch.nn.functional.pad(full, [0, bias_shape[3] - Sk])
+                dbias = full
+        return dq, dk, dv, None, dbias, None, None, None, None
+
+
+def flash_sparse_attn_compact_func(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    attn_mask: torch.Tensor,
+    attn_bias: Optional[torch.Tensor] = None,
+    softmax_scale: Optional[float] = None,
+    is_causal: Optional[bool] = None,
+    capacity: Optional[int] = None,
+    _trusted_capacity: bool = False,
+):
+    """Same result as `flash_sparse_attn_func(query, key, value, attn_mask, attn_bias, softmax_scale, is_causal)`
+    for a row-broadcast mask ({B|1}, {Hk|1}, 1, Sk) and bias ({B|1}, {H|Hk|1}, 1, Sk), computed over the kept keys
+    only. `capacity` bounds the kept keys per mask row (e.g. the keep_window_size the mask was built with); when
+    omitted it is read back from the device. head_dim must be a multiple of 8."""
+    softmax_scale = query.shape[-1] ** (-0.5) if softmax_scale is None else softmax_scale
+    is_causal = bool(is_causal) if is_causal is not None else False
+    if attn_bias is not None and attn_bias.shape[-1] not in (1, key.shape[1]) and attn_bias.shape[-1] < key.shape[1]:
+        raise RuntimeError("attn_bias has fewer keys than key")
+    return _CompactAttnFunc.apply(query, key, value, attn_mask, attn_bias, softmax_scale, is_causal, capacity,
+                                  _trusted_capacity and capacity is not None)

@@ -13,7 +13,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["flash_sparse_attn_func", "FlashDMAttnFunc", "set_kernel_path"]
+__all__ = ["flash_sparse_attn_func", "FlashDMAttnFunc", "set_kernel_path", "set_compaction"]
 
 _KEY_PAD = 128  # mask / bias key dimension is padded to a multiple of this (interface.py:420-430 of the reference)
 _kernel_path = _lib.PATH_AUTO
@@ -24,6 +24,50 @@ def set_kernel_path(path: str) -> None:
     global _kernel_path
     _kernel_path = {"auto": _lib.PATH_AUTO, "simt": _lib.PATH_SIMT, "tcgen05": _lib.PATH_TCGEN05,
                     "decode": _lib.PATH_DECODE}[path]
+
+
+_compaction = "auto"
+
+
+def set_compaction(mode: str) -> None:
+    """"auto" (default): a row-broadcast mask is handled by gathering its kept keys first (see compaction.py);
+    "off": always run over the full key range with tile skipping."""
+    global _compaction
+    if mode not in ("auto", "off"):
+        raise ValueError("compaction mode must be 'auto' or 'off'")
+    _compaction = mode
+
+
+def _compaction_capacity(query, key, attn_mask, attn_bias, softcap, return_attn_probs) -> Optional[int]:
+    """Slots per mask row if this call is to run over gathered keys, else None. Eligible: Sq > 1, head dim a
+    multiple of 8, mask ({B|1}, {Hk|1}, 1, >=Sk), bias absent or row-broadcast, no softcap / returned probabilities.
+    The bound on kept keys comes from the tag `create_mask` leaves on its result; an untagged (or since edited)
+    mask has its counts read back from the device, which synchronises the stream. A mask that keeps more than three
+    quarters of the keys is left to the tile-skipping path."""
+    if _compaction != "auto" or attn_mask is None or softcap or return_attn_probs:
+        return None
+    if query.dim() != 4 or key.dim() != 4 or attn_mask.dim() != 4 or attn_mask.dtype != torch.bool:
+        return None
+    B, Sq, H, d = query.shape
+    Sk, Hk = key.shape[1], key.shape[2]
+    if Sq <= 1 or d % 8 or not query.is_cuda:
+        return None
+    if attn_mask.shape[2] != 1 or attn_mask.shape[1] not in (1, Hk) or attn_mask.shape[0] not in (1, B):
+        return None
+    if attn_mask.shape[3] < Sk:
+        return None
+    if attn_bias is not None:
+        if attn_bias.dim() != 4 or attn_bias.shape[2] != 1 or attn_bias.shape[3] < Sk:
+            return None
+        if attn_bias.shape[0] not in (1, B) or attn_bias.shape[1] not in (1, Hk, H):
+            return None
+    tag = getattr(attn_mask, "_fdma_keep_bound", None)
+    if tag is not None and tag[1] == attn_mask._version:
+        bound = tag[0]
+    else:
+        bound = int(attn_mask[..., :Sk].sum(dim=-1, dtype=torch.int32).max().item())
+    cap = max(_KEY_PAD, round_multiple(bound, _KEY_PAD))
+    return cap if 4 * cap <= 3 * round_multiple(Sk, _KEY_PAD) else None
 
 
 def round_multiple(x: int, m: int) -> int:
@@ -328,7 +372,16 @@ def flash_sparse_attn_func(
     bottom-right corner (key k visible to query q iff k <= q + Sk - Sq). Rows with no visible key return 0.
     softmax_scale defaults to d ** -0.5. softcap > 0 and return_attn_probs=True raise NotImplementedError.
     Returns out (B, Sq, H, d); gradients flow to query, key, value and attn_bias.
+
+    A row-broadcast mask (one keep-set per batch and kv head) is run over its gathered kept keys, which gives the
+    same result in far fewer key tiles when the kept keys are scattered; `set_compaction("off")` disables that.
     """
+    cap = _compaction_capacity(query, key, attn_mask, attn_bias, softcap, return_attn_probs)
+    if cap is not None:
+        from .compaction import flash_sparse_attn_compact_func
+
+        return flash_sparse_attn_compact_func(query, key, value, attn_mask, attn_bias, softmax_scale, is_causal, cap,
+                                              _trusted_capacity=True)
     return FlashDMAttnFunc.apply(
         query, key, value, attn_mask, attn_bias, softmax_scale, is_causal, softcap, deterministic,
         return_attn_probs, torch.is_grad_enabled(),

@@ -124,7 +124,13 @@ def create_mask(
                 f"or query_len {query_len}."
             )
     if type == "topk":
-        return topk_mask(attention_bias, attention_mask, window_size, min_dtype, block_size)
+        mask = topk_mask(attention_bias, attention_mask, window_size, min_dtype, block_size)
+        if block_size is None or block_size <= 1:
+            # At most window_size keys are kept per row. The attention entry point uses this bound to size its
+            # compacted key tensors without reading the counts back; the tensor's version counter ties the bound
+            # to the mask's current contents (any in-place edit invalidates it).
+            mask._fdma_keep_bound = (min(int(window_size), int(mask.shape[-1])), mask._version)
+        return mask
     if type == "relu":
         return relu_mask(attention_bias, attention_mask, min_dtype, block_size)
     raise ValueError(f"Unsupported mask type: {type}. Supported types are 'topk' and 'relu'.")

@@ -80,6 +80,15 @@ typedef struct fdma_fwd_params {
   int32_t path;      /* fdma_path */
   void* workspace;
   size_t workspace_bytes;
+  /* Optional key positions, for K/V that were compacted to the kept keys (fdma_compact_gather): int32
+   * ({B|1}, h_pos, Sk), ascending along the key dimension, h_pos in {1, h_k, h}. NULL: key k sits at position k.
+   * When given, the causal test of key k is key_pos[k] <= q + causal_shift (causal_shift = original Sk - Sq);
+   * is_causal = 0 ignores both. No counterpart in the reference's CUDA backend (its Triton prototype
+   * flash_dmattn_triton.py:49-211 gathers keys the same way). */
+  const int32_t* key_pos;
+  int64_t key_pos_batch_stride, key_pos_head_stride;
+  int32_t h_pos;
+  int32_t causal_shift;
 } fdma_fwd_params;
 
 size_t fdma_fwd_workspace_bytes(const fdma_fwd_params* p);
@@ -176,6 +185,49 @@ int fdma_last_kernel_status(void* stream, int32_t* detail);
  */
 int fdma_fwd_static_scratch(const fdma_fwd_params* p, void* stream);
 size_t fdma_static_scratch_limit(void);
+
+/*
+ * Key compaction for row-broadcast masks (no counterpart in the reference's CUDA backend; its Triton prototype
+ * gathers the top-k keys the same way, flash_sparse_attn/flash_dmattn_triton.py:49-211). When all queries of a
+ * (batch, head) keep the same W of Sk keys, attention over the W gathered keys equals attention over all Sk keys,
+ * provided the causal test uses the keys' original positions (fdma_fwd_params::key_pos).
+ *
+ * fdma_compact_index: for every mask row writes the ascending positions of its kept keys into
+ * key_pos[row][0..count), INT32_MAX into the remaining slots, the number of kept keys into count[row] (which
+ * may exceed `capacity`: positions beyond the capacity are dropped, the caller must check), and, when mask_out is
+ * given, slot < count into mask_out[row][slot].
+ */
+typedef struct fdma_compact_params {
+  const void* mask;                 /* bool bytes (b_mask, h_mask, seqlen_k), keys contiguous */
+  int64_t mask_batch_stride, mask_head_stride;
+  int32_t b_mask, h_mask, seqlen_k, capacity;
+  int32_t* key_pos;                 /* out, dense (b_mask, h_mask, capacity) */
+  int32_t* count;                   /* out, dense (b_mask, h_mask) */
+  void* mask_out;                   /* out or NULL, dense bool bytes (b_mask, h_mask, capacity) */
+} fdma_compact_params;
+int fdma_compact_index(const fdma_compact_params* p, void* stream);
+
+/*
+ * fdma_gather_rows: dst[b][slot][h][:] = src[b][key_pos[b][h / (heads / h_pos)][slot]][h][:], zeros in slots whose
+ * position is outside [0, rows_full). src is (b, rows_full, heads, row_elems), dst (b, capacity, heads,
+ * row_elems); strides in elements, the innermost dimension is contiguous. A (B, H, 1, Sk) bias is passed as
+ * row_elems = 1, row stride 1, head stride = its head stride.
+ * fdma_scatter_rows: the inverse for gradients: dst (b, rows_full, heads, row_elems) is zero-filled, then
+ * dst[b][key_pos[..][slot]][h][:] = src[b][slot][h][:] for the filled slots.
+ */
+typedef struct fdma_rows_params {
+  const void* src;
+  void* dst;
+  const int32_t* key_pos;
+  int64_t key_pos_batch_stride, key_pos_head_stride; /* batch stride 0 for a batch-broadcast list */
+  int64_t src_batch_stride, src_row_stride, src_head_stride;
+  int64_t dst_batch_stride, dst_row_stride, dst_head_stride;
+  int32_t b, heads, h_pos, rows_full, capacity, row_elems;
+  int32_t dtype;                    /* FDMA_BF16 or FDMA_FP16 */
+  int32_t reserved_;
+} fdma_rows_params;
+int fdma_gather_rows(const fdma_rows_params* p, void* stream);
+int fdma_scatter_rows(const fdma_rows_params* p, void* stream);
 
 /*
  * Measurement hook (no counterpart in the reference, which is timed from Python with wall clocks,

@@ -65,10 +65,14 @@ def test_null_and_invalid_arguments_are_rejected_without_a_device():
 
 def test_struct_layout_matches_the_header():
     # sizes measured from the C header with gcc on x86-64 (LP64): a change on either side must show up here
-    assert ctypes.sizeof(_lib.FwdParams) == 264
-    assert ctypes.sizeof(_lib.BwdParams) == 448
+    assert ctypes.sizeof(_lib.FwdParams) == 296
+    assert ctypes.sizeof(_lib.BwdParams) == 480
+    assert ctypes.sizeof(_lib.CompactParams) == 64
+    assert ctypes.sizeof(_lib.RowsParams) == 120
+    assert _lib.FwdParams.key_pos.offset == 264
+    assert _lib.FwdParams.causal_shift.offset == 292
     assert ctypes.sizeof(_lib.MaskParams) == 112
     assert _lib.FwdParams.workspace.offset == 248
-    assert _lib.BwdParams.dout.offset == 264
-    assert _lib.BwdParams.dbias_b.offset == 424
+    assert _lib.BwdParams.dout.offset == 296
+    assert _lib.BwdParams.dbias_b.offset == 456
     assert _lib.MaskParams.min_value.offset == 104

@@ -24,6 +24,18 @@ def dev():
     return torch.device("cuda:0")
 
 
+@pytest.fixture(autouse=True, params=["off", "auto"], ids=["tiles", "compaction"])
+def compaction_mode(request):
+    """Every case runs twice: over the full key range with tile skipping, and with the library's default, which
+    gathers the kept keys first when the mask is row-broadcast (cases with other mask shapes run the same code in
+    both modes)."""
+    from flash_sparse_attn import flash_sparse_attn_interface as iface
+
+    iface.set_compaction(request.param)
+    yield request.param
+    iface.set_compaction("auto")
+
+
 @pytest.fixture
 def kernel_path():
     from flash_sparse_attn import flash_sparse_attn_interface as iface

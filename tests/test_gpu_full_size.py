@@ -22,6 +22,16 @@ def dev():
     return torch.device("cuda:0")
 
 
+@pytest.fixture(autouse=True, params=["off", "auto"], ids=["tiles", "compaction"])
+def compaction_mode(request):
+    """Both routes at full size: tile skipping over all keys, and the default (kept keys gathered first)."""
+    from flash_sparse_attn import flash_sparse_attn_interface as iface
+
+    iface.set_compaction(request.param)
+    yield request.param
+    iface.set_compaction("auto")
+
+
 def _run(q, k, v, mask, bias, dout, causal=True):
     from flash_sparse_attn import flash_sparse_attn_func
 
