@@ -7,11 +7,15 @@ Workload (BASELINE.json configs[2], the shape its metric is quoted on): S = Sq =
 dOut ~ N(0,1), seeded synthetic data. One batch element per GPU (8 independent (batch, kv-head) units); with N GPUs
 the global batch is N, sharded over ranks with no collective in the data path (weak scaling).
 
-A step = one forward + one backward through the C ABI (fdma_fwd, fdma_bwd); create_mask is outside the timed
-region, as in the reference's benchmarks (benchmarks/forward_performance.py:185-204). FLOPs are counted only on
-kept tiles of the tile shape each kernel really uses, from the actual mask (4*d*BM*BN per forward tile, 10*d*BM*BN
-per backward tile). `value` has inputs resident in HBM; `e2e` goes through flash_sparse_attn_func with pinned host
-buffers, copying inputs up and results back inside the timed region.
+A step = one forward + one backward through the C ABI, the same sequence of calls flash_sparse_attn_func makes
+for this mask shape: fdma_compact_index, fdma_gather_rows (K, V, bias), fdma_fwd, fdma_bwd, fdma_scatter_rows
+(dK, dV, dBias). The mask is row-broadcast, so the library gathers the kept keys first and the attention kernels
+run over W instead of Sk keys (--compaction off times fdma_fwd + fdma_bwd over the full key range; the default
+run reports that too, as `tile_path`). create_mask is outside the timed region, as in the reference's benchmarks
+(benchmarks/forward_performance.py:185-204). FLOPs are counted only on the tiles the kernels really process, of
+the tile shape each kernel uses, from the actual mask (4*d*BM*BN per forward tile, 10*d*BM*BN per backward tile);
+both arms use the same count. `value` has inputs resident in HBM; `e2e` goes through flash_sparse_attn_func with
+pinned host buffers, copying inputs up and results back inside the timed region.
 
 --impl reference times the reference's eager algorithm (the CPU oracle port, oracle/oracle.py) on the host cores
 on a bounded sample of the same workload.
@@ -51,33 +55,44 @@ NOMINAL_TFLOPS = 2250.0
 # ------------------------------------------------------------------------------------------------------------
 # FLOP accounting on kept tiles (host side, from the actual mask)
 # ------------------------------------------------------------------------------------------------------------
-def kept_tiles_rowbcast(mask_row: torch.Tensor, Sq: int, Sk: int, bm: int, bn: int, causal: bool) -> int:
+def kept_tiles_rowbcast(mask_row: torch.Tensor, Sq: int, Sk: int, bm: int, bn: int, causal: bool,
+                        compact: bool = False) -> int:
     """Number of (bm x bn) tiles holding at least one kept, causally visible element, for a mask that is the
-    same for every query row. mask_row: bool (Sk,)."""
-    nt = (Sk + bn - 1) // bn
+    same for every query row. mask_row: bool (Sk,). compact: key tiles are runs of bn consecutive KEPT keys (the
+    gathered layout) instead of bn consecutive key positions."""
     mt = (Sq + bm - 1) // bm
-    idx = torch.arange(Sk, device=mask_row.device)
     big = Sk + Sq + 1
-    first = torch.where(mask_row[:Sk], idx, torch.full_like(idx, big))
-    pad = nt * bn - Sk
-    if pad:
-        first = torch.cat([first, torch.full((pad,), big, device=first.device, dtype=first.dtype)])
-    kmin = first.view(nt, bn).amin(dim=1)                       # first kept key of each key tile
+    if compact:
+        pos = torch.nonzero(mask_row[:Sk]).flatten()
+        kmin = pos[::bn]                                        # first position of each gathered key tile
+        nt = kmin.numel()
+        if nt == 0:
+            return 0
+    else:
+        nt = (Sk + bn - 1) // bn
+        idx = torch.arange(Sk, device=mask_row.device)
+        first = torch.where(mask_row[:Sk], idx, torch.full_like(idx, big))
+        pad = nt * bn - Sk
+        if pad:
+            first = torch.cat([first, torch.full((pad,), big, device=first.device, dtype=first.dtype)])
+        kmin = first.view(nt, bn).amin(dim=1)                   # first kept key of each key tile
     last_row = torch.clamp((torch.arange(mt, device=mask_row.device) + 1) * bm - 1, max=Sq - 1)
     limit = last_row + (Sk - Sq) if causal else torch.full_like(last_row, big - 1)
     return int((kmin.view(1, nt) <= limit.view(mt, 1)).sum().item())
 
 
-def count_flops(mask: torch.Tensor, B: int, Sq: int, Sk: int, H: int, Hk: int, d: int, causal: bool) -> dict:
-    """mask (B,Hk,1,Sk) bool. Returns FLOPs per pass under the accounting rules of the metric."""
+def count_flops(mask: torch.Tensor, B: int, Sq: int, Sk: int, H: int, Hk: int, d: int, causal: bool,
+                compact: bool = False) -> dict:
+    """mask (B,Hk,1,Sk) bool. Returns FLOPs per pass under the accounting rules of the metric, for the full-range
+    (compact=False) or the gathered-keys (compact=True) tiling."""
     G = H // Hk
     kept_f = kept_b = kept_c = 0
     for b in range(B):
         for hk in range(Hk):
             row = mask[b, hk, 0]
-            kept_f += G * kept_tiles_rowbcast(row, Sq, Sk, *FWD_TILE, causal)
-            kept_b += G * kept_tiles_rowbcast(row, Sq, Sk, *BWD_TILE, causal)
-            kept_c += G * kept_tiles_rowbcast(row, Sq, Sk, 128, 128, causal)
+            kept_f += G * kept_tiles_rowbcast(row, Sq, Sk, *FWD_TILE, causal, compact)
+            kept_b += G * kept_tiles_rowbcast(row, Sq, Sk, *BWD_TILE, causal, compact)
+            kept_c += G * kept_tiles_rowbcast(row, Sq, Sk, 128, 128, causal, compact)
     mt, nt = (Sq + 127) // 128, (Sk + 127) // 128
     causal_tiles = sum(min(nt, max(0, ((i + 1) * 128 + Sk - Sq + 127) // 128)) for i in range(mt)) if causal else mt * nt
     fwd = 4 * d * FWD_TILE[0] * FWD_TILE[1] * kept_f
@@ -93,6 +108,10 @@ def count_flops(mask: torch.Tensor, B: int, Sq: int, Sk: int, H: int, Hk: int, d
 # clocks sampler
 # ------------------------------------------------------------------------------------------------------------
 class ClockSampler:
+    """nvidia-smi polled every 10 ms from before the warm-up until the timed region ends (the tool needs a few
+    hundred ms before its first sample, longer than a short timed region). The summary takes the samples between
+    `mark()` (start of the timed region, minus the warm-up that directly precedes it) and stop()."""
+
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
@@ -101,11 +120,15 @@ class ClockSampler:
         self.gpu_index = gpu_index
         self.proc = None
         self.lines = []
+        self.t_region = None
+
+    def mark(self):
+        self.t_region = time.time()
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "10",
                  "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -114,7 +137,7 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
 
     def stop(self) -> dict:
         if self.proc is None:
@@ -125,7 +148,8 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
         sm, smax, reasons = [], [], set()
-        for ln in self.lines:
+        in_region = 0
+        for t_line, ln in self.lines:
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 9:
                 continue
@@ -134,6 +158,8 @@ class ClockSampler:
                 smax.append(float(f[2]))
             except ValueError:
                 continue
+            if self.t_region is not None and t_line >= self.t_region:
+                in_region += 1
             for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
@@ -141,6 +167,8 @@ class ClockSampler:
             "sm_mhz": statistics.median(sm) if sm else None,
             "sm_max_mhz": max(smax) if smax else None,
             "samples": len(sm),
+            "samples_in_timed_region": in_region,
+            "window": "warm-up + timed region",
             "reasons": sorted(reasons),
         }
 
@@ -151,7 +179,7 @@ class ClockSampler:
 CPU_ROWS = 1024  # query rows of the bounded CPU sample (the last rows of the sequence: full causal extent)
 
 
-def cpu_sample(steps: int, warmup: int) -> dict:
+def cpu_sample(steps: int, warmup: int, compact: bool = True) -> dict:
     """Eager fp32 forward+backward of ONE kv head (its 4 query heads) x the last CPU_ROWS query rows against
     all 32768 keys, timed on the host cores; FLOPs counted on that slice's kept 128x128 tiles."""
     from oracle import oracle
@@ -159,7 +187,7 @@ def cpu_sample(steps: int, warmup: int) -> dict:
     G = HQ // HKV
     q, k, v, bias, dout = oracle.make_inputs(1, CPU_ROWS, S, G, 1, D, (1, 1, 1, S), seed=0, dtype=torch.bfloat16)
     mask = oracle.create_mask(bias, None, 1, CPU_ROWS, S, WINDOW, torch.finfo(torch.bfloat16).min)
-    flops = count_flops(mask, 1, CPU_ROWS, S, G, 1, D, True)
+    flops = count_flops(mask, 1, CPU_ROWS, S, G, 1, D, True, compact)
     times = []
     for it in range(warmup + steps):
         t0 = time.perf_counter()
@@ -171,7 +199,8 @@ def cpu_sample(steps: int, warmup: int) -> dict:
     return {
         "value": flop_ref / sec / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
         "sample": f"1 kv head x {G} query heads x last {CPU_ROWS} query rows x {S} keys, fp32 eager, "
-                  f"{sec * 1e3:.0f} ms per fwd+bwd, kept-tile FLOPs at 128x128",
+                  f"{sec * 1e3:.0f} ms per fwd+bwd, FLOPs on 128x128 tiles of "
+                  f"{'the gathered kept keys' if compact else 'the full key range'}",
         "ms_per_step": sec * 1e3,
     }
 
@@ -180,7 +209,7 @@ def run_reference(args, rank: int, world: int):
     if rank != 0:
         return
     steps = max(1, min(args.steps, 10))  # ~4 s of host work per step: keeps the arm within a few minutes
-    cb = cpu_sample(steps, min(args.warmup, 1))
+    cb = cpu_sample(steps, min(args.warmup, 1), args.compaction == "auto")
     line = {
         "impl": "reference", "metric": "fwd+bwd TFLOP/s on kept blocks", "value": cb["value"], "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": cb["ms_per_step"],
@@ -205,6 +234,122 @@ def load_peaks():
     return 1400.0, "fallback (sustained)"
 
 
+class AttentionStep:
+    """Pre-allocated buffers and pre-filled C-ABI parameter blocks for one forward + backward of the workload, over
+    the full key range (compact=False: fdma_fwd, fdma_bwd) or over the gathered kept keys (compact=True: the nine
+    calls flash_sparse_attn_func makes for a row-broadcast mask)."""
+
+    def __init__(self, lib, dev, q, k, v, mask, bias, dout, compact: bool):
+        from flash_sparse_attn import _lib, compaction
+        from flash_sparse_attn import flash_sparse_attn_interface as iface
+
+        self.lib, self._lib, self.compact = lib, _lib, compact
+        self.stream = torch.cuda.current_stream(dev)
+        B, Sq, H, d = q.shape
+        Sk, Hk = k.shape[1], k.shape[2]
+        self.out = torch.empty_like(q)
+        self.lse = torch.empty((B, H, Sq), dtype=torch.float32, device=dev)
+        self.dq, self.dk, self.dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        self.dbias = torch.empty_like(bias)
+        self.pre, self.post = [], []  # (function, parameter block) run before the forward / after the backward
+        kk, vv, mm, bb, dkk, dvv, dbb = k, v, mask, bias, self.dk, self.dv, self.dbias
+        if compact:
+            cap = iface.round_multiple(WINDOW, 128)
+            Bm, Hm = mask.shape[0], mask.shape[1]
+            self.key_pos = torch.empty((Bm, Hm, cap), dtype=torch.int32, device=dev)
+            self.count = torch.empty((Bm, Hm), dtype=torch.int32, device=dev)
+            mm = torch.empty((Bm, Hm, 1, cap), dtype=torch.bool, device=dev)
+            kk, vv = (torch.empty((B, cap, Hk, d), dtype=q.dtype, device=dev) for _ in range(2))
+            bb = torch.empty((bias.shape[0], bias.shape[1], 1, cap), dtype=q.dtype, device=dev)
+            dkk, dvv, dbb = torch.empty_like(kk), torch.empty_like(vv), torch.empty_like(bb)
+            m2 = mask[:, :, 0, :Sk]
+            cp = _lib.CompactParams()
+            cp.mask, cp.mask_batch_stride, cp.mask_head_stride = m2.data_ptr(), m2.stride(0), m2.stride(1)
+            cp.b_mask, cp.h_mask, cp.seqlen_k, cp.capacity = Bm, Hm, Sk, cap
+            cp.key_pos, cp.count, cp.mask_out = self.key_pos.data_ptr(), self.count.data_ptr(), mm.data_ptr()
+            self.pre.append((lib.fdma_compact_index, cp))
+            bst = lambda t: (t.stride(0), 1, t.stride(1))  # a (B, H, 1, keys) bias as rows of one element
+            for src, dst in ((k, kk), (v, vv)):
+                self.pre.append((lib.fdma_gather_rows, compaction._rows_params(
+                    src, dst, self.key_pos, B, Hk, Sk, cap, d, iface._bsh(src), iface._bsh(dst))))
+            self.pre.append((lib.fdma_gather_rows, compaction._rows_params(
+                bias, bb, self.key_pos, bias.shape[0], bias.shape[1], Sk, cap, 1, bst(bias), bst(bb))))
+            for src, dst in ((dkk, self.dk), (dvv, self.dv)):
+                self.post.append((lib.fdma_scatter_rows, compaction._rows_params(
+                    src, dst, self.key_pos, B, Hk, Sk, cap, d, iface._bsh(src), iface._bsh(dst))))
+            self.post.append((lib.fdma_scatter_rows, compaction._rows_params(
+                dbb, self.dbias, self.key_pos, bias.shape[0], bias.shape[1], Sk, cap, 1, bst(dbb), bst(self.dbias))))
+        self.keep = (kk, vv, mm, bb, dkk, dvv, dbb)
+        self.fp = _lib.FwdParams()
+        self.bp = _lib.BwdParams()
+        for p in (self.fp, self.bp.f):
+            iface._fill_fwd(p, q, kk, vv, mm, bb, self.out, self.lse, d ** -0.5, True)
+            if compact:
+                p.key_pos, p.key_pos_batch_stride = self.key_pos.data_ptr(), self.key_pos.stride(0)
+                p.key_pos_head_stride, p.h_pos, p.causal_shift = self.key_pos.stride(1), self.key_pos.shape[1], Sk - Sq
+        bp = self.bp
+        bp.dout = dout.data_ptr()
+        bp.do_batch_stride, bp.do_row_stride, bp.do_head_stride = iface._bsh(dout)
+        bp.dq, bp.dk, bp.dv, bp.dbias = self.dq.data_ptr(), dkk.data_ptr(), dvv.data_ptr(), dbb.data_ptr()
+        bp.dq_batch_stride, bp.dq_row_stride, bp.dq_head_stride = iface._bsh(self.dq)
+        bp.dk_batch_stride, bp.dk_row_stride, bp.dk_head_stride = iface._bsh(dkk)
+        bp.dv_batch_stride, bp.dv_row_stride, bp.dv_head_stride = iface._bsh(dvv)
+        bp.dbias_batch_stride, bp.dbias_head_stride, bp.dbias_row_stride = dbb.stride()[:3]
+        bp.dbias_b, bp.dbias_h, bp.dbias_rows, bp.dbias_keys = dbb.shape
+        if compact:  # workspace sizes depend on the positions only through their presence
+            self.run_pre()
+        ws_f = lib.fdma_fwd_workspace_bytes(ctypes.byref(self.fp))
+        ws_b = lib.fdma_bwd_workspace_bytes(ctypes.byref(bp))
+        self.ws = torch.empty(max(ws_f, ws_b, 1), dtype=torch.uint8, device=dev)
+        self.fp.workspace, self.fp.workspace_bytes = self.ws.data_ptr(), ws_f
+        bp.f.workspace, bp.f.workspace_bytes = self.ws.data_ptr(), ws_b
+        # launches per step, from the code paths above: index 1 + gathers 3 | fwd_kernel 1 | bwd_prep, bwd_kernel,
+        # convert_dq 3 (+ 3 partial reductions when the backward grid is split) | scatters 3 (their zero fills are memsets)
+        self.launches = (4 + 1 + 6 + 3) if compact else 4
+
+    def run_pre(self):
+        for fn, prm in self.pre:
+            self._lib.check(fn(ctypes.byref(prm), self.stream.cuda_stream), "compaction")
+
+    def __call__(self, ev=None):
+        lib, st = self.lib, self.stream.cuda_stream
+        self.run_pre()
+        if ev is not None:
+            lib.fdma_time_next_kernel(ev[0].cuda_event, ev[1].cuda_event)
+        self._lib.check(lib.fdma_fwd(ctypes.byref(self.fp), st), "fdma_fwd")
+        if ev is not None:
+            lib.fdma_time_next_kernel(ev[2].cuda_event, ev[3].cuda_event)
+        self._lib.check(lib.fdma_bwd(ctypes.byref(self.bp), st), "fdma_bwd")
+        for fn, prm in self.post:
+            self._lib.check(fn(ctypes.byref(prm), st), "scatter")
+
+
+def time_steps(step, steps: int, stream, barrier, sampler=None):
+    """K steps between two events on the launching stream, barrier + synchronize on both sides; per-step events
+    around the forward and the backward attention kernels. Returns (total ms, mean fwd kernel ms, mean bwd kernel ms,
+    clocks)."""
+    kernel_events = []
+    for _ in range(steps):
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        for e in evs:
+            e.record(stream)  # materialises the underlying cudaEvent_t
+        kernel_events.append(evs)
+    barrier()
+    if sampler is not None:
+        sampler.mark()
+    t_start, t_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t_start.record(stream)
+    for i in range(steps):
+        step(kernel_events[i])
+    t_stop.record(stream)
+    barrier()
+    clocks = sampler.stop() if sampler is not None else None
+    fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in kernel_events)
+    bwd_ms = statistics.mean(e[2].elapsed_time(e[3]) for e in kernel_events)
+    return t_start.elapsed_time(t_stop), fwd_ms, bwd_ms, clocks
+
+
 def run_ours(args, rank: int, world: int, local_rank: int):
     import torch.distributed as dist
 
@@ -216,44 +361,17 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     torch.cuda.set_device(dev)
     lib = _lib.load()
     B = args.batch_per_gpu
+    compact = args.compaction == "auto"
+    iface.set_compaction(args.compaction)
     # seeded synthetic inputs: Q, K, V, bias, dOut ~ N(0,1) drawn in fp32 then cast to bf16; seed differs per rank
     g = torch.Generator(device=dev).manual_seed(1234 + rank)
     rnd = lambda *shape: torch.randn(shape, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
     q, k, v = rnd(B, S, HQ, D), rnd(B, S, HKV, D), rnd(B, S, HKV, D)
     bias, dout = rnd(B, HKV, 1, S), rnd(B, S, HQ, D)
     mask = create_mask(bias, None, B, S, S, WINDOW, torch.finfo(torch.bfloat16).min)
-    flops = count_flops(mask.cpu(), B, S, S, HQ, HKV, D, True)  # on the host: keeps the launch list clean
-
-    out = torch.empty_like(q)
-    lse = torch.empty((B, HQ, S), dtype=torch.float32, device=dev)
-    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-    dbias = torch.empty_like(bias)
-    fp = _lib.FwdParams()
-    iface._fill_fwd(fp, q, k, v, mask, bias, out, lse, D ** -0.5, True)
-    bp = _lib.BwdParams()
-    iface._fill_fwd(bp.f, q, k, v, mask, bias, out, lse, D ** -0.5, True)
-    bp.dout = dout.data_ptr()
-    bp.do_batch_stride, bp.do_row_stride, bp.do_head_stride = iface._bsh(dout)
-    bp.dq, bp.dk, bp.dv, bp.dbias = dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dbias.data_ptr()
-    bp.dq_batch_stride, bp.dq_row_stride, bp.dq_head_stride = iface._bsh(dq)
-    bp.dk_batch_stride, bp.dk_row_stride, bp.dk_head_stride = iface._bsh(dk)
-    bp.dv_batch_stride, bp.dv_row_stride, bp.dv_head_stride = iface._bsh(dv)
-    bp.dbias_batch_stride, bp.dbias_head_stride, bp.dbias_row_stride = dbias.stride()[:3]
-    bp.dbias_b, bp.dbias_h, bp.dbias_rows, bp.dbias_keys = dbias.shape
-    ws_f = lib.fdma_fwd_workspace_bytes(ctypes.byref(fp))
-    ws_b = lib.fdma_bwd_workspace_bytes(ctypes.byref(bp))
-    ws = torch.empty(max(ws_f, ws_b, 1), dtype=torch.uint8, device=dev)
-    fp.workspace, fp.workspace_bytes = ws.data_ptr(), ws_f
-    bp.f.workspace, bp.f.workspace_bytes = ws.data_ptr(), ws_b
+    mask_host = mask.cpu()
+    flops = count_flops(mask_host, B, S, S, HQ, HKV, D, True, compact)  # on the host: keeps the launch list clean
     stream = torch.cuda.current_stream(dev)
-
-    def step(ev=None):
-        if ev is not None:
-            lib.fdma_time_next_kernel(ev[0].cuda_event, ev[1].cuda_event)
-        _lib.check(lib.fdma_fwd(ctypes.byref(fp), stream.cuda_stream), "fdma_fwd")
-        if ev is not None:
-            lib.fdma_time_next_kernel(ev[2].cuda_event, ev[3].cuda_event)
-        _lib.check(lib.fdma_bwd(ctypes.byref(bp), stream.cuda_stream), "fdma_bwd")
 
     def barrier():
         if world > 1:
@@ -261,30 +379,36 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         torch.cuda.synchronize(dev)
 
     # ---- device-resident timing ----
-    for _ in range(args.warmup):
-        step()
-    kernel_events = []
-    for _ in range(args.steps):
-        evs = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
-        for e in evs:
-            e.record(stream)  # materialises the underlying cudaEvent_t
-        kernel_events.append(evs)
-    barrier()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
+    step = AttentionStep(lib, dev, q, k, v, mask, bias, dout, compact)
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler is not None:
         sampler.start()
-    t_start, t_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    t_start.record(stream)
-    for i in range(args.steps):
-        step(kernel_events[i])
-    t_stop.record(stream)
-    barrier()
-    clocks = sampler.stop() if rank == 0 else None
-    ms_total = t_start.elapsed_time(t_stop)
-    fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in kernel_events)
-    bwd_ms = statistics.mean(e[2].elapsed_time(e[3]) for e in kernel_events)
+    # warm-up: at least W steps, and at least half a second of load so that clocks and the sampler have settled
+    t_w = time.time()
+    n_w = 0
+    while n_w < args.warmup or time.time() - t_w < args.min_warmup_seconds:
+        step()
+        n_w += 1
+        if n_w % 8 == 0:
+            torch.cuda.synchronize(dev)
+    ms_total, fwd_ms, bwd_ms, clocks = time_steps(step, args.steps, stream, barrier, sampler)
     _lib.check(lib.fdma_last_kernel_status(stream.cuda_stream, None), "kernel status")
+    out, dq, dk, dv, dbias = step.out, step.dq, step.dk, step.dv, step.dbias
+
+    # ---- the same workload over the full key range (tile skipping only), for comparison ----
+    tile = None
+    if compact and not args.no_tile_path:
+        tstep = AttentionStep(lib, dev, q, k, v, mask, bias, dout, False)
+        for _ in range(3):
+            tstep()
+        t_steps = max(1, min(args.steps, 5))
+        t_ms, t_fwd, t_bwd, _ = time_steps(tstep, t_steps, stream, barrier)
+        t_fl = count_flops(mask_host, B, S, S, HQ, HKV, D, True, False)
+        tile = {"ms_per_step": t_ms / t_steps, "fwd_kernel_ms": t_fwd, "bwd_kernel_ms": t_bwd,
+                "tflops_on_its_kept_tiles": t_fl["total"] / (t_ms / t_steps * 1e-3) / 1e12,
+                "note": "per GPU, rank 0; fdma_fwd + fdma_bwd over all Sk keys, skipping tiles without a kept key"}
+        _lib.check(lib.fdma_last_kernel_status(stream.cuda_stream, None), "kernel status")
+        del tstep
 
     # ---- end to end through the public API with pinned host buffers ----
     host_in = {n: t.detach().cpu().pin_memory() for n, t in (("q", q), ("k", k), ("v", v), ("bias", bias),
@@ -335,18 +459,21 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     value = tot / (ms_per_step * 1e-3) / 1e12
     peak, peak_src = load_peaks()
     bwd_tflops = (bwd_fl / world) / (bwd_ms * 1e-3) / 1e12  # per launch, per GPU
-    cpu = cpu_sample(1, 1) if world == 1 and not args.no_cpu else None
+    cpu = cpu_sample(1, 1, compact) if world == 1 and not args.no_cpu else None
     line = {
         "metric": "fwd+bwd TFLOP/s on kept blocks", "value": value, "unit": "TFLOP/s", "n_gpus": world,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "steps": args.steps, "warmup": args.warmup, "warmup_steps_run": n_w, "ms_per_step": ms_per_step,
+        "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": WORKLOAD, "global_batch": B * world, "seq_len": S, "window": WINDOW,
                    "parallelism": f"(batch x kv-head) units sharded over {world} GPU(s), no collective",
                    "l2": "inputs larger than L2 (Q alone is 256 MiB per batch element)",
+                   "key_compaction": args.compaction,
+                   "flops": ("tiles of the gathered kept keys that the kernels process" if compact
+                             else "tiles of the full key range that hold a kept key"),
                    "tiles": {"fwd": list(FWD_TILE), "bwd": list(BWD_TILE)}},
         "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
         "tflops_canonical_128x128_tiles": canon / (ms_per_step * 1e-3) / 1e12,
-        "tflops_causal_dense": dense / (ms_per_step * 1e-3) / 1e12,
         "utilisation_of_nominal_2250": value / world / NOMINAL_TFLOPS,
         "roofline": {"bound": "tensor", "kernel": "bwd_kernel", "achieved": bwd_tflops, "peak": peak,
                      "unit": "TFLOP/s", "frac": bwd_tflops / peak, "peak_source": "of " + peak_src,
@@ -354,9 +481,11 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "e2e": {"value": tot / (e2e_ms * 1e-3) / 1e12 if e2e_ms == e2e_ms else None, "unit": "TFLOP/s",
                 "ms_per_step": e2e_ms if e2e_ms == e2e_ms else None,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "gpu_launches": args.steps * 4,  # fwd_kernel + bwd_prep_kernel + bwd_kernel + bwd_convert_dq_kernel
+        "gpu_launches": args.steps * step.launches,
         "clocks": clocks,
     }
+    if tile is not None:
+        line["tile_path"] = tile
     if cpu is not None:
         line["cpu_baseline"] = {k_: cpu[k_] for k_ in ("value", "unit", "cores", "kind", "sample")}
     print(json.dumps(line), flush=True)
@@ -429,6 +558,11 @@ def main():
     ap.add_argument("--workload", default="sharded", choices=["sharded", "ring"],
                     help="sharded = the headline benchmark; ring = single long sequence over a KV ring (needs >= 2 ranks)")
     ap.add_argument("--ring-seq-len", type=int, default=131072)
+    ap.add_argument("--compaction", default="auto", choices=["auto", "off"],
+                    help="auto = the library's default route for this mask (kept keys gathered first); off = full key range")
+    ap.add_argument("--no-tile-path", action="store_true", help="skip the full-key-range comparison leg")
+    ap.add_argument("--min-warmup-seconds", type=float, default=0.5,
+                    help="warm-up runs at least this long (0 for profiler captures, where launch counts must be fixed)")
     args = ap.parse_args()
     if args.impl == "ours":
         args.warmup = max(args.warmup, 3)

@@ -95,33 +95,38 @@ struct SmemB {
   static constexpr int kAlloc = kTotal + 1024;
 };
 
-// D = rowsum(dO o O), LSE in log2 units; rows [Sq, Sq_r) are padding (+inf / 0). One warp per (b, h, row).
+// D = rowsum(dO o O), LSE in log2 units; rows [Sq, Sq_r) are padding (+inf / 0). Head dim 128: sixteen lanes hold
+// one row (16 B each), a warp covers eight consecutive query rows of one (b, h) with all loads issued up front.
 template <bool kBf16>
-__global__ void bwd_prep_kernel(const void* __restrict__ out, const void* __restrict__ dout,
-                                const float* __restrict__ lse, float* __restrict__ lse2, float* __restrict__ dsum,
-                                int B, int H, int Sq, int Sq_r, int d, int64_t ob, int64_t orow, int64_t oh,
-                                int64_t gb, int64_t grow, int64_t gh) {
-  const int lane = threadIdx.x & 31;
+__global__ void __launch_bounds__(256) bwd_prep_kernel(const void* __restrict__ out, const void* __restrict__ dout,
+                                                        const float* __restrict__ lse, float* __restrict__ lse2,
+                                                        float* __restrict__ dsum, int B, int H, int Sq, int Sq_r,
+                                                        int64_t ob, int64_t orow, int64_t oh, int64_t gb, int64_t grow,
+                                                        int64_t gh) {
+  const int lane = threadIdx.x & 31, sub = lane >> 4, l16 = lane & 15;
   const int64_t w = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
-  const int64_t total = static_cast<int64_t>(B) * H * Sq_r;
+  const int groups = Sq_r / 8;
+  const int64_t total = static_cast<int64_t>(B) * H * groups;
   if (w >= total) return;
-  const int q = static_cast<int>(w % Sq_r);
-  const int h = static_cast<int>((w / Sq_r) % H);
-  const int b = static_cast<int>(w / (static_cast<int64_t>(Sq_r) * H));
-  if (q >= Sq) {
-    if (lane == 0) {
-      lse2[w] = CUDART_INF_F;
-      dsum[w] = 0.f;
+  const int q0 = static_cast<int>(w % groups) * 8;
+  const int h = static_cast<int>((w / groups) % H);
+  const int b = static_cast<int>(w / (static_cast<int64_t>(groups) * H));
+  const uint16_t* o = reinterpret_cast<const uint16_t*>(out) + b * ob + h * oh + l16 * 8;
+  const uint16_t* g = reinterpret_cast<const uint16_t*>(dout) + b * gb + h * gh + l16 * 8;
+  uint4 a[4], c[4];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int q = q0 + u * 2 + sub;
+    a[u] = c[u] = make_uint4(0, 0, 0, 0);
+    if (q < Sq) {
+      a[u] = *reinterpret_cast<const uint4*>(o + static_cast<int64_t>(q) * orow);
+      c[u] = *reinterpret_cast<const uint4*>(g + static_cast<int64_t>(q) * grow);
     }
-    return;
   }
-  const uint16_t* o = reinterpret_cast<const uint16_t*>(out) + b * ob + q * orow + h * oh;
-  const uint16_t* g = reinterpret_cast<const uint16_t*>(dout) + b * gb + q * grow + h * gh;
-  float acc = 0.f;
-  for (int i = lane * 8; i < d; i += 256) {
-    const uint4 a = *reinterpret_cast<const uint4*>(o + i);
-    const uint4 c = *reinterpret_cast<const uint4*>(g + i);
-    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, cw[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const uint32_t aw[4] = {a[u].x, a[u].y, a[u].z, a[u].w}, cw[4] = {c[u].x, c[u].y, c[u].z, c[u].w};
+    float acc = 0.f;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       float a0, a1, c0, c1;
@@ -136,13 +141,19 @@ __global__ void bwd_prep_kernel(const void* __restrict__ out, const void* __rest
       acc = fmaf(a0, c0, acc);
       acc = fmaf(a1, c1, acc);
     }
-  }
 #pragma unroll
-  for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
-  if (lane == 0) {
-    const float l = lse[(static_cast<int64_t>(b) * H + h) * Sq + q];
-    lse2[w] = l * kLog2e;  // +inf stays +inf
-    dsum[w] = acc;
+    for (int sft = 8; sft > 0; sft >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, sft);
+    const int q = q0 + u * 2 + sub;
+    if (l16 == 0) {
+      const int64_t idx = (static_cast<int64_t>(b) * H + h) * Sq_r + q;
+      if (q < Sq) {
+        lse2[idx] = lse[(static_cast<int64_t>(b) * H + h) * Sq + q] * kLog2e;
+        dsum[idx] = acc;
+      } else {
+        lse2[idx] = CUDART_INF_F;
+        dsum[idx] = 0.f;
+      }
+    }
   }
 }
 
@@ -945,10 +956,10 @@ int launch(const fdma_bwd_params& bp, const BwdPlan& pl, cudaStream_t stream) {
   cudaError_t e = cudaMemsetAsync(dq_acc, 0, dq_bytes, stream);
   if (e != cudaSuccess) return static_cast<int>(e);
   {
-    const int64_t warps = static_cast<int64_t>(p.b) * p.h * pl.sq_r;
+    const int64_t warps = static_cast<int64_t>(p.b) * p.h * (pl.sq_r / 8);
     const int64_t blocks = (warps * 32 + 255) / 256;
     bwd_prep_kernel<kBf16><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
-        p.out, bp.dout, p.lse, lse2, dsum, p.b, p.h, p.seqlen_q, pl.sq_r, p.d, p.o_batch_stride, p.o_row_stride,
+        p.out, bp.dout, p.lse, lse2, dsum, p.b, p.h, p.seqlen_q, pl.sq_r, p.o_batch_stride, p.o_row_stride,
         p.o_head_stride, bp.do_batch_stride, bp.do_row_stride, bp.do_head_stride);
     e = cudaGetLastError();
     if (e != cudaSuccess) return static_cast<int>(e);

@@ -8,6 +8,7 @@
 // The reference's CUDA backend has no such path; its Triton prototype gathers keys by top-k index
 // (flash_sparse_attn/flash_dmattn_triton.py:49-211). All three kernels are plain HBM-bound copies.
 #include <cstdint>
+#include <utility>
 #include <cuda_runtime.h>
 
 #include "fdma_internal.h"
@@ -152,6 +153,32 @@ bool all16(const fdma_rows_params& p, int eb) {
   return a16(p.src) && a16(p.dst) && (static_cast<int64_t>(p.row_elems) * eb) % 16 == 0;
 }
 
+// True when the destination's elements form one contiguous block (any order of the dimensions), so that the zero
+// fill of a scatter can be a single memset.
+bool dst_is_dense(const fdma_rows_params& p) {
+  const int64_t ext_all[4] = {p.b, p.rows_full, p.heads, p.row_elems};
+  const int64_t str_all[4] = {p.dst_batch_stride, p.dst_row_stride, p.dst_head_stride, 1};
+  int64_t ext[4], str[4];
+  int n = 0;
+  for (int i = 0; i < 4; ++i)
+    if (ext_all[i] != 1) {  // a dimension of extent 1 is never stepped over
+      ext[n] = ext_all[i];
+      str[n] = str_all[i];
+      ++n;
+    }
+  for (int i = 1; i < n; ++i)  // insertion sort by stride
+    for (int j = i; j > 0 && str[j] < str[j - 1]; --j) {
+      std::swap(ext[j], ext[j - 1]);
+      std::swap(str[j], str[j - 1]);
+    }
+  int64_t expect = 1;
+  for (int i = 0; i < n; ++i) {
+    if (str[i] != expect) return false;
+    expect *= ext[i];
+  }
+  return true;
+}
+
 int check_rows(const fdma_rows_params* p) {
   if (!p || !p->src || !p->dst || !p->key_pos) return FDMA_ERR_BAD_ARG;
   if (p->b <= 0 || p->heads <= 0 || p->h_pos <= 0 || p->rows_full <= 0 || p->capacity <= 0 || p->row_elems <= 0)
@@ -208,10 +235,16 @@ extern "C" int fdma_scatter_rows(const fdma_rows_params* p, void* stream) {
   const RowsArgs a = make_args(*p);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool v16 = all16(*p, 2);
-  const int64_t zwarps = static_cast<int64_t>(p->b) * p->rows_full * p->heads;
-  const unsigned zblocks = static_cast<unsigned>((zwarps * 32 + 255) / 256);
-  if (v16) zero_rows_kernel<16><<<zblocks, 256, 0, s>>>(a.dst, a.dst_sb, a.dst_sr, a.dst_sh, a.b, a.rows_full, a.heads, a.row_bytes);
-  else zero_rows_kernel<2><<<zblocks, 256, 0, s>>>(a.dst, a.dst_sb, a.dst_sr, a.dst_sh, a.b, a.rows_full, a.heads, a.row_bytes);
+  if (dst_is_dense(*p)) {
+    const size_t bytes = static_cast<size_t>(p->b) * p->rows_full * p->heads * a.row_bytes;
+    const cudaError_t e = cudaMemsetAsync(a.dst, 0, bytes, s);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  } else {
+    const int64_t zwarps = static_cast<int64_t>(p->b) * p->rows_full * p->heads;
+    const unsigned zblocks = static_cast<unsigned>((zwarps * 32 + 255) / 256);
+    if (v16) zero_rows_kernel<16><<<zblocks, 256, 0, s>>>(a.dst, a.dst_sb, a.dst_sr, a.dst_sh, a.b, a.rows_full, a.heads, a.row_bytes);
+    else zero_rows_kernel<2><<<zblocks, 256, 0, s>>>(a.dst, a.dst_sb, a.dst_sr, a.dst_sh, a.b, a.rows_full, a.heads, a.row_bytes);
+  }
   const int64_t warps = static_cast<int64_t>(p->b) * p->capacity * p->heads;
   const unsigned blocks = static_cast<unsigned>((warps * 32 + 255) / 256);
   if (v16) rows_kernel<true, 16><<<blocks, 256, 0, s>>>(a);

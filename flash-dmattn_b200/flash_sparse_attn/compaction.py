@@ -49,7 +49,8 @@ def _row_mask(attn_mask: torch.Tensor, B: int, Hk: int, Sk: int) -> torch.Tensor
     return m if m.stride(-1) == 1 else m.contiguous()
 
 
-def _rows_call(fn, src, dst, key_pos, b, heads, rows_full, cap, row_elems, src_strides, dst_strides, device):
+def _rows_params(src, dst, key_pos, b, heads, rows_full, cap, row_elems, src_strides, dst_strides):
+    """fdma_rows_params for a gather (src full, dst compact) or a scatter (src compact, dst full)."""
     rp = _lib.RowsParams()
     rp.src, rp.dst, rp.key_pos = src.data_ptr(), dst.data_ptr(), key_pos.data_ptr()
     rp.key_pos_batch_stride = 0 if key_pos.shape[0] == 1 else key_pos.stride(0)
@@ -58,6 +59,11 @@ def _rows_call(fn, src, dst, key_pos, b, heads, rows_full, cap, row_elems, src_s
     rp.dst_batch_stride, rp.dst_row_stride, rp.dst_head_stride = dst_strides
     rp.b, rp.heads, rp.h_pos, rp.rows_full, rp.capacity, rp.row_elems = b, heads, key_pos.shape[1], rows_full, cap, row_elems
     rp.dtype = _dtype_code(src)
+    return rp
+
+
+def _rows_call(fn, src, dst, key_pos, b, heads, rows_full, cap, row_elems, src_strides, dst_strides, device):
+    rp = _rows_params(src, dst, key_pos, b, heads, rows_full, cap, row_elems, src_strides, dst_strides)
     _lib.check(fn(ctypes.byref(rp), _stream_ptr(device)), fn.__name__)
 
 
