@@ -140,8 +140,56 @@ def test_compact_matches_tile_path_full_window(dev):
     q, k, v, bias, dout = oracle.make_inputs(B, S, S, H, Hk, d, (B, Hk, 1, S), seed=2, dtype=dtype)
     q, k, v, bias, dout = (t.to(dev) for t in (q, k, v, bias, dout))
     mask = create_mask(bias, None, B, S, S, W, torch.finfo(dtype).min)
-    a = flash_sparse_attn_func(q, k, v, mask, bias, is_causal=True)
+    from flash_sparse_attn import flash_sparse_attn_interface as iface
+
+    iface.set_compaction("off")
+    try:
+        a = flash_sparse_attn_func(q, k, v, mask, bias, is_causal=True)
+    finally:
+        iface.set_compaction("auto")
     b = flash_sparse_attn_compact_func(q, k, v, mask, bias, is_causal=True, capacity=W)
     torch.cuda.synchronize()
     _kernel_status_ok()
     assert (a.float() - b.float()).abs().max().item() <= 2e-2
+
+
+def test_default_route_selection(dev):
+    """flash_sparse_attn_func picks the gathered-keys route from the mask's shape: the bound left by create_mask
+    sizes the gather without a read-back, an in-place edit of the mask voids that bound (counts are read back
+    instead), a mostly-kept mask and a per-query mask stay on the full-range route."""
+    from flash_sparse_attn import flash_sparse_attn_func
+    from flash_sparse_attn import flash_sparse_attn_interface as iface
+    from flash_sparse_attn.utils.mask import create_mask
+
+    B, S, H, Hk, d, W = 1, 1024, 4, 2, 128, 256
+    dtype = torch.bfloat16
+    q, k, v, bias, dout = oracle.make_inputs(B, S, S, H, Hk, d, (B, Hk, 1, S), seed=4, dtype=dtype)
+    qd, kd, vd, bd = (t.to(dev) for t in (q, k, v, bias))
+    mask = create_mask(bd, None, B, S, S, W, torch.finfo(dtype).min)
+    assert mask._fdma_keep_bound == (W, mask._version)
+    assert iface._compaction_capacity(qd, kd, mask, bd, None, None) == 256
+    ref = oracle.attention_forward(q, k, v, mask.cpu(), bias, None, True)[0]
+    check("out", flash_sparse_attn_func(qd, kd, vd, mask, bd, is_causal=True).cpu(), ref, dtype)
+
+    # in-place edit: 100 more keys kept than the stale bound says
+    extra = torch.zeros_like(mask)
+    extra[..., :400] = True
+    mask.logical_or_(extra)
+    kept = int(mask.sum(-1).max())
+    assert kept > W
+    assert iface._compaction_capacity(qd, kd, mask, bd, None, None) == (kept + 127) // 128 * 128
+    ref = oracle.attention_forward(q, k, v, mask.cpu(), bias, None, True)[0]
+    check("out", flash_sparse_attn_func(qd, kd, vd, mask, bd, is_causal=True).cpu(), ref, dtype)
+
+    dense = torch.ones(B, Hk, 1, S, dtype=torch.bool, device=dev)
+    assert iface._compaction_capacity(qd, kd, dense, bd, None, None) is None
+    perq = torch.ones(B, Hk, S, S, dtype=torch.bool, device=dev)
+    assert iface._compaction_capacity(qd, kd, perq, bd, None, None) is None
+    iface.set_compaction("off")
+    try:
+        assert iface._compaction_capacity(qd, kd, create_mask(bd, None, B, S, S, W, torch.finfo(dtype).min), bd,
+                                          None, None) is None
+    finally:
+        iface.set_compaction("auto")
+    torch.cuda.synchronize()
+    _kernel_status_ok()
