@@ -93,6 +93,13 @@ def count_flops(mask: torch.Tensor, B: int, Sq: int, Sk: int, H: int, Hk: int, d
             kept_f += G * kept_tiles_rowbcast(row, Sq, Sk, *FWD_TILE, causal, compact)
             kept_b += G * kept_tiles_rowbcast(row, Sq, Sk, *BWD_TILE, causal, compact)
             kept_c += G * kept_tiles_rowbcast(row, Sq, Sk, 128, 128, causal, compact)
+    # element level: kept, causally visible (query, key) pairs
+    nnz = 0
+    for b in range(B):
+        for hk in range(Hk):
+            pos = torch.nonzero(mask[b, hk, 0, :Sk]).flatten()
+            vis = (Sq - torch.clamp(pos - (Sk - Sq), min=0)) if causal else torch.full_like(pos, Sq)
+            nnz += G * int(torch.clamp(vis, min=0).sum().item())
     mt, nt = (Sq + 127) // 128, (Sk + 127) // 128
     causal_tiles = sum(min(nt, max(0, ((i + 1) * 128 + Sk - Sq + 127) // 128)) for i in range(mt)) if causal else mt * nt
     fwd = 4 * d * FWD_TILE[0] * FWD_TILE[1] * kept_f
@@ -101,6 +108,7 @@ def count_flops(mask: torch.Tensor, B: int, Sq: int, Sk: int, H: int, Hk: int, d
         "fwd": fwd, "bwd": bwd, "total": fwd + bwd,
         "canonical_128x128": 14 * d * 128 * 128 * kept_c,
         "causal_dense": 14 * d * 128 * 128 * causal_tiles * B * H,
+        "element_level": 14 * d * nnz,
     }
 
 
@@ -449,12 +457,13 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         dist.all_reduce(vals, op=dist.ReduceOp.MAX)
     ms_total, e2e_ms, fwd_ms, bwd_ms = vals.tolist()
     flop_sum = torch.tensor([float(flops["total"]), float(flops["canonical_128x128"]), float(flops["causal_dense"]),
-                             float(flops["bwd"]), float(flops["fwd"])], dtype=torch.float64, device=dev)
+                             float(flops["bwd"]), float(flops["fwd"]), float(flops["element_level"])],
+                            dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(flop_sum, op=dist.ReduceOp.SUM)
     if rank != 0:
         return
-    tot, canon, dense, bwd_fl, fwd_fl = flop_sum.tolist()
+    tot, canon, dense, bwd_fl, fwd_fl, elem_fl = flop_sum.tolist()
     ms_per_step = ms_total / args.steps
     value = tot / (ms_per_step * 1e-3) / 1e12
     peak, peak_src = load_peaks()
@@ -474,6 +483,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                    "tiles": {"fwd": list(FWD_TILE), "bwd": list(BWD_TILE)}},
         "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
         "tflops_canonical_128x128_tiles": canon / (ms_per_step * 1e-3) / 1e12,
+        "tflops_element_level": elem_fl / (ms_per_step * 1e-3) / 1e12,
+        "tflops_causal_dense_equivalent": dense / (ms_per_step * 1e-3) / 1e12,
         "utilisation_of_nominal_2250": value / world / NOMINAL_TFLOPS,
         "roofline": {"bound": "tensor", "kernel": "bwd_kernel", "achieved": bwd_tflops, "peak": peak,
                      "unit": "TFLOP/s", "frac": bwd_tflops / peak, "peak_source": "of " + peak_src,
