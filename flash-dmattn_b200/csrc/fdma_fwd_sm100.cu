@@ -40,6 +40,10 @@ constexpr int kThreads = 384;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;
+#ifndef FDMA_POLY_PAIRS
+#define FDMA_POLY_PAIRS 0x0000u
+#endif
+constexpr unsigned kPolyPairs = FDMA_POLY_PAIRS;  // bit i: pair i of every 16 pairs uses exp2_poly2
 
 // Codes stored in the status word when a wait gives up.
 enum WaitCode {
@@ -567,7 +571,8 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const float2 x = __fadd2_rn(s2[c * 16 + i], nm2);
-            const float2 pp = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+            // a fixed subset of the pairs is exponentiated on the FMA pipe to unload the transcendental unit
+            const float2 pp = ((kPolyPairs >> i) & 1) ? exp2_poly2(x) : make_float2(fast_exp2(x.x), fast_exp2(x.y));
             ls[i & 3] = __fadd2_rn(ls[i & 3], pp);
             pk[i] = pack_16x2<kBf16>(pp.x, pp.y);
           }
@@ -597,7 +602,8 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
     tc_fence_after_sync();
     if (ok) {
       const bool in_range = qrow < Sq;  // TMEM loads below are warp-collective: every lane runs them
-      const bool alive = scnt > 0 && l > 0.f;
+      // m_ref stays -inf iff every score of the row was masked (l can then hold 2^-125 terms of exp2_poly2)
+      const bool alive = scnt > 0 && l > 0.f && m_ref != -CUDART_INF_F;
       const float inv = alive ? 1.f / l : 0.f;
       unsigned char* orow = reinterpret_cast<unsigned char*>(p.out) +
                             (b * p.o_batch_stride + static_cast<int64_t>(qclamp) * p.o_row_stride +

@@ -316,6 +316,23 @@ __device__ __forceinline__ float exp2_if(float x, uint32_t on) {
   return y;
 }
 // max of three (one instruction on sm_100)
+// 2^x for a pair of values on the FMA pipe instead of the transcendental unit: round-to-nearest split x = j + f with
+// f in [-0.5, 0.5], cubic minimax polynomial for 2^f (relative error 7.5e-5, far below one bf16 rounding), exponent
+// added through the integer bits. x is clamped at -125, so a masked (-inf) score yields 2^-125, not 0; callers must
+// not rely on an exact zero. Valid for x < 100.
+__device__ __forceinline__ float2 exp2_poly2(float2 x) {
+  x.x = fmaxf(x.x, -125.f);
+  x.y = fmaxf(x.y, -125.f);
+  const float2 t = __fadd2_rn(x, make_float2(12582912.f, 12582912.f));  // 1.5 * 2^23: integer part in the low bits
+  const float2 j = __fadd2_rn(t, make_float2(-12582912.f, -12582912.f));
+  const float2 f = __ffma2_rn(j, make_float2(-1.f, -1.f), x);
+  float2 p = __ffma2_rn(f, make_float2(0.055171460f, 0.055171460f), make_float2(0.24261086f, 0.24261086f));
+  p = __ffma2_rn(p, f, make_float2(0.69326097f, 0.69326097f));
+  p = __ffma2_rn(p, f, make_float2(0.99992812f, 0.99992812f));
+  return make_float2(__uint_as_float(__float_as_uint(p.x) + (__float_as_uint(t.x) << 23)),
+                     __uint_as_float(__float_as_uint(p.y) + (__float_as_uint(t.y) << 23)));
+}
+
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
