@@ -22,7 +22,6 @@
 #include <math_constants.h>
 
 #include <algorithm>
-#include <cstdlib>
 
 #include "fdma_internal.h"
 #include "fdma_ptx.cuh"
@@ -870,7 +869,6 @@ struct BwdPlan {
 // tiles evens out; every split keeps at least 32 steps.
 int pick_nsplit(const fdma_fwd_params& p) {
   const int64_t ctas = static_cast<int64_t>((p.seqlen_k + kBN - 1) / kBN) * p.h_k * p.b;
-  if (const char* e = getenv("FDMA_BWD_SPLIT_TUNE")) return std::max(1, atoi(e));
   if (ctas >= 2 * 148) return 1;
   const int64_t steps = static_cast<int64_t>((p.seqlen_q + kBM - 1) / kBM) * (p.h / p.h_k);
   const int64_t want = (8 * 148 + ctas - 1) / ctas;

@@ -301,20 +301,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// exp2(x) if `on` is non-zero, else 0 -- as a PREDICATED ex2, so a switched-off element costs an issue slot but no
-// time on the transcendental unit (a select after an unconditional ex2 would not save that).
-__device__ __forceinline__ float exp2_if(float x, uint32_t on) {
-  float y;
-  asm("{\n\t"
-      ".reg .pred q;\n\t"
-      "setp.ne.u32 q, %2, 0;\n\t"
-      "mov.f32 %0, 0f00000000;\n\t"
-      "@q ex2.approx.ftz.f32 %0, %1;\n\t"
-      "}\n"
-      : "=f"(y)
-      : "f"(x), "r"(on));
-  return y;
-}
 // max of three (one instruction on sm_100)
 // 2^x for a pair of values on the FMA pipe instead of the transcendental unit: round-to-nearest split x = j + f with
 // f in [-0.5, 0.5], cubic minimax polynomial for 2^f (relative error 7.5e-5, far below one bf16 rounding), exponent

@@ -46,6 +46,8 @@ def _compaction_capacity(query, key, attn_mask, attn_bias, softcap, return_attn_
     quarters of the keys is left to the tile-skipping path."""
     if _compaction != "auto" or attn_mask is None or softcap or return_attn_probs:
         return None
+    if torch.compiler.is_compiling():  # traced graphs keep to the registered custom ops
+        return None
     if query.dim() != 4 or key.dim() != 4 or attn_mask.dim() != 4 or attn_mask.dtype != torch.bool:
         return None
     B, Sq, H, d = query.shape
