@@ -552,6 +552,13 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
                                               hb * p.bias_head_stride + key
                                         : nullptr;
           const uint8_t* mcol = p.mask ? p.mask + b * p.mask_batch_stride + hm * p.mask_head_stride + key : nullptr;
+          if (g == 0 && m + 1 < M64) {
+            // next query tile's bias / mask bytes of this warp's 32 keys: lane j asks L2 for row j
+            const int64_t qn = min((m + 1) * kBM + half * 32 + lane, Sq - 1);
+            const int wkey = min(n * kBN + (warp & 3) * 32, Sk - 1) - key;  // warp's first key, relative to this lane's
+            if (bcol) prefetch_l2(bcol + wkey + qn * p.bias_row_stride);
+            if (mcol) prefetch_l2(mcol + wkey + qn * p.mask_row_stride);
+          }
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             float two[2];

@@ -149,8 +149,18 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
   volatile int* s_abort = reinterpret_cast<volatile int*>(smem + L::kMiscOff + 4);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int mblk = gridDim.x - 1 - blockIdx.x;  // heaviest (latest) query blocks first under causal masking
-  const int h = blockIdx.y, b = blockIdx.z;
+  // Query block and head of this CTA. Heaviest (latest) query blocks first under causal masking. Per-query masks
+  // and biases are read from global memory by every head that shares them, so in that mode the heads of one kv
+  // group take consecutive CTA indices for the same query block and meet their shared tiles in L2.
+  int mblk = gridDim.x - 1 - blockIdx.x;
+  int h = blockIdx.y;
+  if (!kBcast) {
+    const int G = p.h / p.h_k;
+    const int lin = blockIdx.x + gridDim.x * blockIdx.y;
+    h = (lin / (G * static_cast<int>(gridDim.x))) * G + lin % G;
+    mblk = gridDim.x - 1 - (lin / G) % gridDim.x;
+  }
+  const int b = blockIdx.z;
   const int hk = h / (p.h / p.h_k);
   const int hm = h / (p.h / p.h_mask);
   const int hb = h / (p.h / p.h_bias);
@@ -458,6 +468,18 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
         }
         const int kbase = j * kBN;
         const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
+        if (!kBcast) {
+          // this row's mask and bias bytes of the next tile it will process: into L2 while this tile is worked on
+          int jn = j + 1;
+          while (jn < nT && !(s_flags[jn] & (1 << t))) ++jn;
+          if (jn < nT) {
+            if (mrow) prefetch_l2(mrow + jn * kBN);
+            if (brow) {
+              prefetch_l2(brow + jn * kBN);
+              prefetch_l2(brow + jn * kBN + 64);
+            }
+          }
+        }
         // scores in log2 units with bias and mask folded in
         if (kBcast) {
           const float4* bm4 = reinterpret_cast<const float4*>(s_bm + slot * kBN);

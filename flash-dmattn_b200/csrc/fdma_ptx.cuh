@@ -301,6 +301,9 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ void prefetch_l2(const void* ptr) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr));
+}
 // max of three (one instruction on sm_100)
 // 2^x for a pair of values on the FMA pipe instead of the transcendental unit: round-to-nearest split x = j + f with
 // f in [-0.5, 0.5], cubic minimax polynomial for 2^f (relative error 7.5e-5, far below one bf16 rounding), exponent

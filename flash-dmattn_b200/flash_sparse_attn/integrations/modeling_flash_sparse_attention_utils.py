@@ -1,0 +1,80 @@
+"""Dense (no padding, no packing) branch of the reference's HuggingFace glue
+(flash_sparse_attn/integrations/modeling_flash_sparse_attention_utils.py:425-596): recast fp32 activations to the
+model's half-precision dtype (:321-339), build the top-`window_size` mask from the bias only when the key length
+exceeds the window (:570-583), and call `flash_sparse_attn_func`.
+
+The reference's two other branches -- a 2-D padding mask (unpad -> varlen kernel -> pad, :511-536) and packed
+sequences given by position ids or cu_seqlens (:538-565) -- end in its varlen kernels, which this package does not
+build; they raise NotImplementedError here instead of silently attending across examples.
+"""
+import os
+from typing import Optional
+
+import torch
+
+from ..flash_sparse_attn_interface import flash_sparse_attn_func
+from ..utils.mask import create_mask
+
+
+def fsa_peft_integration_check(q, k, v, bias, target_dtype: Optional[torch.dtype] = None):
+    """fp32 activations (PEFT keeps layer norms in fp32) go back to `target_dtype`; anything else passes through."""
+    if target_dtype is not None and q.dtype == torch.float32:
+        q, k, v = q.to(target_dtype), k.to(target_dtype), v.to(target_dtype)
+        bias = bias.to(target_dtype) if bias is not None else None
+    return q, k, v, bias
+
+
+def _is_packed_sequence(position_ids: Optional[torch.Tensor], batch_size: int) -> bool:
+    """Packed (padding-free) batches show up as one row of position ids that restarts from 0 somewhere
+    (reference :279-296)."""
+    if position_ids is None or position_ids.dim() != 2 or batch_size != 1 or position_ids.shape[1] < 2:
+        return False
+    expected = torch.arange(position_ids.shape[1], device=position_ids.device) + position_ids.min()
+    return not bool((position_ids[0] == expected).all())
+
+
+def _flash_sparse_attention_forward(
+    query_states: torch.Tensor,
+    key_states: torch.Tensor,
+    value_states: torch.Tensor,
+    attention_mask: Optional[torch.Tensor],
+    attention_bias: Optional[torch.Tensor],
+    query_length: int,
+    key_length: int,
+    is_causal: bool,
+    position_ids: Optional[torch.Tensor] = None,
+    softmax_scale: Optional[float] = None,
+    window_size: Optional[int] = None,
+    softcap: Optional[float] = None,
+    deterministic: Optional[bool] = None,
+    cu_seq_lens_q: Optional[torch.LongTensor] = None,
+    cu_seq_lens_k: Optional[torch.LongTensor] = None,
+    max_length_q: Optional[int] = None,
+    max_length_k: Optional[int] = None,
+    target_dtype: Optional[torch.dtype] = None,
+    implementation: Optional[str] = None,
+    **kwargs,
+):
+    """query/key/value (B, S, H, d). Returns (B, Sq, H, d). Same argument list as the reference function."""
+    if attention_mask is not None and attention_mask.dim() == 2 and attention_bias is not None:
+        raise ValueError("If shape of attention_mask is (batch_size, seq_len), attention_bias has to be None.")
+    if attention_mask is not None and attention_mask.dim() == 2:
+        raise NotImplementedError("2-D padding masks need the variable-length kernels, which are not built")
+    packed = all(x is not None for x in (cu_seq_lens_q, cu_seq_lens_k, max_length_q, max_length_k))
+    if packed or _is_packed_sequence(position_ids, query_states.size(0)):
+        raise NotImplementedError("packed sequences need the variable-length kernels, which are not built")
+
+    query_states, key_states, value_states, attention_bias = fsa_peft_integration_check(
+        query_states, key_states, value_states, attention_bias, target_dtype)
+    if deterministic is None:
+        deterministic = os.getenv("FLASH_SPARSE_ATTENTION_DETERMINISTIC", "0") == "1"
+
+    if attention_bias is not None and window_size is not None and key_length > window_size:
+        attention_mask = create_mask(
+            attention_bias, attention_mask, batch_size=query_states.size(0), query_len=query_length,
+            key_len=key_length, window_size=window_size, min_dtype=torch.finfo(attention_bias.dtype).min)
+    out = flash_sparse_attn_func(
+        query_states, key_states, value_states, attention_mask, attention_bias,
+        softmax_scale=softmax_scale, is_causal=is_causal and query_length != 1,
+        softcap=softcap, deterministic=deterministic)
+    return out[0] if isinstance(out, tuple) else out
