@@ -20,7 +20,7 @@ import torch
 from . import _lib
 from .flash_sparse_attn_interface import (_bsh, _check_inputs, _dtype_code, _fill_fwd, _stream_ptr, round_multiple)
 
-__all__ = ["CompactKeys", "compact_keys", "flash_sparse_attn_compact_func"]
+__all__ = ["CompactKeys", "compact_keys", "compact_forward", "compact_backward", "flash_sparse_attn_compact_func"]
 
 _TILE = 128
 
@@ -134,26 +134,84 @@ def _set_positions(p, ck: CompactKeys, seqlen_q: int):
     p.causal_shift = ck.seqlen_k - seqlen_q
 
 
+def compact_forward(q: torch.Tensor, ck: CompactKeys, softmax_scale: float, is_causal: bool):
+    """Forward over gathered keys: returns (out (B,Sq,H,d), lse (B,H,Sq) fp32)."""
+    lib = _lib.load()
+    _check_inputs(q, ck.key, ck.value, ck.mask, ck.bias)
+    B, Sq, H, d = q.shape
+    dev = q.device
+    with torch.cuda.device(dev):
+        out = torch.empty_like(q)
+        lse = torch.empty((B, H, Sq), dtype=torch.float32, device=dev)
+        p = _lib.FwdParams()
+        _fill_fwd(p, q, ck.key, ck.value, ck.mask, ck.bias, out, lse, softmax_scale, is_causal)
+        _set_positions(p, ck, Sq)
+        ws_bytes = lib.fdma_fwd_workspace_bytes(ctypes.byref(p))
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev) if ws_bytes else None
+        if ws is not None:
+            p.workspace, p.workspace_bytes = ws.data_ptr(), ws_bytes
+        _lib.check(lib.fdma_fwd(ctypes.byref(p), _stream_ptr(dev)), "fdma_fwd")
+    return out, lse
+
+
+def compact_backward(dout, q, ck: CompactKeys, out, lse, softmax_scale: float, is_causal: bool, k_shape,
+                     bias_shape=None):
+    """Backward over gathered keys, gradients scattered back to full shapes: returns dq, dk, dv (shape k_shape) and
+    dbias (shape bias_shape, or None). Dimensions the bias broadcast over are summed."""
+    lib = _lib.load()
+    k_c, v_c, mask_c, bias_c, key_pos, Sk = ck.key, ck.value, ck.mask, ck.bias, ck.key_pos, ck.seqlen_k
+    B, Sq, H, d = q.shape
+    Hk, cap = k_c.shape[2], k_c.shape[1]
+    dev = q.device
+    dout = dout if dout.stride(-1) == 1 else dout.contiguous()
+    with torch.cuda.device(dev):
+        dq = torch.empty_like(q)
+        dk_c, dv_c = torch.empty_like(k_c), torch.empty_like(v_c)
+        dbias_c = torch.empty_like(bias_c) if bias_c is not None else None
+        bp = _lib.BwdParams()
+        _fill_fwd(bp.f, q, k_c, v_c, mask_c, bias_c, out, lse, softmax_scale, is_causal)
+        _set_positions(bp.f, ck, Sq)
+        bp.dout = dout.data_ptr()
+        bp.do_batch_stride, bp.do_row_stride, bp.do_head_stride = _bsh(dout)
+        bp.dq, bp.dk, bp.dv = dq.data_ptr(), dk_c.data_ptr(), dv_c.data_ptr()
+        bp.dq_batch_stride, bp.dq_row_stride, bp.dq_head_stride = _bsh(dq)
+        bp.dk_batch_stride, bp.dk_row_stride, bp.dk_head_stride = _bsh(dk_c)
+        bp.dv_batch_stride, bp.dv_row_stride, bp.dv_head_stride = _bsh(dv_c)
+        if dbias_c is not None:
+            bp.dbias = dbias_c.data_ptr()
+            bp.dbias_batch_stride, bp.dbias_head_stride, bp.dbias_row_stride = dbias_c.stride()[:3]
+            bp.dbias_b, bp.dbias_h, bp.dbias_rows, bp.dbias_keys = dbias_c.shape
+        ws_bytes = lib.fdma_bwd_workspace_bytes(ctypes.byref(bp))
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev) if ws_bytes else None
+        if ws is not None:
+            bp.f.workspace, bp.f.workspace_bytes = ws.data_ptr(), ws_bytes
+        _lib.check(lib.fdma_bwd(ctypes.byref(bp), _stream_ptr(dev)), "fdma_bwd")
+        dk = torch.empty(k_shape, dtype=q.dtype, device=dev)
+        dv = torch.empty(k_shape, dtype=q.dtype, device=dev)
+        for src, dst in ((dk_c, dk), (dv_c, dv)):
+            _rows_call(lib.fdma_scatter_rows, src, dst, key_pos, B, Hk, Sk, cap, d, _bsh(src), _bsh(dst), dev)
+        dbias = None
+        if dbias_c is not None:
+            Bc, Hc = dbias_c.shape[0], dbias_c.shape[1]
+            full = torch.empty((Bc, Hc, 1, Sk), dtype=q.dtype, device=dev)
+            _rows_call(lib.fdma_scatter_rows, dbias_c, full, key_pos, Bc, Hc, Sk, cap, 1,
+                       (dbias_c.stride(0), 1, dbias_c.stride(1)), (full.stride(0), 1, full.stride(1)), dev)
+            # dimensions the bias broadcast over (and the compaction widened) are summed back
+            for dim in (0, 1, 3):
+                if bias_shape[dim] == 1 and full.shape[dim] != 1:
+                    full = full.sum(dim=dim, keepdim=True, dtype=torch.float32).to(q.dtype)
+            if bias_shape[3] > Sk:
+                full = torch.nn.functional.pad(full, [0, bias_shape[3] - Sk])
+            dbias = full
+    return dq, dk, dv, dbias
+
+
 class _CompactAttnFunc(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, mask, bias, softmax_scale, is_causal, capacity, trusted):
-        lib = _lib.load()
         q = q if q.stride(-1) == 1 else q.contiguous()
         ck = compact_keys(k, v, mask, bias, capacity, check_capacity=not trusted)
-        _check_inputs(q, ck.key, ck.value, ck.mask, ck.bias)
-        B, Sq, H, d = q.shape
-        dev = q.device
-        with torch.cuda.device(dev):
-            out = torch.empty_like(q)
-            lse = torch.empty((B, H, Sq), dtype=torch.float32, device=dev)
-            p = _lib.FwdParams()
-            _fill_fwd(p, q, ck.key, ck.value, ck.mask, ck.bias, out, lse, softmax_scale, is_causal)
-            _set_positions(p, ck, Sq)
-            ws_bytes = lib.fdma_fwd_workspace_bytes(ctypes.byref(p))
-            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev) if ws_bytes else None
-            if ws is not None:
-                p.workspace, p.workspace_bytes = ws.data_ptr(), ws_bytes
-            _lib.check(lib.fdma_fwd(ctypes.byref(p), _stream_ptr(dev)), "fdma_fwd")
+        out, lse = compact_forward(q, ck, softmax_scale, is_causal)
         saved = [q, ck.key, ck.value, ck.mask, ck.key_pos, out, lse] + ([ck.bias] if ck.bias is not None else [])
         ctx.save_for_backward(*saved)
         ctx.has_bias = ck.bias is not None
@@ -162,55 +220,12 @@ class _CompactAttnFunc(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dout):
-        lib = _lib.load()
         saved = ctx.saved_tensors
         q, k_c, v_c, mask_c, key_pos, out, lse = saved[:7]
         bias_c = saved[7] if ctx.has_bias else None
         softmax_scale, is_causal, Sk, k_shape, bias_shape = ctx.meta
-        B, Sq, H, d = q.shape
-        Hk, cap = k_c.shape[2], k_c.shape[1]
-        dev = q.device
-        dout = dout if dout.stride(-1) == 1 else dout.contiguous()
         ck = CompactKeys(k_c, v_c, mask_c, bias_c, key_pos, None, Sk)
-        with torch.cuda.device(dev):
-            dq = torch.empty_like(q)
-            dk_c, dv_c = torch.empty_like(k_c), torch.empty_like(v_c)
-            dbias_c = torch.empty_like(bias_c) if bias_c is not None else None
-            bp = _lib.BwdParams()
-            _fill_fwd(bp.f, q, k_c, v_c, mask_c, bias_c, out, lse, softmax_scale, is_causal)
-            _set_positions(bp.f, ck, Sq)
-            bp.dout = dout.data_ptr()
-            bp.do_batch_stride, bp.do_row_stride, bp.do_head_stride = _bsh(dout)
-            bp.dq, bp.dk, bp.dv = dq.data_ptr(), dk_c.data_ptr(), dv_c.data_ptr()
-            bp.dq_batch_stride, bp.dq_row_stride, bp.dq_head_stride = _bsh(dq)
-            bp.dk_batch_stride, bp.dk_row_stride, bp.dk_head_stride = _bsh(dk_c)
-            bp.dv_batch_stride, bp.dv_row_stride, bp.dv_head_stride = _bsh(dv_c)
-            if dbias_c is not None:
-                bp.dbias = dbias_c.data_ptr()
-                bp.dbias_batch_stride, bp.dbias_head_stride, bp.dbias_row_stride = dbias_c.stride()[:3]
-                bp.dbias_b, bp.dbias_h, bp.dbias_rows, bp.dbias_keys = dbias_c.shape
-            ws_bytes = lib.fdma_bwd_workspace_bytes(ctypes.byref(bp))
-            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev) if ws_bytes else None
-            if ws is not None:
-                bp.f.workspace, bp.f.workspace_bytes = ws.data_ptr(), ws_bytes
-            _lib.check(lib.fdma_bwd(ctypes.byref(bp), _stream_ptr(dev)), "fdma_bwd")
-            dk = torch.empty(k_shape, dtype=q.dtype, device=dev)
-            dv = torch.empty(k_shape, dtype=q.dtype, device=dev)
-            for src, dst in ((dk_c, dk), (dv_c, dv)):
-                _rows_call(lib.fdma_scatter_rows, src, dst, key_pos, B, Hk, Sk, cap, d, _bsh(src), _bsh(dst), dev)
-            dbias = None
-            if dbias_c is not None:
-                Bc, Hc = dbias_c.shape[0], dbias_c.shape[1]
-                full = torch.empty((Bc, Hc, 1, Sk), dtype=q.dtype, device=dev)
-                _rows_call(lib.fdma_scatter_rows, dbias_c, full, key_pos, Bc, Hc, Sk, cap, 1,
-                           (dbias_c.stride(0), 1, dbias_c.stride(1)), (full.stride(0), 1, full.stride(1)), dev)
-                # dimensions the bias broadcast over (and the compaction widened) are summed back
-                for dim in (0, 1, 3):
-                    if bias_shape[dim] == 1 and full.shape[dim] != 1:
-                        full = full.sum(dim=dim, keepdim=True, dtype=torch.float32).to(q.dtype)
-                if bias_shape[3] > Sk:
-                    full = torch.nn.functional.pad(full, [0, bias_shape[3] - Sk])
-                dbias = full
+        dq, dk, dv, dbias = compact_backward(dout, q, ck, out, lse, softmax_scale, is_causal, k_shape, bias_shape)
         return dq, dk, dv, None, dbias, None, None, None, None
 
 

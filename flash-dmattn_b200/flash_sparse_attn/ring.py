@@ -67,6 +67,37 @@ def _default_bwd(dout, q, k, v, mask, bias, out, lse, scale, causal):
     return dq, dk, dv, dbias
 
 
+def _compact_pair_fns(capacity: int):
+    """Per-pair operators that gather the kept keys of the visiting chunk first (flash_sparse_attn/compaction.py):
+    a chunk pair is either fully visible or the causal diagonal of two equally long chunks, so plain causal
+    semantics on the chunk's own key positions apply. `capacity` bounds the kept keys of any chunk."""
+    from . import compaction
+
+    def fwd(q, k, v, mask, bias, scale, causal):
+        ck = compaction.compact_keys(k, v, mask, bias, capacity, check_capacity=False)
+        return compaction.compact_forward(q, ck, scale, causal)
+
+    def bwd(dout, q, k, v, mask, bias, out, lse, scale, causal):
+        ck = compaction.compact_keys(k, v, mask, bias, capacity, check_capacity=False)
+        return compaction.compact_backward(dout, q, ck, out, lse, scale, causal, tuple(k.shape),
+                                           tuple(bias.shape) if bias is not None else None)
+
+    return fwd, bwd
+
+
+def _chunk_capacity(mask: Optional[torch.Tensor], group, chunk: int) -> Optional[int]:
+    """Largest number of kept keys in any chunk of any rank (one all-reduce and one read-back per call), rounded
+    up to 128 -- or None when gathering would not pay (no mask, CPU tensors, more than 3/4 of a chunk kept)."""
+    from . import flash_sparse_attn_interface as iface
+
+    if mask is None or not mask.is_cuda or iface._compaction != "auto":
+        return None
+    counts = mask.reshape(*mask.shape[:2], 2, chunk).sum(dim=-1, dtype=torch.int32).max().reshape(1)
+    dist.all_reduce(counts, op=dist.ReduceOp.MAX, group=group)
+    cap = max(128, (int(counts.item()) + 127) // 128 * 128)
+    return cap if 4 * cap <= 3 * chunk else None
+
+
 def _pad_keys(t: Optional[torch.Tensor], keys: int) -> Optional[torch.Tensor]:
     """mask / bias key dimension rounded up to a multiple of 128, as the operator expects."""
     if t is None:
@@ -149,6 +180,10 @@ class RingAttnFunc(torch.autograd.Function):
                 raise ValueError("ring attention takes query-broadcast mask/bias of local key length: (B|1, h, 1, 2C)")
         scale = d ** -0.5 if softmax_scale is None else softmax_scale
         causal = bool(is_causal)
+        if fwd_fn is _default_fwd and bwd_fn is _default_bwd and d % 8 == 0:
+            cap = _chunk_capacity(mask, group, C)
+            if cap is not None:
+                fwd_fn, bwd_fn = _compact_pair_fns(cap)
         payload = [torch.stack([k, v])]
         if bias is not None:
             payload.append(bias)

@@ -1,5 +1,6 @@
 """KV-ring context parallelism on real GPUs (needs at least two): NCCL ranks as child processes, tcgen05 kernels
-underneath, compared with the fp32 oracle on the full sequence."""
+underneath (each chunk pair over its full key range, and with the kept keys of the visiting chunk gathered first),
+compared with the fp32 oracle on the full sequence."""
 import os
 import socket
 
@@ -9,11 +10,14 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, causal):
+def _worker(rank, world, port, causal, route):
     import torch.distributed as dist
 
+    from flash_sparse_attn import flash_sparse_attn_interface as iface
     from flash_sparse_attn import ring
     from oracle import oracle
+
+    iface.set_compaction(route)
 
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -45,8 +49,9 @@ def _worker(rank, world, port, causal):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("route", ["off", "auto"], ids=["tiles", "compaction"])
 @pytest.mark.parametrize("causal", [True, False])
-def test_ring_two_gpus(causal):
+def test_ring_two_gpus(causal, route):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
@@ -54,4 +59,4 @@ def test_ring_two_gpus(causal):
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
-    mp.spawn(_worker, args=(2, port, causal), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, port, causal, route), nprocs=2, join=True)
