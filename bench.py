@@ -609,6 +609,83 @@ def run_ring(args, rank: int, world: int, local_rank: int):
     print(json.dumps(line), flush=True)
 
 
+def run_decode(args, rank: int, world: int, local_rank: int):
+    """Secondary workload (not the headline line): BASELINE config 4, single-query forward over a KV cache,
+    B = 32 per GPU (--decode-batch), Sk = 65536, Hq = 32, Hkv = 8, d = 128, top-4096 mask, non-causal. HBM-bound:
+    reported as GB/s of the bytes the kernel's skip granule (one key row) makes it read."""
+    import torch.distributed as dist
+
+    from flash_sparse_attn import _lib, flash_sparse_attn_func
+    from flash_sparse_attn.utils.mask import create_mask
+
+    dev = torch.device(f"cuda:{local_rank}")
+    torch.cuda.set_device(dev)
+    B, Sk, H, Hk, d, w = args.decode_batch, 65536, 32, 8, 128, 4096
+    g = torch.Generator(device=dev).manual_seed(4321 + rank)
+    rnd = lambda *shape: torch.randn(shape, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    q, k, v, bias = rnd(B, 1, H, d), rnd(B, Sk, Hk, d), rnd(B, Sk, Hk, d), rnd(B, Hk, 1, Sk)
+    mask = create_mask(bias, None, B, 1, Sk, w, torch.finfo(torch.bfloat16).min)
+    kept = int(mask.sum().item())
+    nbytes = kept * 2 * d * 2 + mask.numel() + kept * 2 + 2 * q.numel() * 2  # K+V rows, mask bytes, bias, Q, O
+    stream = torch.cuda.current_stream(dev)
+    with torch.no_grad():
+        for _ in range(max(args.warmup, 3)):
+            flash_sparse_attn_func(q, k, v, attn_mask=mask, attn_bias=bias)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        kev = []
+        for _ in range(args.steps):
+            pair = [torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)]
+            for e in pair:
+                e.record(stream)
+            kev.append(pair)
+        torch.cuda.synchronize(dev)
+        lib = _lib.load()
+        e0.record(stream)
+        for i in range(args.steps):
+            lib.fdma_time_next_kernel(kev[i][0].cuda_event, kev[i][1].cuda_event)
+            flash_sparse_attn_func(q, k, v, attn_mask=mask, attn_bias=bias)
+        e1.record(stream)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+    _lib.check(_lib.load().fdma_last_kernel_status(stream.cuda_stream, None), "kernel status")
+    kernel_ms = statistics.mean(a.elapsed_time(b_) for a, b_ in kev)
+    vals = torch.tensor([e0.elapsed_time(e1) / args.steps, float(nbytes), kernel_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        ms_t = vals[:1].clone()
+        dist.all_reduce(ms_t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(vals, op=dist.ReduceOp.SUM)
+        vals[0] = ms_t[0]
+    if rank != 0:
+        return
+    ms, total_bytes, kernel_ms = vals.tolist()
+    kernel_ms /= world
+    peak = 6538.9
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    src = "fallback"
+    if os.path.exists(path):
+        with open(path) as f:
+            peak, src = float(json.load(f).get("hbm_gbs", peak)), "measured (copy)"
+    gbs = total_bytes / (ms * 1e-3) / 1e9
+    line = {
+        "metric": "decode forward GB/s of bytes read at key-row granularity", "value": gbs, "unit": "GB/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"decode: B={B} per GPU, Sq=1, Sk={Sk}, Hq={H}, Hkv={Hk}, d={d}, W={w}, non-causal",
+                   "bytes_per_step": total_bytes, "l2": "K/V cache far larger than L2"},
+        "decode_kernel_ms": kernel_ms,
+        "roofline": {"bound": "hbm", "kernel": "decode_pipe_kernel",
+                     "achieved": total_bytes / world / (kernel_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                     "frac": total_bytes / world / (kernel_ms * 1e-3) / 1e9 / peak, "peak_source": "of " + src,
+                     "traffic": None},
+        "gpu_launches": args.steps * 2,  # decode_kernel + decode_merge_kernel
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -620,8 +697,10 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     ap.add_argument("--seq-len", type=int, default=S, help="profiling only: shorter sequence")
     ap.add_argument("--window", type=int, default=WINDOW, help="profiling only: window for --seq-len")
-    ap.add_argument("--workload", default="sharded", choices=["sharded", "ring"],
-                    help="sharded = the headline benchmark; ring = single long sequence over a KV ring (needs >= 2 ranks)")
+    ap.add_argument("--workload", default="sharded", choices=["sharded", "ring", "decode"],
+                    help="sharded = the headline benchmark; ring = single long sequence over a KV ring (needs >= 2 "
+                         "ranks); decode = single-query forward over a KV cache (HBM-bound)")
+    ap.add_argument("--decode-batch", type=int, default=32)
     ap.add_argument("--ring-seq-len", type=int, default=131072)
     ap.add_argument("--compaction", default="auto", choices=["auto", "off"],
                     help="auto = the library's default route for this mask (kept keys gathered first); off = full key range")
@@ -647,6 +726,8 @@ def main():
     try:
         if args.workload == "ring":
             run_ring(args, rank, world, local_rank)
+        elif args.workload == "decode":
+            run_decode(args, rank, world, local_rank)
         else:
             run_ours(args, rank, world, local_rank)
     finally:

@@ -205,6 +205,296 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(const DecodeParams p) 
   }
 }
 
+// ---- pipelined variant for G * rows-per-batch == 32 (G = 4: 8 rows, G = 8: 4 rows), head dim <= 128 ------------
+// Same scan / queue / partial scheme as decode_kernel, with two changes that matter when the kernel is bound by the
+// latency of scattered row reads:
+//  * rows travel global -> shared memory with cp.async into a ring of kPipeStages batches per warp, so the next
+//    batches of K / V rows are in flight (holding no registers) while the current one is computed;
+//  * the rows x G scores of a batch are reduced across lanes with one halving butterfly (31 shuffles for 32 sums
+//    instead of 5 per sum), leaving score (row t, head g) in lane t * G + g; that lane alone evaluates the exp2, and the
+//    probabilities and rescale factors reach the other lanes through shared memory.
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem))),
+               "l"(gmem)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+constexpr int kPipeStages = 2;  // row batches per warp: one being computed, the other in flight (3 measured the same)
+
+template <int EPL, int G>
+struct PipeSmem {
+  static constexpr int D = 32 * EPL;
+  static constexpr int kRows = 32 / G;                      // rows per batch
+  static constexpr int kStageBytes = 2 * kRows * D * 2;     // K rows then V rows, 16-bit
+  static constexpr int kWarpBytes = kPipeStages * kStageBytes;
+  static constexpr int kTotal = kWarps * kWarpBytes;
+};
+
+template <int EPL, int G, bool kBf16>
+__global__ void __launch_bounds__(kThreads, 2) decode_pipe_kernel(const DecodeParams p) {
+  using L = PipeSmem<EPL, G>;
+  constexpr int D = L::D, R = L::kRows;
+  constexpr int kChunksPerRow = D / 8;                      // 16-byte pieces of a row
+  constexpr int kRowsPerCopy = 32 / kChunksPerRow;          // rows covered by one warp-wide cp.async
+  extern __shared__ __align__(16) unsigned char s_rows[];
+  __shared__ int s_queue[kWarps][kQueue];
+  __shared__ float s_qbias[kWarps][kQueue];
+  __shared__ float s_pbias[kWarps][kPipeStages][R];         // bias of the rows of each stage
+  __shared__ __align__(16) float s_prob[kWarps][32];        // probabilities of the batch, index t * G + g
+  __shared__ __align__(16) float s_corr[kWarps][G];         // rescale factor of the running state per head
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int split = blockIdx.x, b = blockIdx.z;
+  const int h0 = blockIdx.y * G;
+  const int hk = h0 / p.group;
+  const int hm = p.h_mask == p.h ? h0 : (p.h_mask == p.h_k ? hk : 0);
+  const int hb = p.h_bias == p.h ? h0 : (p.h_bias == p.h_k ? hk : 0);
+  const uint8_t* mrow = p.mask ? p.mask + b * p.mask_batch_stride + hm * p.mask_head_stride : nullptr;
+  const uint16_t* brow = p.bias ? reinterpret_cast<const uint16_t*>(p.bias) + b * p.bias_batch_stride + hb * p.bias_head_stride
+                                : nullptr;
+  const uint16_t* kbase = reinterpret_cast<const uint16_t*>(p.k) + b * p.k_batch_stride + hk * p.k_head_stride;
+  const uint16_t* vbase = reinterpret_cast<const uint16_t*>(p.v) + b * p.v_batch_stride + hk * p.v_head_stride;
+  unsigned char* my_rows = s_rows + warp * L::kWarpBytes;
+
+  float qv[G][EPL];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    const uint16_t* qp = reinterpret_cast<const uint16_t*>(p.q) + b * p.q_batch_stride + (h0 + g) * p.q_head_stride + lane * EPL;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) qv[g][e] = raw_to_f<kBf16>(qp[e]) * p.scale_log2;
+  }
+  float acc[G][EPL];
+#pragma unroll
+  for (int g = 0; g < G; ++g)
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) acc[g][e] = 0.f;
+  float my_m = -CUDART_INF_F, my_l = 0.f;                   // running max / sum of head my_g (same in all its lanes)
+
+  auto load_elems = [&](const unsigned char* row, float (&out)[EPL]) {
+    if (EPL == 4) {
+      const uint2 r = *reinterpret_cast<const uint2*>(row + lane * 8);
+      out[0] = raw_to_f<kBf16>(static_cast<uint16_t>(r.x & 0xFFFFu));
+      out[1] = raw_to_f<kBf16>(static_cast<uint16_t>(r.x >> 16));
+      out[2] = raw_to_f<kBf16>(static_cast<uint16_t>(r.y & 0xFFFFu));
+      out[3] = raw_to_f<kBf16>(static_cast<uint16_t>(r.y >> 16));
+    } else {
+      const uint32_t r = *reinterpret_cast<const uint32_t*>(row + lane * 4);
+      out[0] = raw_to_f<kBf16>(static_cast<uint16_t>(r & 0xFFFFu));
+      out[1] = raw_to_f<kBf16>(static_cast<uint16_t>(r >> 16));
+    }
+  };
+
+  // queue entries [first, first + n) -> stage: start the row copies, remember the rows' biases
+  auto issue = [&](int first, int n, int stage) {
+    unsigned char* dst = my_rows + stage * L::kStageBytes;
+    const int sub = lane / kChunksPerRow, chunk = lane % kChunksPerRow;
+#pragma unroll
+    for (int r0 = 0; r0 < R; r0 += kRowsPerCopy) {
+      const int t = r0 + sub;
+      if (t < R) {
+        const int64_t key = s_queue[warp][first + min(t, n - 1)];
+        cp_async16(dst + t * (D * 2) + chunk * 16, kbase + key * p.k_row_stride + chunk * 8);
+        cp_async16(dst + (R + t) * (D * 2) + chunk * 16, vbase + key * p.v_row_stride + chunk * 8);
+      }
+    }
+    cp_async_commit();
+    if (lane < R) s_pbias[warp][stage][lane] = lane < n ? s_qbias[warp][first + lane] : -CUDART_INF_F;
+  };
+
+  // the rows of `stage` have landed: scores, online softmax, value accumulation
+  auto consume = [&](int stage) {
+    __syncwarp();
+    const unsigned char* src = my_rows + stage * L::kStageBytes;
+    float v[32];
+#pragma unroll
+    for (int t = 0; t < R; ++t) {
+      float kr[EPL];
+      load_elems(src + t * (D * 2), kr);
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        float d = 0.f;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) d = fmaf(qv[g][e], kr[e], d);
+        v[t * G + g] = d;
+      }
+    }
+    // halving butterfly: after the step with offset o a lane keeps the half selected by its bit o
+#pragma unroll
+    for (int o = 16, n = 32; o > 0; o >>= 1, n >>= 1) {
+      const bool upper = (lane & o) != 0;
+#pragma unroll
+      for (int i = 0; i < n / 2; ++i) {
+        const float send = upper ? v[i] : v[i + n / 2];
+        const float keep = upper ? v[i + n / 2] : v[i];
+        v[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+      }
+    }
+    const int my_t = lane / G;
+    const float sc = v[0] + s_pbias[warp][stage][my_t];     // -inf for the padding rows of a short batch
+    float mx = sc;
+#pragma unroll
+    for (int o = G; o < 32; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    const float m_new = fmaxf(my_m, mx);
+    const float pw = m_new == -CUDART_INF_F ? 0.f : exp2f(sc - m_new);
+    const float corr = my_m == -CUDART_INF_F ? 0.f : exp2f(my_m - m_new);
+    float psum = pw;
+#pragma unroll
+    for (int o = G; o < 32; o <<= 1) psum += __shfl_xor_sync(0xffffffffu, psum, o);
+    my_l = my_l * corr + psum;
+    my_m = m_new;
+    s_prob[warp][lane] = pw;
+    if (lane < G) s_corr[warp][lane] = corr;
+    __syncwarp();
+    float cg[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) cg[g] = s_corr[warp][g];
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) acc[g][e] *= cg[g];
+#pragma unroll
+    for (int t = 0; t < R; ++t) {
+      float vr[EPL];
+      load_elems(src + (R + t) * (D * 2), vr);
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const float pg = s_prob[warp][t * G + g];
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) acc[g][e] = fmaf(pg, vr[e], acc[g][e]);
+      }
+    }
+    __syncwarp();
+  };
+
+  // Scan in pieces of 512 keys per warp: every lane fetches the 16 mask bytes and 16 biases of 16 consecutive keys
+  // with three independent vector loads, then the warp walks the 16 byte positions without touching global memory
+  // (position j of all lanes forms one 32-key group; the order in which kept keys are queued does not matter).
+  // The loop below has ONE copy of the scan step and ONE of issue / consume: with the phases of a warp's life
+  // sharing code, the warps of an SM partition stay inside the instruction cache.
+  constexpr int kPiece = 512;
+  const int pieces_total = (p.seqlen_k + kPiece - 1) / kPiece;
+  const int pieces_per_split = (pieces_total + p.nsplit - 1) / p.nsplit;
+  const int c_end = min(pieces_total, (split + 1) * pieces_per_split);
+  int c = split * pieces_per_split + warp;  // next piece of this warp
+  int left = 0, gi = 0, base = 0;           // 32-key groups left in the loaded piece, index of the current one
+  uint32_t mw[4] = {0u, 0u, 0u, 0u};        // mw[0] / bw[0..1] always hold the word the current group is in
+  uint32_t bw[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+  int head = 0, qn = 0;                     // queue entries [head, qn) wait for their batch
+  int pend = 0, st_w = 0, st_r = 0;         // batches in flight, stage to fill next, stage to compute next
+  for (;;) {
+    while (qn - head < R && (left > 0 || c < c_end)) {
+      if (left == 0) {
+        base = c * kPiece + lane * 16;
+        c += kWarps;
+        left = 16;
+        gi = 0;
+        if (base + 16 <= p.seqlen_k) {
+          mw[0] = mw[1] = mw[2] = mw[3] = 0x01010101u;
+          if (mrow) {
+            const uint4 mv = *reinterpret_cast<const uint4*>(mrow + base);
+            mw[0] = mv.x; mw[1] = mv.y; mw[2] = mv.z; mw[3] = mv.w;
+          }
+          if (brow) {
+            const uint4 b0 = *reinterpret_cast<const uint4*>(brow + base);
+            const uint4 b1 = *reinterpret_cast<const uint4*>(brow + base + 8);
+            bw[0] = b0.x; bw[1] = b0.y; bw[2] = b0.z; bw[3] = b0.w;
+            bw[4] = b1.x; bw[5] = b1.y; bw[6] = b1.z; bw[7] = b1.w;
+          }
+        } else {  // ragged end of the row: byte by byte, keys beyond the end count as masked
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int key = base + j;
+            uint32_t mbyte = 0u, bhalf = 0u;
+            if (key < p.seqlen_k) {
+              mbyte = mrow ? (mrow[key] != 0 ? 1u : 0u) : 1u;
+              if (brow) bhalf = brow[key];
+            }
+            mw[j >> 2] = (mw[j >> 2] & ~(0xFFu << ((j & 3) * 8))) | (mbyte << ((j & 3) * 8));
+            bw[j >> 1] = (bw[j >> 1] & ~(0xFFFFu << ((j & 1) * 16))) | (bhalf << ((j & 1) * 16));
+          }
+        }
+      }
+      int adv = 1;
+      if ((gi & 3) == 0 && __ballot_sync(0xffffffffu, mw[0] != 0u) == 0u) {
+        adv = 4;  // 128 keys without a kept one
+      } else {
+        const int i = gi & 3;
+        const bool keep = ((mw[0] >> (8 * i)) & 0xFFu) != 0u;
+        const uint32_t bits = __ballot_sync(0xffffffffu, keep);
+        if (bits != 0u) {
+          if (qn > kQueue - 32) {  // make room: move the waiting entries (fewer than one batch) to the front
+            const int rest = qn - head;
+            int kk = 0;
+            float bb = 0.f;
+            if (lane < rest) {
+              kk = s_queue[warp][head + lane];
+              bb = s_qbias[warp][head + lane];
+            }
+            __syncwarp();
+            if (lane < rest) {
+              s_queue[warp][lane] = kk;
+              s_qbias[warp][lane] = bb;
+            }
+            head = 0;
+            qn = rest;
+          }
+          if (keep) {
+            const int pos = qn + __popc(bits & ((1u << lane) - 1u));
+            const uint32_t bpair = (i & 2) ? bw[1] : bw[0];
+            const uint16_t braw = static_cast<uint16_t>((i & 1) ? (bpair >> 16) : (bpair & 0xFFFFu));
+            s_queue[warp][pos] = base + gi;
+            s_qbias[warp][pos] = brow ? raw_to_f<kBf16>(braw) * 1.4426950408889634f : 0.f;
+          }
+          qn += __popc(bits);
+          __syncwarp();
+        }
+      }
+      gi += adv;
+      left -= adv;
+      if ((gi & 3) == 0) {  // next word of the piece moves into place
+        mw[0] = mw[1]; mw[1] = mw[2]; mw[2] = mw[3];
+        bw[0] = bw[2]; bw[1] = bw[3]; bw[2] = bw[4]; bw[3] = bw[5]; bw[4] = bw[6]; bw[5] = bw[7];
+      }
+    }
+    // one batch goes out; once every stage is taken (or nothing is left to send) the oldest batch is computed
+    // while the newer ones load
+    const int n = min(R, qn - head);
+    if (n > 0) {
+      issue(head, n, st_w);
+      head += n;
+      st_w = st_w + 1 == kPipeStages ? 0 : st_w + 1;
+      ++pend;
+    }
+    if (pend == kPipeStages || (n == 0 && pend > 0)) {
+      static_assert(kPipeStages <= 3, "add a wait for deeper rings");
+      if (pend >= 3) cp_async_wait<2>();  // all but the newest (pend - 1) groups have landed
+      else if (pend == 2) cp_async_wait<1>();
+      else cp_async_wait<0>();
+      consume(st_r);
+      st_r = st_r + 1 == kPipeStages ? 0 : st_r + 1;
+      --pend;
+    }
+    if (n == 0 && pend == 0) break;
+  }
+
+  // one partial per warp; lane g (row 0 of the butterfly layout) holds head g's running max and sum
+  const int P = p.nsplit * kWarps;
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    float* dst = p.partial + ((static_cast<int64_t>(b) * p.h + h0 + g) * P + split * kWarps + warp) * (D + 2);
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) dst[lane * EPL + e] = acc[g][e];
+    if (lane == g) {
+      dst[D] = my_m;
+      dst[D + 1] = my_l;
+    }
+  }
+}
+
 // O = sum_i 2^(m_i - M) acc_i / sum_i 2^(m_i - M) l_i, LSE = (M + log2(sum)) * ln2; one warp per (b, h).
 template <bool kBf16>
 __global__ void decode_merge_kernel(const float* __restrict__ partial, void* __restrict__ out, float* __restrict__ lse,
@@ -239,11 +529,25 @@ __global__ void decode_merge_kernel(const float* __restrict__ partial, void* __r
 }
 
 int pick_splits(const fdma_fwd_params& p, int ctas_per_split) {
-  // aim at ~4 CTAs per SM; every split needs at least a few 32-key chunks per warp
-  const int target = 148 * 4;
-  int ns = std::max(1, target / std::max(1, ctas_per_split));
-  const int max_by_len = std::max(1, (p.seqlen_k + 32 * kWarps * 4 - 1) / (32 * kWarps * 4));
-  return std::min(std::min(ns, max_by_len), 64);
+  // Two CTAs are resident per SM and all CTAs of a launch take about the same time, so the launch lasts
+  // ceil(splits * ctas_per_split / slots) rounds of 1 / splits of the work each: pick the split count with the
+  // smallest product (a small charge per split covers the extra partials). Every split keeps at least four
+  // 512-key pieces per warp... unless the row is shorter than that.
+  const int slots = 148 * 2;
+  const int max_by_len = std::max(1, (p.seqlen_k + 512 * kWarps * 4 - 1) / (512 * kWarps * 4));
+  const int limit = std::min(max_by_len, 32);
+  int best = 1;
+  double best_cost = 1e30;
+  for (int ns = 1; ns <= limit; ++ns) {
+    const int64_t ctas = static_cast<int64_t>(ns) * std::max(1, ctas_per_split);
+    const double rounds = static_cast<double>((ctas + slots - 1) / slots);
+    const double cost = rounds / ns + 0.01 * ns;
+    if (cost < best_cost) {
+      best_cost = cost;
+      best = ns;
+    }
+  }
+  return best;
 }
 
 bool group_shares_mask_bias(const fdma_fwd_params& p) {
@@ -259,8 +563,34 @@ int group_size(const fdma_fwd_params& p) {
   return 1;
 }
 
+template <int EPL, int G, bool kBf16>
+int launch_pipe(const DecodeParams& dp, dim3 grid, cudaStream_t stream) {
+  using L = PipeSmem<EPL, G>;
+  auto kern = decode_pipe_kernel<EPL, G, kBf16>;
+  const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  kern<<<grid, kThreads, L::kTotal, stream>>>(dp);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// cp.async moves 16-byte pieces: K / V bases and row strides must keep rows 16-byte aligned
+bool pipe_ok(const DecodeParams& dp) {
+  auto a16 = [](const void* x) { return (reinterpret_cast<uintptr_t>(x) & 15u) == 0; };
+  const int64_t strides[6] = {dp.k_batch_stride, dp.k_row_stride, dp.k_head_stride,
+                              dp.v_batch_stride, dp.v_row_stride, dp.v_head_stride};
+  for (int64_t s : strides)
+    if (s % 8) return false;
+  // the scan reads 16 mask bytes and 16 biases per lane with 16-byte loads
+  if (dp.mask && (!a16(dp.mask) || dp.mask_batch_stride % 16 || dp.mask_head_stride % 16)) return false;
+  if (dp.bias && (!a16(dp.bias) || dp.bias_batch_stride % 8 || dp.bias_head_stride % 8)) return false;
+  return a16(dp.k) && a16(dp.v);
+}
+
 template <int EPL, bool kBf16>
 int launch_epl(const DecodeParams& dp, int G, dim3 grid, cudaStream_t stream) {
+  // (G = 8 at head dim 128 would spill at the register budget of three CTAs per SM: it stays on decode_kernel)
+  if (EPL <= 4 && G == 4 && pipe_ok(dp)) return launch_pipe<(EPL <= 4 ? EPL : 4), 4, kBf16>(dp, grid, stream);
+  if (EPL <= 2 && G == 8 && pipe_ok(dp)) return launch_pipe<(EPL <= 2 ? EPL : 2), 8, kBf16>(dp, grid, stream);
   switch (G) {
     case 1: decode_kernel<EPL, 1, kBf16><<<grid, kThreads, 0, stream>>>(dp); break;
     case 2: decode_kernel<EPL, 2, kBf16><<<grid, kThreads, 0, stream>>>(dp); break;
@@ -318,10 +648,14 @@ int decode_fwd(const fdma_fwd_params& p, cudaStream_t stream) {
   dp.scale_log2 = p.softmax_scale * 1.4426950408889634f;
   dim3 grid(ns, p.h / G, p.b);
   const bool bf = p.dtype == FDMA_BF16;
+  cudaEvent_t ev0, ev1;
+  take_timing_events(&ev0, &ev1);
+  if (ev0) cudaEventRecord(ev0, stream);
   int st;
   if (p.d == 64) st = bf ? launch_epl<2, true>(dp, G, grid, stream) : launch_epl<2, false>(dp, G, grid, stream);
   else if (p.d == 128) st = bf ? launch_epl<4, true>(dp, G, grid, stream) : launch_epl<4, false>(dp, G, grid, stream);
   else st = bf ? launch_epl<8, true>(dp, G, grid, stream) : launch_epl<8, false>(dp, G, grid, stream);
+  if (ev1) cudaEventRecord(ev1, stream);
   if (st) return st;
   const int64_t warps = static_cast<int64_t>(p.b) * p.h;
   const unsigned blocks = static_cast<unsigned>((warps * 32 + 255) / 256);
