@@ -32,11 +32,8 @@ namespace {
 
 constexpr int kBM = 128;          // query rows per tile
 constexpr int kBN = 128;          // keys per tile
-constexpr int kNQ = 2;            // query tiles per CTA
-constexpr int kStages = 4;        // K/V ring slots
 constexpr int kBmSlots = 4;       // bias+mask addend ring slots
 constexpr int kMaxTiles = 8192;   // key tiles per row the tile-flag table can hold (Sk <= 1M)
-constexpr int kThreads = 384;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;
@@ -70,8 +67,14 @@ struct FwdKernelParams {
   float scale_log2;  // softmax_scale * log2(e)
 };
 
+// Head dims 64 and 128: two query tiles (softmax warpgroups) per CTA share every K / V tile; TMEM S0|S1|O0|O1.
+// Head dim 256: the O accumulator alone takes 256 TMEM columns and a K or V tile 64 KiB of shared memory, so a CTA
+// owns ONE query tile (TMEM S|O = 128 + 256 columns) and the K/V ring has two slots.
 template <int D>
 struct Smem {
+  static constexpr int kNQ = D == 256 ? 1 : 2;          // query tiles per CTA
+  static constexpr int kThreads = 128 + 128 * kNQ;
+  static constexpr int kStages = D == 256 ? 2 : 4;      // K/V ring slots
   static constexpr int kQBytes = kBM * D * 2;
   static constexpr int kKvBytes = kBN * D * 2;
   static constexpr int kQOff = 0;
@@ -125,8 +128,9 @@ __global__ void tile_activity_kernel(const uint8_t* __restrict__ mask, int64_t s
 }
 
 template <int D, bool kBf16, bool kBcast>
-__global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant__ FwdKernelParams p) {
+__global__ void __launch_bounds__(Smem<D>::kThreads, 1) fwd_kernel(const __grid_constant__ FwdKernelParams p) {
   using L = Smem<D>;
+  constexpr int kNQ = L::kNQ, kStages = L::kStages, kThreads = L::kThreads;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) &
                                                          ~static_cast<uintptr_t>(1023));
@@ -183,7 +187,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
     if (m0 >= Sq) ne = 0;
     n_end[t] = ne;
   }
-  const int nT = max(n_end[0], n_end[1]);
+  const int nT = max(n_end[0], n_end[kNQ - 1]);
   const WaitCtl ctl{s_abort, p.status};
 
   // ---------------- set-up: barriers, TMEM, tile flags ----------------
@@ -202,7 +206,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
     mbar_init(bar_stagger, kBM);
     for (int i = 0; i < kBmSlots; ++i) {
       mbar_init(bar_bm_full + i, 1);
-      mbar_init(bar_bm_empty + i, 8);  // one arrival per softmax warp
+      mbar_init(bar_bm_empty + i, 4 * kNQ);  // one arrival per softmax warp
     }
     fence_mbar_init();
   }
@@ -237,8 +241,9 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
         any = acc != 0;
       }
       if (any) {
-        if (j < n_end[0]) f |= 1;
-        if (j < n_end[1]) f |= 2;
+#pragma unroll
+        for (int t = 0; t < kNQ; ++t)
+          if (j < n_end[t]) f |= (1 << t);
         if (pos_row) {  // the tile's smallest position against the last row of each query tile
           const int64_t pmin = pos_row[j * kBN];
 #pragma unroll
@@ -270,7 +275,8 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
 
   // ---------------- roles ----------------
   if (warp < 4) {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+  // (one query tile per CTA: 256 threads have 256 registers each available, nothing to re-partition)
+  if (kNQ == 2) asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
   if (warp == 0) {
     if (lane == 0 && nT > 0) {
       FDMA_PROF_BEGIN();
@@ -335,7 +341,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
             ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(3 + t, mbar_wait(bar_p_full + t, pcnt[t] & 1, ctl, kWaitP)));
             if (!ok) break;
             tc_fence_after_sync();
-            const uint32_t o_col = tmem_base + 2 * kBN + t * 128;
+            const uint32_t o_col = tmem_base + kNQ * kBN + t * 128;
             const uint32_t v_base = kv_addr + (v_it % kStages) * L::kKvBytes;
 #pragma unroll
             for (int kk = 0; kk < kBN / 16; ++kk) {
@@ -415,7 +421,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
     }
   }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+    if (kNQ == 2) asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
     // ---------------- softmax warpgroup for query tile t ----------------
     const int t = (warp - 4) >> 2;
     const int row = (warp & 3) * 32 + lane;          // row inside the tile == TMEM lane
@@ -423,7 +429,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
     const int qrow = m0 + row;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t s_taddr = tmem_base + lane_addr + t * kBN;
-    const uint32_t o_taddr = tmem_base + lane_addr + 2 * kBN + t * 128;
+    const uint32_t o_taddr = tmem_base + lane_addr + kNQ * kBN + t * 128;
     const int qclamp = min(qrow, Sq - 1);
     const uint8_t* mrow = nullptr;
     const uint16_t* brow = nullptr;
@@ -442,7 +448,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_kernel(const __grid_constant_
     // length of both. Warpgroup 1 therefore starts only when warpgroup 0 reaches the exp2 phase of its first
     // tile, which keeps the two loops roughly half a period apart.
     bool stagger_sent = false;
-    if (t == 1) ok = __all_sync(0xffffffffu, mbar_wait(bar_stagger, 0, ctl, kWaitS));
+    if (kNQ == 2 && t == 1) ok = __all_sync(0xffffffffu, mbar_wait(bar_stagger, 0, ctl, kWaitS));
     for (int j = 0; j < nT && ok; ++j) {
       const uint8_t fl = s_flags[j];
       if (fl == 0) continue;
@@ -688,6 +694,7 @@ bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u
 template <int D, bool kBf16, bool kBcast>
 int launch(const fdma_fwd_params& p, const FwdPlan& pl, cudaStream_t stream) {
   using L = Smem<D>;
+  constexpr int kNQ = L::kNQ;
   FwdKernelParams kp;
   const uint32_t box[4] = {64, 1, static_cast<uint32_t>(kBM), 1};
   // Tensor maps over (d, heads, rows, batch). A dimension of extent 1 is never stepped over, so whatever stride
@@ -747,7 +754,7 @@ int launch(const fdma_fwd_params& p, const FwdPlan& pl, cudaStream_t stream) {
   cudaEvent_t ev0, ev1;
   take_timing_events(&ev0, &ev1);
   if (ev0) cudaEventRecord(ev0, stream);
-  kern<<<grid, kThreads, L::kAlloc, stream>>>(kp);
+  kern<<<grid, L::kThreads, L::kAlloc, stream>>>(kp);
   if (ev1) cudaEventRecord(ev1, stream);
   return static_cast<int>(cudaGetLastError());
 }
@@ -773,7 +780,7 @@ int launch_tile_activity(const fdma_fwd_params& p, uint8_t* act, cudaStream_t st
 }
 
 bool tc_fwd_supported(const fdma_fwd_params& p) {
-  if (p.d != 64 && p.d != 128) return false;
+  if (p.d != 64 && p.d != 128 && p.d != 256) return false;
   if (p.seqlen_k <= 0 || p.seqlen_k > kMaxTiles * kBN) return false;
   if (p.h > 65535 || p.b > 65535) return false;
   // TMA: 16-byte aligned bases and strides
@@ -811,6 +818,7 @@ size_t tc_fwd_workspace_bytes(const fdma_fwd_params& p) { return plan(p).act_byt
 int tc_fwd(const fdma_fwd_params& p, cudaStream_t stream) {
   const FwdPlan pl = plan(p);
   if (p.d == 64) return launch_d<64>(p, pl, stream);
+  if (p.d == 256) return launch_d<256>(p, pl, stream);
   return launch_d<128>(p, pl, stream);
 }
 

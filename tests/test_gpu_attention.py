@@ -161,6 +161,11 @@ TC_CASES = [
     ((2, 384, 384, 2, 1, 64), "perq", "none", 0, False),
     ((1, 300, 420, 4, 4, 128), "perhead", "randq", 0, True),
     ((1, 256, 512, 2, 1, 128), "bcast", "randq", 0, True),      # broadcast bias with per-query mask
+    # head dim 256: one query tile per CTA, two-slot K/V ring
+    ((1, 384, 640, 4, 1, 256), "bcast", "topk", 200, True),     # MQA as in BASELINE config 5, Sq < Sk
+    ((2, 300, 300, 2, 2, 256), "bcast", "block", 100, True),    # ragged, whole key tiles skipped
+    ((1, 256, 1280, 2, 1, 256), "perq", "randq", 0, False),     # per-query bias and mask, 10 key tiles
+    ((1, 640, 128, 2, 2, 256), "none", "none", 0, True),        # Sq > Sk
 ]
 
 
