@@ -72,6 +72,22 @@ def _compaction_capacity(query, key, attn_mask, attn_bias, softcap, return_attn_
     return cap if 4 * cap <= 3 * round_multiple(Sk, _KEY_PAD) else None
 
 
+def _kernel_head_dim(d: int, needs_grad: bool) -> int:
+    """Head dim the tensor-core kernels run this call at: the forward kernels exist for 64, 128 and 256, the backward
+    kernel for 128. Smaller head dims are zero-padded up to the next of these (zero columns change neither the scores
+    nor the kept columns of the results; the reference likewise runs every head dim on the next larger kernel,
+    csrc/flash_sparse_attn/src/static_switch.h:60-82). Head dims the padded route cannot serve keep their
+    size and run on the CUDA-core kernels."""
+    if _kernel_path != _lib.PATH_AUTO:
+        return d
+    if needs_grad:
+        return 128 if d <= 128 else d
+    for target in (64, 128, 256):
+        if d <= target:
+            return target
+    return d
+
+
 def round_multiple(x: int, m: int) -> int:
     return (x + m - 1) // m * m
 
@@ -378,6 +394,15 @@ def flash_sparse_attn_func(
     A row-broadcast mask (one keep-set per batch and kv head) is run over its gathered kept keys, which gives the
     same result in far fewer key tiles when the kept keys are scattered; `set_compaction("off")` disables that.
     """
+    d = query.shape[-1]
+    needs_grad = torch.is_grad_enabled() and any(t.requires_grad for t in (query, key, value))
+    d_run = _kernel_head_dim(d, needs_grad) if query.dim() == 4 and not return_attn_probs else d
+    if d_run != d:
+        softmax_scale = d ** (-0.5) if softmax_scale is None else softmax_scale
+        query, key, value = (torch.nn.functional.pad(t, [0, d_run - d]) for t in (query, key, value))
+        out = flash_sparse_attn_func(query, key, value, attn_mask, attn_bias, softmax_scale, is_causal, softcap,
+                                     deterministic, return_attn_probs)
+        return out[..., :d]
     cap = _compaction_capacity(query, key, attn_mask, attn_bias, softcap, return_attn_probs)
     if cap is not None:
         from .compaction import flash_sparse_attn_compact_func

@@ -213,6 +213,28 @@ def test_tcgen05_backward_fp16_and_run_to_run_spread(dev, kernel_path):
     assert torch.equal(a[2], b[2]) and torch.equal(a[3], b[3])  # dK, dV have a fixed accumulation order
 
 
+PADDED_DIM_CASES = [
+    ((1, 256, 256, 2, 1, 64), "bcast", "topk", 128, True),      # BASELINE config 1 geometry: d=64 trains at 128
+    ((2, 200, 333, 4, 2, 32), "perq", "randq", 0, True),
+    ((1, 300, 300, 3, 3, 96), "perhead", "none", 0, False),
+    ((1, 160, 160, 2, 2, 40), "bcast", "topk", 50, True),
+    ((1, 256, 384, 2, 1, 192), "bcast", "topk", 100, True),     # forward at 256, backward on the CUDA-core kernels
+]
+
+
+@pytest.mark.parametrize("geom,bias_kind,mask_kind,window,causal", PADDED_DIM_CASES)
+def test_default_path_pads_small_head_dims(dev, geom, bias_kind, mask_kind, window, causal):
+    """With the default kernel choice, head dims without a tensor-core kernel of their own are zero-padded to the
+    next one (64 / 128 / 256 forward, 128 when gradients are needed); results and gradients keep their shape."""
+    from flash_sparse_attn import flash_sparse_attn_interface as iface
+
+    d = geom[-1]
+    assert iface._kernel_head_dim(d, True) == (128 if d <= 128 else d)
+    assert iface._kernel_head_dim(d, False) == (64 if d <= 64 else 128 if d <= 128 else 256)
+    case = build_case(dev, *geom, bias_kind, mask_kind, window, torch.bfloat16)
+    compare_all(case, causal, torch.bfloat16)
+
+
 DECODE_CASES = [
     ((1, 1, 700, 8, 2, 128), "bcast", "topk", 100, "decode"),     # GQA group of 4 shares K/V rows
     ((2, 1, 5000, 4, 4, 64), "b1h1", "block", 300, "decode"),     # MHA, fully broadcast bias, long runs of skipped keys
