@@ -126,3 +126,26 @@ def test_one_kv_head_group_against_chunked_oracle_at_32k(dev):
         lim = 2e-2 + (3 * r["floor_max_abs"] if reduced else 0.0)
         mlim = 2e-3 + (2 * r["floor_mean_abs"] if reduced else 0.0)
         assert r["max_abs"] <= lim and r["mean_abs"] <= mlim, r
+
+
+def test_config5_geometry_forward_properties(dev):
+    """BASELINE config 5 on one GPU, forward only (its backward runs on the CUDA-core kernels and is covered at small
+    sizes): B=1, S=131072, Hq=16, Hkv=1, d=256, top-1024 row-broadcast mask, causal. Softmax weights sum to one on
+    rows that see a key, rows before the first kept key give zero, and the output is linear in V."""
+    from flash_sparse_attn import flash_sparse_attn_func
+
+    B, S, H, Hk, d, W = 1, 131072, 16, 1, 256, 1024
+    q, k, v, mask, bias, _ = _gen(dev, B, S, H, Hk, d, 1, W, seed=3)
+    first_kept = int(mask[0, 0, 0].float().argmax())
+    with torch.no_grad():
+        o1 = flash_sparse_attn_func(q, k, torch.ones_like(v), attn_mask=mask, attn_bias=bias, is_causal=True).float()
+        assert torch.isfinite(o1).all()
+        assert (o1[:, first_kept:] - 1).abs().max() < 1e-2
+        assert (o1[:, :first_kept] == 0).all()
+        del o1
+        v2 = torch.randn_like(v)
+        o_a = flash_sparse_attn_func(q, k, v, attn_mask=mask, attn_bias=bias, is_causal=True).float()
+        o_b = flash_sparse_attn_func(q, k, v2, attn_mask=mask, attn_bias=bias, is_causal=True).float()
+        o_ab = flash_sparse_attn_func(q, k, (v.float() + v2.float()).to(v.dtype), attn_mask=mask, attn_bias=bias,
+                                      is_causal=True).float()
+    assert (o_ab - (o_a + o_b)).abs().max() < 6e-2
