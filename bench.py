@@ -690,6 +690,53 @@ def run_decode(args, rank: int, world: int, local_rank: int):
     print(json.dumps(line), flush=True)
 
 
+def run_mask(args, rank: int, world: int, local_rank: int):
+    """Secondary workload (not the headline line): create_mask alone at BASELINE config 2's size, 65536 rows (B=1,
+    Hkv=8, Sq=8192) x 8192 keys of bf16 bias, top-1024 per row. HBM-bound: GB/s of bias bytes read + mask bytes
+    written. --mask-rows shrinks it for profiler captures."""
+    from flash_sparse_attn import _lib
+    from flash_sparse_attn.utils.mask import create_mask
+
+    if rank != 0:
+        return
+    dev = torch.device(f"cuda:{local_rank}")
+    torch.cuda.set_device(dev)
+    rows, keys, w = args.mask_rows, 8192, 1024
+    g = torch.Generator(device=dev).manual_seed(77)
+    bias = torch.randn((1, 8, rows // 8, keys), generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    min_dtype = torch.finfo(torch.bfloat16).min
+    stream = torch.cuda.current_stream(dev)
+    for _ in range(max(args.warmup, 3)):
+        mask = create_mask(bias, None, 1, rows // 8, keys, w, min_dtype)
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        mask = create_mask(bias, None, 1, rows // 8, keys, w, min_dtype)
+    e1.record(stream)
+    torch.cuda.synchronize(dev)
+    ms = e0.elapsed_time(e1) / args.steps
+    assert int(mask[0, 0, 0].sum()) == w
+    nbytes = bias.numel() * 2 + mask.numel()
+    peak, src = 6538.9, "fallback"
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            peak, src = float(json.load(f).get("hbm_gbs", peak)), "measured (copy)"
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    line = {
+        "metric": "create_mask GB/s (bias read + mask written)", "value": gbs, "unit": "GB/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"create_mask: {rows} rows x {keys} keys bf16, top-{w} per row", "bytes_per_step": nbytes,
+                   "l2": "bias larger than L2"},
+        "roofline": {"bound": "hbm", "kernel": "topk16_reg_kernel", "achieved": gbs, "peak": peak, "unit": "GB/s",
+                     "frac": gbs / peak, "peak_source": "of " + src, "traffic": None},
+        "gpu_launches": args.steps,
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -701,10 +748,11 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     ap.add_argument("--seq-len", type=int, default=S, help="profiling only: shorter sequence")
     ap.add_argument("--window", type=int, default=WINDOW, help="profiling only: window for --seq-len")
-    ap.add_argument("--workload", default="sharded", choices=["sharded", "ring", "decode"],
+    ap.add_argument("--workload", default="sharded", choices=["sharded", "ring", "decode", "mask"],
                     help="sharded = the headline benchmark; ring = single long sequence over a KV ring (needs >= 2 "
                          "ranks); decode = single-query forward over a KV cache (HBM-bound)")
     ap.add_argument("--decode-batch", type=int, default=32)
+    ap.add_argument("--mask-rows", type=int, default=65536)
     ap.add_argument("--ring-seq-len", type=int, default=131072)
     ap.add_argument("--compaction", default="auto", choices=["auto", "off"],
                     help="auto = the library's default route for this mask (kept keys gathered first); off = full key range")
@@ -732,6 +780,8 @@ def main():
             run_ring(args, rank, world, local_rank)
         elif args.workload == "decode":
             run_decode(args, rank, world, local_rank)
+        elif args.workload == "mask":
+            run_mask(args, rank, world, local_rank)
         else:
             run_ours(args, rank, world, local_rank)
     finally:
