@@ -282,11 +282,10 @@ __global__ void __launch_bounds__(kThreads) topk16_reg_kernel(const fdma_mask_pa
       }
     }
   };
-  constexpr bool kPrefetch = false;  // measured on B200: keeping two rows in flight (more registers, fewer CTAs) is slower
-  if (kPrefetch) fetch(blockIdx.x);
+  // (Fetching the next row while this one is processed was measured on B200: more registers, fewer CTAs, slower.)
   for (int64_t row = blockIdx.x; row < total_rows; row += gridDim.x) {
   const RowPtrs rp = locate(p, row, 2);
-  if (!kPrefetch) fetch(row);
+  fetch(row);
   // ---- transform: chunk c holds keys [c*2048 + tid*8, +8) of the row ----
   uint32_t kw[CHUNKS][4];
 #pragma unroll
@@ -311,7 +310,6 @@ __global__ void __launch_bounds__(kThreads) topk16_reg_kernel(const fdma_mask_pa
       kw[c][0] = kw[c][1] = kw[c][2] = kw[c][3] = 0u;  // below every real key, never counted, never written
     }
   }
-  if (kPrefetch) fetch(row + gridDim.x);
   for (int i = lane; i < 256; i += 32) s_hist[warp][i] = 0;
   if (tid == 0) {
     s_prefix = 0;
