@@ -1070,6 +1070,7 @@ int launch(const fdma_bwd_params& bp, const BwdPlan& pl, cudaStream_t stream) {
 
 bool tc_bwd_supported(const fdma_bwd_params& bp) {
   const fdma_fwd_params& p = bp.f;
+  if (p.d == 256) return tc_bwd256_supported(bp);
   if (!tc_fwd_supported(p)) return false;
   if (p.d != kD) return false;
   if (p.h_k > 65535) return false;
@@ -1090,9 +1091,12 @@ bool tc_bwd_supported(const fdma_bwd_params& bp) {
   return true;
 }
 
-size_t tc_bwd_workspace_bytes(const fdma_bwd_params& p) { return plan(p).total; }
+size_t tc_bwd_workspace_bytes(const fdma_bwd_params& p) {
+  return p.f.d == 256 ? tc_bwd256_workspace_bytes(p) : plan(p).total;
+}
 
 int tc_bwd(const fdma_bwd_params& p, cudaStream_t stream) {
+  if (p.f.d == 256) return tc_bwd256(p, stream);
   const BwdPlan pl = plan(p);
   return p.f.dtype == FDMA_BF16 ? launch<true>(p, pl, stream) : launch<false>(p, pl, stream);
 }

@@ -25,6 +25,11 @@ int tc_fwd(const fdma_fwd_params& p, cudaStream_t stream);
 // Per-tile mask activity map for per-query masks: act[b][h_mask][ceil(Sq/128)][ceil(Sk/128)] bytes.
 int launch_tile_activity(const fdma_fwd_params& p, uint8_t* act, cudaStream_t stream);
 
+// head dim 256, row-broadcast mask / bias (fdma_bwd256_sm100.cu); reached through the three tc_bwd entry points
+bool tc_bwd256_supported(const fdma_bwd_params& p);
+size_t tc_bwd256_workspace_bytes(const fdma_bwd_params& p);
+int tc_bwd256(const fdma_bwd_params& p, cudaStream_t stream);
+
 bool tc_bwd_supported(const fdma_bwd_params& p);
 size_t tc_bwd_workspace_bytes(const fdma_bwd_params& p);
 int tc_bwd(const fdma_bwd_params& p, cudaStream_t stream);

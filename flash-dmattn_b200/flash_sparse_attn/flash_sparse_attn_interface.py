@@ -74,14 +74,13 @@ def _compaction_capacity(query, key, attn_mask, attn_bias, softcap, return_attn_
 
 def _kernel_head_dim(d: int, needs_grad: bool) -> int:
     """Head dim the tensor-core kernels run this call at: the forward kernels exist for 64, 128 and 256, the backward
-    kernel for 128. Smaller head dims are zero-padded up to the next of these (zero columns change neither the scores
-    nor the kept columns of the results; the reference likewise runs every head dim on the next larger kernel,
-    csrc/flash_sparse_attn/src/static_switch.h:60-82). Head dims the padded route cannot serve keep their
-    size and run on the CUDA-core kernels."""
+    kernels for 128 and 256. Other head dims are zero-padded up to the next of these (zero columns change neither the
+    scores nor the kept columns of the results; the reference likewise runs every head dim on the next larger kernel,
+    csrc/flash_sparse_attn/src/static_switch.h:60-82)."""
     if _kernel_path != _lib.PATH_AUTO:
         return d
     if needs_grad:
-        return 128 if d <= 128 else d
+        return 128 if d <= 128 else (256 if d <= 256 else d)
     for target in (64, 128, 256):
         if d <= target:
             return target

@@ -213,12 +213,30 @@ def test_tcgen05_backward_fp16_and_run_to_run_spread(dev, kernel_path):
     assert torch.equal(a[2], b[2]) and torch.equal(a[3], b[3])  # dK, dV have a fixed accumulation order
 
 
+TC_BWD256_CASES = [
+    ((1, 384, 640, 4, 1, 256), "bcast", "topk", 200, True),     # MQA as in BASELINE config 5, Sq < Sk
+    ((2, 300, 300, 4, 2, 256), "bcast", "block", 100, True),    # ragged, GQA, whole key tiles without a kept key
+    ((1, 256, 256, 2, 2, 256), "bcast", "topk", 64, False),     # MHA, non-causal
+    ((1, 640, 128, 2, 1, 256), "none", "none", 0, True),        # Sq > Sk, neither mask nor bias
+    ((1, 1024, 1024, 8, 1, 256), "bcast", "topk", 300, True),   # 8 key tiles x 16 query tiles x 8 heads: split grid
+    ((1, 200, 520, 2, 1, 256), "none", "topk", 130, False),     # mask only, no dBias
+]
+
+
+@pytest.mark.parametrize("geom,bias_kind,mask_kind,window,causal", TC_BWD256_CASES)
+def test_tcgen05_backward_head_dim_256(dev, kernel_path, geom, bias_kind, mask_kind, window, causal):
+    """Head dim 256: two-pass backward kernel (dV + dQ + dBias, then dK) for row-broadcast masks and biases."""
+    kernel_path("tcgen05")
+    case = build_case(dev, *geom, bias_kind, mask_kind, window, torch.bfloat16)
+    compare_all(case, causal, torch.bfloat16)
+
+
 PADDED_DIM_CASES = [
     ((1, 256, 256, 2, 1, 64), "bcast", "topk", 128, True),      # BASELINE config 1 geometry: d=64 trains at 128
     ((2, 200, 333, 4, 2, 32), "perq", "randq", 0, True),
     ((1, 300, 300, 3, 3, 96), "perhead", "none", 0, False),
     ((1, 160, 160, 2, 2, 40), "bcast", "topk", 50, True),
-    ((1, 256, 384, 2, 1, 192), "bcast", "topk", 100, True),     # forward at 256, backward on the CUDA-core kernels
+    ((1, 256, 384, 2, 1, 192), "bcast", "topk", 100, True),     # forward and backward at 256
 ]
 
 
@@ -229,7 +247,7 @@ def test_default_path_pads_small_head_dims(dev, geom, bias_kind, mask_kind, wind
     from flash_sparse_attn import flash_sparse_attn_interface as iface
 
     d = geom[-1]
-    assert iface._kernel_head_dim(d, True) == (128 if d <= 128 else d)
+    assert iface._kernel_head_dim(d, True) == (128 if d <= 128 else 256)
     assert iface._kernel_head_dim(d, False) == (64 if d <= 64 else 128 if d <= 128 else 256)
     case = build_case(dev, *geom, bias_kind, mask_kind, window, torch.bfloat16)
     compare_all(case, causal, torch.bfloat16)
