@@ -540,8 +540,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 
 def run_ring(args, rank: int, world: int, local_rank: int):
     """Secondary workload (not the headline line): one long sequence, KV-ring context parallel over all ranks.
-    BASELINE config-5 geometry with head dim 128 instead of 256 (the tcgen05 kernels cover 64 and 128):
-    B=1, S=131072, Hq=16, Hkv=1, top-1024 query-broadcast mask, causal, fwd+bwd with dBias."""
+    BASELINE config 5: B=1, S=131072, Hq=16, Hkv=1, d=256, top-1024 query-broadcast mask, causal, fwd+bwd with
+    dBias."""
     import torch.distributed as dist
 
     from flash_sparse_attn import ring
@@ -552,7 +552,7 @@ def run_ring(args, rank: int, world: int, local_rank: int):
     from flash_sparse_attn import flash_sparse_attn_interface as iface
 
     iface.set_compaction(args.compaction)
-    B, Sr, H, Hk, d, w = 1, args.ring_seq_len, 16, 1, 128, 1024
+    B, Sr, H, Hk, d, w = 1, args.ring_seq_len, 16, 1, args.ring_head_dim, 1024
     g = torch.Generator(device="cpu").manual_seed(7)
     bias_full = torch.randn((B, Hk, 1, Sr), generator=g).to(torch.bfloat16)
     mask_full = create_mask(bias_full.to(dev), None, B, Sr, Sr, w, torch.finfo(torch.bfloat16).min).cpu()
@@ -603,7 +603,7 @@ def run_ring(args, rank: int, world: int, local_rank: int):
         "metric": "fwd+bwd TFLOP/s on kept blocks (KV-ring context parallel)", "value": flops_done / (ms.item() * 1e-3) / 1e12,
         "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms.item(),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"ring: B=1 S={Sr} Hq=16 Hkv=1 d=128 W=1024 causal, bias (1,1,1,S)",
+        "config": {"workload": f"ring: B=1 S={Sr} Hq=16 Hkv=1 d={d} W=1024 causal, bias (1,1,1,S)",
                    "parallelism": f"KV ring over {world} ranks, zig-zag chunks of {Sr // (2 * world)} tokens",
                    "key_compaction": "per chunk pair" if gathered else "off",
                    "flops": ("128x128 tiles of each key chunk's gathered kept keys, per visible chunk pair" if gathered
@@ -754,6 +754,7 @@ def main():
     ap.add_argument("--decode-batch", type=int, default=32)
     ap.add_argument("--mask-rows", type=int, default=65536)
     ap.add_argument("--ring-seq-len", type=int, default=131072)
+    ap.add_argument("--ring-head-dim", type=int, default=256, help="256 = BASELINE config 5; 128 for comparison")
     ap.add_argument("--compaction", default="auto", choices=["auto", "off"],
                     help="auto = the library's default route for this mask (kept keys gathered first); off = full key range")
     ap.add_argument("--no-tile-path", action="store_true", help="skip the full-key-range comparison leg")

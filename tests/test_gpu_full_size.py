@@ -56,8 +56,11 @@ def _gen(dev, B, S, H, Hk, d, bias_rows, window, seed):
 @pytest.mark.parametrize("name,B,S,H,Hk,d,bias_rows,window", [
     ("config3_one_batch_element", 1, 32768, 32, 8, 128, 1, 2048),
     ("config2", 1, 8192, 32, 8, 128, 8192, 1024),
+    ("config5_on_one_gpu", 1, 131072, 16, 1, 256, 1, 1024),
 ])
-def test_properties_at_full_size(dev, name, B, S, H, Hk, d, bias_rows, window):
+def test_properties_at_full_size(dev, compaction_mode, name, B, S, H, Hk, d, bias_rows, window):
+    if name.startswith("config5") and compaction_mode == "off":
+        pytest.skip("317 TFLOP over the full key range: covered at small sizes, run here over the gathered keys only")
     q, k, v, mask, bias, dout = _gen(dev, B, S, H, Hk, d, bias_rows, window, seed=0)
     G = H // Hk
     # rows that see at least one key: causal AND mask

@@ -10,7 +10,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, causal, route):
+def _worker(rank, world, port, causal, route, d):
     import torch.distributed as dist
 
     from flash_sparse_attn import flash_sparse_attn_interface as iface
@@ -25,7 +25,7 @@ def _worker(rank, world, port, causal, route):
     dev = torch.device(f"cuda:{rank}")
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
-        B, H, Hk, d = 1, 4, 1, 128
+        B, H, Hk = 1, 4, 1
         S = 2 * world * 256
         q, k, v, bias, dout = oracle.make_inputs(B, S, S, H, Hk, d, (B, Hk, 1, S), seed=5, dtype=torch.bfloat16)
         mask = oracle.create_mask(bias, None, B, S, S, S // 4, torch.finfo(torch.bfloat16).min)
@@ -49,9 +49,11 @@ def _worker(rank, world, port, causal, route):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("route", ["off", "auto"], ids=["tiles", "compaction"])
-@pytest.mark.parametrize("causal", [True, False])
-def test_ring_two_gpus(causal, route):
+@pytest.mark.parametrize("causal,route,d", [
+    (True, "off", 128), (False, "off", 128), (True, "auto", 128), (False, "auto", 128),
+    (True, "auto", 256),   # BASELINE config 5's head dim: tcgen05 forward and two-pass backward under the ring
+], ids=["causal-tiles", "full-tiles", "causal-compaction", "full-compaction", "causal-compaction-d256"])
+def test_ring_two_gpus(causal, route, d):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
@@ -59,4 +61,4 @@ def test_ring_two_gpus(causal, route):
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
-    mp.spawn(_worker, args=(2, port, causal, route), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, port, causal, route, d), nprocs=2, join=True)
