@@ -41,11 +41,12 @@ S, HQ, HKV, D, WINDOW = 32768, 32, 8, 128, 2048
 WORKLOAD = "S=32768 W=2048 d=128 Hq=32 Hkv=8 causal, bias (B,Hkv,1,Sk), B=1 per GPU"
 
 
-def set_geometry(seq_len: int, window: int):
-    """Smaller sequence lengths exist for profiler captures only; the reported benchmark uses the defaults."""
-    global S, WINDOW, WORKLOAD
-    S, WINDOW = seq_len, window
-    WORKLOAD = f"S={S} W={WINDOW} d=128 Hq=32 Hkv=8 causal, bias (B,Hkv,1,Sk), B=1 per GPU"
+def set_geometry(seq_len: int, window: int, head_dim: int = 128):
+    """Other sequence lengths and head dims exist for profiler captures only; the reported benchmark uses the
+    defaults."""
+    global S, WINDOW, D, WORKLOAD
+    S, WINDOW, D = seq_len, window, head_dim
+    WORKLOAD = f"S={S} W={WINDOW} d={D} Hq=32 Hkv=8 causal, bias (B,Hkv,1,Sk), B=1 per GPU"
 
 
 FWD_TILE, BWD_TILE = (128, 128), (64, 128)
@@ -748,6 +749,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     ap.add_argument("--seq-len", type=int, default=S, help="profiling only: shorter sequence")
     ap.add_argument("--window", type=int, default=WINDOW, help="profiling only: window for --seq-len")
+    ap.add_argument("--head-dim", type=int, default=D, choices=[64, 128, 256], help="profiling only")
     ap.add_argument("--workload", default="sharded", choices=["sharded", "ring", "decode", "mask"],
                     help="sharded = the headline benchmark; ring = single long sequence over a KV ring (needs >= 2 "
                          "ranks); decode = single-query forward over a KV cache (HBM-bound)")
@@ -763,8 +765,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "ours":
         args.warmup = max(args.warmup, 3)
-    if args.seq_len != S or args.window != WINDOW:
-        set_geometry(args.seq_len, args.window)
+    if args.seq_len != S or args.window != WINDOW or args.head_dim != D:
+        set_geometry(args.seq_len, args.window, args.head_dim)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
