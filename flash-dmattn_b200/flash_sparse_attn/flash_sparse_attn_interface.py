@@ -206,8 +206,8 @@ def _flash_sparse_attn_forward(
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     if softcap != 0.0:
         raise NotImplementedError("softcap > 0 is not built into the B200 kernels")
-    if return_softmax:
-        raise NotImplementedError("return_attn_probs=True is not built into the B200 kernels")
+    # return_softmax: the caller gets softmax_lse; the probability matrix itself is never materialised (third result
+    # stays empty), which the reference only offers for testing (interface.py:672-676)
     q, k, v, mask, bias = [maybe_contiguous(x) for x in (q, k, v, mask, bias)]
     _check_inputs(q, k, v, mask, bias)
     lib = _lib.load()
@@ -387,7 +387,8 @@ def flash_sparse_attn_func(
     attn_mask: bool ({B|1}, {H|Hk|1}, {Sq|1}, {Sk|1}), False = masked out; attn_bias: same broadcast rules,
     dtype of query, added to the scaled scores before the softmax. is_causal aligns the causal mask to the
     bottom-right corner (key k visible to query q iff k <= q + Sk - Sq). Rows with no visible key return 0.
-    softmax_scale defaults to d ** -0.5. softcap > 0 and return_attn_probs=True raise NotImplementedError.
+    softmax_scale defaults to d ** -0.5. softcap > 0 raises NotImplementedError. return_attn_probs=True returns
+    (out, softmax_lse (B, H, Sq) fp32, empty tensor): the probability matrix is not materialised.
     Returns out (B, Sq, H, d); gradients flow to query, key, value and attn_bias.
 
     A row-broadcast mask (one keep-set per batch and kv head) is run over its gathered kept keys, which gives the

@@ -336,14 +336,30 @@ def test_golden_config1_through_the_operator(dev, golden_dir):
     assert (ref[0] - gold).abs().max() < 0.1
 
 
+def test_return_attn_probs_gives_lse(dev):
+    """return_attn_probs=True returns (out, softmax_lse, empty): LSE (natural log, (B,H,Sq) fp32) matches the oracle,
+    rows without a visible key report +inf."""
+    from flash_sparse_attn import flash_sparse_attn_func
+
+    q, k, v, mask, bias, _ = build_case(dev, 1, 300, 420, 4, 2, 128, "bcast", "topk", 90, torch.bfloat16)
+    mask = mask.clone()
+    mask[:, 1] = False  # the query heads of kv head 1 see nothing
+    out, lse, probs = flash_sparse_attn_func(q, k, v, attn_mask=mask, attn_bias=bias, is_causal=True,
+                                             return_attn_probs=True)
+    ref_out, ref_lse = oracle.attention_forward(q, k, v, mask, bias, None, True)
+    check("out", out, ref_out, torch.bfloat16)
+    assert probs.numel() == 0 and lse.shape == (1, 4, 300) and lse.dtype == torch.float32
+    finite = torch.isfinite(ref_lse)
+    assert torch.equal(torch.isposinf(lse.cpu()), torch.isposinf(ref_lse.cpu()))
+    assert (lse.cpu()[finite.cpu()] - ref_lse.cpu()[finite.cpu()]).abs().max() <= 2e-2
+
+
 def test_error_paths_on_device(dev):
     from flash_sparse_attn import flash_sparse_attn_func
 
     q = torch.randn(1, 16, 2, 64, device=dev, dtype=torch.bfloat16)
     with pytest.raises(NotImplementedError):
         flash_sparse_attn_func(q, q, q, softcap=1.0)
-    with pytest.raises(NotImplementedError):
-        flash_sparse_attn_func(q, q, q, return_attn_probs=True)
     with pytest.raises(RuntimeError):
         flash_sparse_attn_func(q, q[:, :, :1].expand(1, 16, 3, 64), q)
     with pytest.raises(RuntimeError):
