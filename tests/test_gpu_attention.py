@@ -220,7 +220,16 @@ TC_BWD256_CASES = [
     ((1, 640, 128, 2, 1, 256), "none", "none", 0, True),        # Sq > Sk, neither mask nor bias
     ((1, 1024, 1024, 8, 1, 256), "bcast", "topk", 300, True),   # 8 key tiles x 16 query tiles x 8 heads: split grid
     ((1, 200, 520, 2, 1, 256), "none", "topk", 130, False),     # mask only, no dBias
+    ((2, 130, 130, 16, 2, 256), "bcast", "topk", 40, True),     # batch of 2, groups of 8, ragged query tile
+    ((1, 1, 700, 8, 2, 256), "bcast", "topk", 100, False),      # single query row
+    ((1, 2048, 256, 2, 1, 256), "b1h1", "none", 0, True),       # 2 key tiles x 32 query tiles: 64 splits; Sq > Sk
 ]
+
+
+def test_tcgen05_backward_head_dim_256_fp16(dev, kernel_path):
+    kernel_path("tcgen05")
+    case = build_case(dev, 1, 256, 384, 4, 2, 256, "bcast", "topk", 100, torch.float16)
+    compare_all(case, True, torch.float16)
 
 
 @pytest.mark.parametrize("geom,bias_kind,mask_kind,window,causal", TC_BWD256_CASES)
