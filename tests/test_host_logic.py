@@ -104,3 +104,51 @@ def test_create_mask_argument_errors():
         mask_mod.create_mask(bias, None, 2, 4, 16, 4, -1e30, type="sigmoid")
     with pytest.raises(ValueError, match="block_size"):
         mask_mod.create_mask(bias, None, 2, 4, 16, 4, -1e30, block_size=0)
+
+
+def test_head_dim_routing_and_compaction_eligibility():
+    """Which head dim a call runs at, and which mask shapes take the gathered-keys route (metadata only: the
+    capacity comes from the bound create_mask leaves on its result, never from the device here)."""
+    for d, fwd, bwd in ((32, 64, 128), (64, 64, 128), (72, 128, 128), (128, 128, 128), (136, 256, 256),
+                        (256, 256, 256), (320, 320, 320)):
+        assert iface._kernel_head_dim(d, False) == fwd and iface._kernel_head_dim(d, True) == bwd
+    iface.set_kernel_path("simt")
+    try:
+        assert iface._kernel_head_dim(40, True) == 40  # a forced kernel family keeps the head dim
+    finally:
+        iface.set_kernel_path("auto")
+
+    B, Sq, Sk, H, Hk, d = 2, 256, 4096, 8, 2, 128
+    orig = torch.Tensor.is_cuda
+    torch.Tensor.is_cuda = property(lambda self: True)
+    try:
+        q = torch.empty(B, Sq, H, d, dtype=torch.bfloat16, device="meta")
+        k = torch.empty(B, Sk, Hk, d, dtype=torch.bfloat16, device="meta")
+        bias = torch.empty(B, Hk, 1, Sk, dtype=torch.bfloat16, device="meta")
+
+        def tagged(shape, bound):
+            m = torch.empty(shape, dtype=torch.bool, device="meta")
+            m._fdma_keep_bound = (bound, m._version)
+            return m
+
+        cap = lambda m, b=bias, **kw: iface._compaction_capacity(q, k, m, b, kw.get("softcap"), kw.get("probs"))
+        assert cap(tagged((B, Hk, 1, Sk), 300)) == 384          # rounded up to whole 128-key tiles
+        assert cap(tagged((1, 1, 1, Sk), 1)) == 128
+        assert cap(tagged((B, Hk, 1, Sk), 3500)) is None        # more than 3/4 of the keys kept: tile skipping
+        assert cap(tagged((B, Hk, Sq, Sk), 300)) is None        # per-query mask
+        assert cap(tagged((B, H, 1, Sk), 300)) is None          # one row per QUERY head: K/V cannot be shared
+        assert cap(tagged((B, Hk, 1, Sk), 300), torch.empty(B, Hk, Sq, Sk, dtype=torch.bfloat16, device="meta")) is None
+        assert cap(tagged((B, Hk, 1, Sk), 300), None) == 384
+        assert cap(tagged((B, Hk, 1, Sk), 300), probs=True) is None
+        assert cap(None) is None
+        q1 = torch.empty(B, 1, H, d, dtype=torch.bfloat16, device="meta")
+        assert iface._compaction_capacity(q1, k, tagged((B, Hk, 1, Sk), 300), bias, None, None) is None  # decode
+        iface.set_compaction("off")
+        try:
+            assert cap(tagged((B, Hk, 1, Sk), 300)) is None
+        finally:
+            iface.set_compaction("auto")
+        with pytest.raises(ValueError):
+            iface.set_compaction("sometimes")
+    finally:
+        torch.Tensor.is_cuda = orig
