@@ -1,6 +1,6 @@
 """Generates tests/golden/*.npz by RUNNING THE REFERENCE'S OWN PYTHON CODE (needs the reference checkout).
 
-    python tests/golden/make_golden.py [/path/to/flash-dmattn checkout]
+    python tests/golden/make_golden.py /path/to/flash-dmattn-checkout
 
 Imported from the reference: `flash_sparse_attn.utils.mask.create_mask` and
 `benchmarks/backward_equivalence.py::dynamic_mask_attention_python` (its eager forward+backward). Every case
@@ -15,7 +15,9 @@ import sys
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) != 2:
+    sys.exit("usage: python tests/golden/make_golden.py /path/to/flash-dmattn-checkout")
+REF = sys.argv[1]
 sys.path.insert(0, REF)
 sys.path.insert(0, os.path.join(REF, "benchmarks"))
 with contextlib.redirect_stdout(io.StringIO()):
