@@ -489,7 +489,8 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
     const bool direct_group = mode == kDbDirect && p.dbias_h != p.h;  // one dbias head per kv head
     uint16_t* dbias16 = reinterpret_cast<uint16_t*>(p.dbias);
     // Row-broadcast bias / mask that do not depend on the query head: one value per thread for the whole CTA.
-    const bool hoist = kBcast && (G == 1 || ((!p.bias || p.h_bias != p.h) && (!p.mask || p.h_mask != p.h)));
+    const bool group_inv = G == 1 || ((!p.bias || p.h_bias != p.h) && (!p.mask || p.h_mask != p.h));
+    const bool hoist = kBcast && group_inv;
     // mask / bias head of query head h, without integer division (extents are 1, h_k or h)
     auto hm_of = [&](int h) { return p.h_mask == p.h ? h : (p.h_mask == p.h_k ? hk : 0); };
     auto hb_of = [&](int h) { return p.h_bias == p.h ? h : (p.h_bias == p.h_k ? hk : 0); };
@@ -510,6 +511,10 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
     for (int m = m_first; m < M64 && ok; ++m) {
       const int q0 = m * kBM + half * 32;
       bool group_touched = false;
+      // Per-query bias / mask shared by the query heads of the group: the 32 (query, key) addends of this thread are
+      // fetched for the first active head of the query tile and reused by the others.
+      float2 bias2[16];
+      bool bias2_loaded = false;
       for (int g = 0; g < G && ok; ++g) {
         const int h = hk * G + g;
         const bool active = m >= m_start && s_act[(act_g > 1 ? g : 0) * MT + (m >> 1)] != 0;
@@ -528,7 +533,6 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         const bool diag = causal && static_cast<int64_t>(ckey_wmax) > static_cast<int64_t>(q0) + coff;  // warp-uniform
         const bool per_elem = !kBcast || diag;
         float bv = bv_h;
-        float2 bias2[16];
         if (kBcast) {
           if (!hoist) {
             const int hm = hm_of(h), hb = hb_of(h);
@@ -547,6 +551,8 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
                                      ckey - coff > q0 + 2 * j + 1 ? -CUDART_INF_F : bv);
           }
         } else {
+          if (!(group_inv && bias2_loaded)) {
+          bias2_loaded = true;
           const int hm = hm_of(h), hb = hb_of(h);
           const uint16_t* bcol = p.bias ? reinterpret_cast<const uint16_t*>(p.bias) + b * p.bias_batch_stride +
                                               hb * p.bias_head_stride + key
@@ -577,6 +583,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
               if (ckey - coff > q0 + 2 * j) bias2[j].x = -CUDART_INF_F;
               if (ckey - coff > q0 + 2 * j + 1) bias2[j].y = -CUDART_INF_F;
             }
+          }
           }
         }
         // LSE*log2e and D of the step's 64 queries arrive in shared memory with the Q/dO stage
