@@ -691,6 +691,55 @@ def run_decode(args, rank: int, world: int, local_rank: int):
     print(json.dumps(line), flush=True)
 
 
+def run_perquery(args, rank: int, world: int, local_rank: int):
+    """Secondary workload (not the headline line): BASELINE config 2, per-query bias and mask. B=1, S=8192, Hq=32,
+    Hkv=8, d=128, bias (B,Hkv,Sq,Sk) ~ N(0,1), mask = top-1024 per query row AND causal, fwd+bwd with a per-query
+    dBias, through the C ABI on device-resident tensors. FLOPs on 128x128 (forward) / 64x128 (backward) tiles that
+    hold a kept, causally visible element."""
+    from flash_sparse_attn import _lib
+    from flash_sparse_attn.utils.mask import create_mask
+
+    if rank != 0:
+        return
+    dev = torch.device(f"cuda:{local_rank}")
+    torch.cuda.set_device(dev)
+    lib = _lib.load()
+    B, Sq, w = 1, 8192, 1024
+    g = torch.Generator(device=dev).manual_seed(99)
+    rnd = lambda *shape: torch.randn(shape, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    q, k, v = rnd(B, Sq, HQ, D), rnd(B, Sq, HKV, D), rnd(B, Sq, HKV, D)
+    bias, dout = rnd(B, HKV, Sq, Sq), rnd(B, Sq, HQ, D)
+    mask = create_mask(bias, None, B, Sq, Sq, w, torch.finfo(torch.bfloat16).min)
+    vis = mask & torch.ones(Sq, Sq, dtype=torch.bool, device=dev).tril()
+    G = HQ // HKV
+    tiles_f = int(vis.view(B, HKV, Sq // 128, 128, Sq // 128, 128).any(dim=5).any(dim=3).sum().item()) * G
+    tiles_b = int(vis.view(B, HKV, Sq // 64, 64, Sq // 128, 128).any(dim=5).any(dim=3).sum().item()) * G
+    del vis
+    flops = 4 * D * 128 * 128 * tiles_f + 10 * D * 64 * 128 * tiles_b
+    stream = torch.cuda.current_stream(dev)
+    step = AttentionStep(lib, dev, q, k, v, mask, bias, dout, False)
+    for _ in range(max(args.warmup, 3)):
+        step()
+    ms_total, fwd_ms, bwd_ms, _ = time_steps(step, args.steps, stream, lambda: torch.cuda.synchronize(dev))
+    _lib.check(lib.fdma_last_kernel_status(stream.cuda_stream, None), "kernel status")
+    ms = ms_total / args.steps
+    peak, peak_src = load_peaks()
+    bwd_tf = 10 * D * 64 * 128 * tiles_b / (bwd_ms * 1e-3) / 1e12
+    line = {
+        "metric": "fwd+bwd TFLOP/s on kept blocks (per-query bias and mask)", "value": flops / (ms * 1e-3) / 1e12,
+        "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"per-query: B=1 S={Sq} Hq={HQ} Hkv={HKV} d={D} W={w} causal, bias and mask (B,Hkv,Sq,Sk)",
+                   "l2": "bias (1 GiB) and mask (0.5 GiB) are larger than L2",
+                   "tiles": {"fwd": list(FWD_TILE), "bwd": list(BWD_TILE)}},
+        "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
+        "roofline": {"bound": "tensor", "kernel": "bwd_kernel", "achieved": bwd_tf, "peak": peak, "unit": "TFLOP/s",
+                     "frac": bwd_tf / peak, "peak_source": "of " + peak_src, "traffic": None},
+        "gpu_launches": args.steps * 5,  # tile_activity x2, fwd_kernel, bwd_prep, bwd_kernel (+ convert_dq)
+    }
+    print(json.dumps(line), flush=True)
+
+
 def run_mask(args, rank: int, world: int, local_rank: int):
     """Secondary workload (not the headline line): create_mask alone at BASELINE config 2's size, 65536 rows (B=1,
     Hkv=8, Sq=8192) x 8192 keys of bf16 bias, top-1024 per row. HBM-bound: GB/s of bias bytes read + mask bytes
@@ -750,7 +799,7 @@ def main():
     ap.add_argument("--seq-len", type=int, default=S, help="profiling only: shorter sequence")
     ap.add_argument("--window", type=int, default=WINDOW, help="profiling only: window for --seq-len")
     ap.add_argument("--head-dim", type=int, default=D, choices=[64, 128, 256], help="profiling only")
-    ap.add_argument("--workload", default="sharded", choices=["sharded", "ring", "decode", "mask"],
+    ap.add_argument("--workload", default="sharded", choices=["sharded", "ring", "decode", "mask", "perquery"],
                     help="sharded = the headline benchmark; ring = single long sequence over a KV ring (needs >= 2 "
                          "ranks); decode = single-query forward over a KV cache (HBM-bound)")
     ap.add_argument("--decode-batch", type=int, default=32)
@@ -785,6 +834,8 @@ def main():
             run_decode(args, rank, world, local_rank)
         elif args.workload == "mask":
             run_mask(args, rank, world, local_rank)
+        elif args.workload == "perquery":
+            run_perquery(args, rank, world, local_rank)
         else:
             run_ours(args, rank, world, local_rank)
     finally:
