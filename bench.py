@@ -565,8 +565,13 @@ def run_ring(args, rank: int, world: int, local_rank: int):
     bias = ring.zigzag_split(bias_full, 3, rank, world).contiguous().to(dev).requires_grad_(True)
     mask = ring.zigzag_split(mask_full, 3, rank, world).contiguous().to(dev)
 
+    from flash_sparse_attn import gathered_cp
+
     def step():
-        out = ring.ring_flash_sparse_attn_func(q, k, v, mask, bias, None, True)
+        if args.cp_scheme == "gathered":
+            out = gathered_cp.gathered_cp_flash_sparse_attn_func(q, k, v, mask, bias, None, True)
+        else:
+            out = ring.ring_flash_sparse_attn_func(q, k, v, mask, bias, None, True)
         out.backward(dout)
         q.grad = k.grad = v.grad = bias.grad = None
 
@@ -589,7 +594,7 @@ def run_ring(args, rank: int, world: int, local_rank: int):
     C = Sr // (2 * world)
     kept_per_chunk = mask_full.reshape(B, Hk, 2 * world, C).sum(-1)
     cap = max(128, (int(kept_per_chunk.max()) + 127) // 128 * 128)
-    gathered = args.compaction == "auto" and 4 * cap <= 3 * C
+    gathered = args.compaction == "auto" and 4 * cap <= 3 * C and args.cp_scheme == "ring"
     tiles = 0
     if gathered:
         for b in range(B):
@@ -600,14 +605,20 @@ def run_ring(args, rank: int, world: int, local_rank: int):
                     tiles += (H // Hk) * ((2 * world - 1 - kc) * (C // 128) * n_kt +
                                           kept_tiles_rowbcast(row, C, C, 128, 128, True, True))
     flops_done = 14 * d * 128 * 128 * tiles if gathered else fl["canonical_128x128"]
+    if args.cp_scheme == "gathered":  # every query chunk runs over ALL gathered keys of the sequence at once
+        flops_done = count_flops(mask_full, B, Sr, Sr, H, Hk, d, True, True)["canonical_128x128"]
     line = {
         "metric": "fwd+bwd TFLOP/s on kept blocks (KV-ring context parallel)", "value": flops_done / (ms.item() * 1e-3) / 1e12,
         "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms.item(),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"ring: B=1 S={Sr} Hq=16 Hkv=1 d={d} W=1024 causal, bias (1,1,1,S)",
-                   "parallelism": f"KV ring over {world} ranks, zig-zag chunks of {Sr // (2 * world)} tokens",
-                   "key_compaction": "per chunk pair" if gathered else "off",
-                   "flops": ("128x128 tiles of each key chunk's gathered kept keys, per visible chunk pair" if gathered
+                   "parallelism": (f"kept K/V rows all-reduced over {world} ranks, zig-zag query chunks of "
+                                   f"{Sr // (2 * world)} tokens" if args.cp_scheme == "gathered" else
+                                   f"KV ring over {world} ranks, zig-zag chunks of {Sr // (2 * world)} tokens"),
+                   "key_compaction": ("whole sequence" if args.cp_scheme == "gathered" else
+                                      "per chunk pair" if gathered else "off"),
+                   "flops": ("128x128 tiles of the sequence's gathered kept keys" if args.cp_scheme == "gathered" else
+                             "128x128 tiles of each key chunk's gathered kept keys, per visible chunk pair" if gathered
                              else "kept 128x128 tiles of the global mask")},
         "tflops_on_full_range_kept_tiles": fl["canonical_128x128"] / (ms.item() * 1e-3) / 1e12,
     }
@@ -806,6 +817,8 @@ def main():
     ap.add_argument("--mask-rows", type=int, default=65536)
     ap.add_argument("--ring-seq-len", type=int, default=131072)
     ap.add_argument("--ring-head-dim", type=int, default=256, help="256 = BASELINE config 5; 128 for comparison")
+    ap.add_argument("--cp-scheme", default="ring", choices=["ring", "gathered"],
+                    help="--workload ring: rotate K/V chunks (ring) or all-reduce the kept K/V rows (gathered)")
     ap.add_argument("--compaction", default="auto", choices=["auto", "off"],
                     help="auto = the library's default route for this mask (kept keys gathered first); off = full key range")
     ap.add_argument("--no-tile-path", action="store_true", help="skip the full-key-range comparison leg")

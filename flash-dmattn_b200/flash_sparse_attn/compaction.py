@@ -20,7 +20,8 @@ import torch
 from . import _lib
 from .flash_sparse_attn_interface import (_bsh, _check_inputs, _dtype_code, _fill_fwd, _stream_ptr, round_multiple)
 
-__all__ = ["CompactKeys", "compact_keys", "compact_forward", "compact_backward", "flash_sparse_attn_compact_func"]
+__all__ = ["CompactKeys", "compact_keys", "index_kept_keys", "gather_kept_keys", "scatter_kept_rows",
+           "compact_forward", "compact_backward", "flash_sparse_attn_compact_func"]
 
 _TILE = 128
 
@@ -88,11 +89,19 @@ def compact_keys(key: torch.Tensor, value: torch.Tensor, attn_mask: torch.Tensor
     multiple of 128); when omitted it is taken from the fullest mask row, which costs one device synchronisation.
     A row with more kept keys than `capacity` raises; that check reads the counts back (one synchronisation) and is
     skipped with check_capacity=False, for callers that know the bound holds."""
-    lib = _lib.load()
     B, Sk, Hk, d = key.shape
     m = _row_mask(attn_mask, B, Hk, Sk)
-    Bm, Hm = m.shape[0], m.shape[1]
-    dev = key.device
+    key_pos, count, mask_c = index_kept_keys(m, capacity, check_capacity)
+    k_c, v_c, bias_c = gather_kept_keys(key, value, attn_bias, key_pos)
+    return CompactKeys(k_c, v_c, mask_c, bias_c, key_pos, count, Sk)
+
+
+def index_kept_keys(m: torch.Tensor, capacity: Optional[int] = None, check_capacity: bool = True):
+    """m: bool (Bm, Hm, Sk), keys contiguous. Returns key_pos (Bm,Hm,Wp) int32 (ascending positions of the kept
+    keys, INT32_MAX in unused slots), count (Bm,Hm) int32 and the compact mask (Bm,Hm,1,Wp)."""
+    lib = _lib.load()
+    Bm, Hm, Sk = m.shape
+    dev = m.device
     with torch.cuda.device(dev):
         if capacity is None:
             capacity = int(m.sum(dim=-1, dtype=torch.int32).max().item())
@@ -108,6 +117,17 @@ def compact_keys(key: torch.Tensor, value: torch.Tensor, attn_mask: torch.Tensor
         _lib.check(lib.fdma_compact_index(ctypes.byref(cp), _stream_ptr(dev)), "fdma_compact_index")
         if check_capacity and int(count.max().item()) > cap:
             raise RuntimeError(f"a mask row keeps more than capacity={cap} keys")
+    return key_pos, count, mask_c
+
+
+def gather_kept_keys(key, value, attn_bias, key_pos):
+    """K, V (B,Sk,Hk,d) and bias ({B|1},{H|Hk|1},1,Sk) rows at key_pos (Bm,Hm,Wp) -> (B,Wp,Hk,d) x 2 and
+    (Bc,Hc,1,Wp); slots whose position lies outside [0, Sk) come out as zeros."""
+    lib = _lib.load()
+    B, Sk, Hk, d = key.shape
+    cap = key_pos.shape[-1]
+    dev = key.device
+    with torch.cuda.device(dev):
         key = key if key.stride(-1) == 1 else key.contiguous()
         value = value if value.stride(-1) == 1 else value.contiguous()
         k_c = torch.empty((B, cap, Hk, d), dtype=key.dtype, device=dev)
@@ -123,19 +143,40 @@ def compact_keys(key: torch.Tensor, value: torch.Tensor, attn_mask: torch.Tensor
             sr = 0 if attn_bias.shape[3] == 1 else attn_bias.stride(3)
             _rows_call(lib.fdma_gather_rows, attn_bias, bias_c, key_pos, Bc, Hc, Sk, cap, 1, (sb, sr, sh),
                        (bias_c.stride(0), 1, bias_c.stride(1)), dev)
-    return CompactKeys(k_c, v_c, mask_c, bias_c, key_pos, count, Sk)
+    return k_c, v_c, bias_c
 
 
-def _set_positions(p, ck: CompactKeys, seqlen_q: int):
+def scatter_kept_rows(src_c: torch.Tensor, key_pos: torch.Tensor, rows_full: int, bias_layout: bool = False) -> torch.Tensor:
+    """Inverse of the gather for gradients: src_c (B,Wp,Hk,d) -> (B,rows_full,Hk,d), or with bias_layout
+    (Bc,Hc,1,Wp) -> (Bc,Hc,1,rows_full); rows that no slot points at are zero."""
+    lib = _lib.load()
+    dev = src_c.device
+    cap = key_pos.shape[-1]
+    with torch.cuda.device(dev):
+        if bias_layout:
+            Bc, Hc = src_c.shape[0], src_c.shape[1]
+            full = torch.empty((Bc, Hc, 1, rows_full), dtype=src_c.dtype, device=dev)
+            _rows_call(lib.fdma_scatter_rows, src_c, full, key_pos, Bc, Hc, rows_full, cap, 1,
+                       (src_c.stride(0), 1, src_c.stride(1)), (full.stride(0), 1, full.stride(1)), dev)
+            return full
+        B, _, Hk, d = src_c.shape
+        full = torch.empty((B, rows_full, Hk, d), dtype=src_c.dtype, device=dev)
+        _rows_call(lib.fdma_scatter_rows, src_c, full, key_pos, B, Hk, rows_full, cap, d, _bsh(src_c), _bsh(full), dev)
+        return full
+
+
+def _set_positions(p, ck: CompactKeys, seqlen_q: int, causal_shift: Optional[int] = None):
     p.key_pos = ck.key_pos.data_ptr()
     p.key_pos_batch_stride = 0 if ck.key_pos.shape[0] == 1 else ck.key_pos.stride(0)
     p.key_pos_head_stride = ck.key_pos.stride(1)
     p.h_pos = ck.key_pos.shape[1]
-    p.causal_shift = ck.seqlen_k - seqlen_q
+    p.causal_shift = ck.seqlen_k - seqlen_q if causal_shift is None else causal_shift
 
 
-def compact_forward(q: torch.Tensor, ck: CompactKeys, softmax_scale: float, is_causal: bool):
-    """Forward over gathered keys: returns (out (B,Sq,H,d), lse (B,H,Sq) fp32)."""
+def compact_forward(q: torch.Tensor, ck: CompactKeys, softmax_scale: float, is_causal: bool,
+                    causal_shift: Optional[int] = None):
+    """Forward over gathered keys: returns (out (B,Sq,H,d), lse (B,H,Sq) fp32). Key slot k is visible to query row
+    i iff key_pos[k] <= i + causal_shift (default: the bottom-right alignment, seqlen_k - seqlen_q)."""
     lib = _lib.load()
     _check_inputs(q, ck.key, ck.value, ck.mask, ck.bias)
     B, Sq, H, d = q.shape
@@ -145,7 +186,7 @@ def compact_forward(q: torch.Tensor, ck: CompactKeys, softmax_scale: float, is_c
         lse = torch.empty((B, H, Sq), dtype=torch.float32, device=dev)
         p = _lib.FwdParams()
         _fill_fwd(p, q, ck.key, ck.value, ck.mask, ck.bias, out, lse, softmax_scale, is_causal)
-        _set_positions(p, ck, Sq)
+        _set_positions(p, ck, Sq, causal_shift)
         ws_bytes = lib.fdma_fwd_workspace_bytes(ctypes.byref(p))
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev) if ws_bytes else None
         if ws is not None:
@@ -155,9 +196,10 @@ def compact_forward(q: torch.Tensor, ck: CompactKeys, softmax_scale: float, is_c
 
 
 def compact_backward(dout, q, ck: CompactKeys, out, lse, softmax_scale: float, is_causal: bool, k_shape,
-                     bias_shape=None):
+                     bias_shape=None, causal_shift: Optional[int] = None, scatter: bool = True):
     """Backward over gathered keys, gradients scattered back to full shapes: returns dq, dk, dv (shape k_shape) and
-    dbias (shape bias_shape, or None). Dimensions the bias broadcast over are summed."""
+    dbias (shape bias_shape, or None). Dimensions the bias broadcast over are summed. scatter=False returns the
+    gradients of the gathered tensors themselves (dq, dk_c, dv_c, dbias_c)."""
     lib = _lib.load()
     k_c, v_c, mask_c, bias_c, key_pos, Sk = ck.key, ck.value, ck.mask, ck.bias, ck.key_pos, ck.seqlen_k
     B, Sq, H, d = q.shape
@@ -170,7 +212,7 @@ def compact_backward(dout, q, ck: CompactKeys, out, lse, softmax_scale: float, i
         dbias_c = torch.empty_like(bias_c) if bias_c is not None else None
         bp = _lib.BwdParams()
         _fill_fwd(bp.f, q, k_c, v_c, mask_c, bias_c, out, lse, softmax_scale, is_causal)
-        _set_positions(bp.f, ck, Sq)
+        _set_positions(bp.f, ck, Sq, causal_shift)
         bp.dout = dout.data_ptr()
         bp.do_batch_stride, bp.do_row_stride, bp.do_head_stride = _bsh(dout)
         bp.dq, bp.dk, bp.dv = dq.data_ptr(), dk_c.data_ptr(), dv_c.data_ptr()
@@ -186,6 +228,8 @@ def compact_backward(dout, q, ck: CompactKeys, out, lse, softmax_scale: float, i
         if ws is not None:
             bp.f.workspace, bp.f.workspace_bytes = ws.data_ptr(), ws_bytes
         _lib.check(lib.fdma_bwd(ctypes.byref(bp), _stream_ptr(dev)), "fdma_bwd")
+        if not scatter:
+            return dq, dk_c, dv_c, dbias_c
         dk = torch.empty(k_shape, dtype=q.dtype, device=dev)
         dv = torch.empty(k_shape, dtype=q.dtype, device=dev)
         for src, dst in ((dk_c, dk), (dv_c, dv)):

@@ -10,7 +10,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, causal, route, d):
+def _worker(rank, world, port, causal, route, d, scheme="ring"):
     import torch.distributed as dist
 
     from flash_sparse_attn import flash_sparse_attn_interface as iface
@@ -33,7 +33,12 @@ def _worker(rank, world, port, causal, route, d):
         loc = lambda t, dim: ring.zigzag_split(t, dim, rank, world).contiguous().to(dev)
         ql, kl, vl = (loc(t, 1).requires_grad_(True) for t in (q, k, v))
         bl = loc(bias, 3).requires_grad_(True)
-        out = ring.ring_flash_sparse_attn_func(ql, kl, vl, loc(mask, 3), bl, None, causal)
+        if scheme == "ring":
+            out = ring.ring_flash_sparse_attn_func(ql, kl, vl, loc(mask, 3), bl, None, causal)
+        else:
+            from flash_sparse_attn import gathered_cp
+
+            out = gathered_cp.gathered_cp_flash_sparse_attn_func(ql, kl, vl, loc(mask, 3), bl, None, causal)
         out.backward(loc(dout, 1))
 
         def gather(t, dim):
@@ -62,3 +67,16 @@ def test_ring_two_gpus(causal, route, d):
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     mp.spawn(_worker, args=(2, port, causal, route, d), nprocs=2, join=True)
+
+
+@pytest.mark.parametrize("causal,d", [(True, 128), (False, 128), (True, 256)])
+def test_gathered_keys_context_parallel_two_gpus(causal, d):
+    """The same check for the gathered-keys scheme (all-reduce of the kept K/V rows instead of a ring)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_worker, args=(2, port, causal, "auto", d, "gathered"), nprocs=2, join=True)
