@@ -608,7 +608,9 @@ def run_ring(args, rank: int, world: int, local_rank: int):
     if args.cp_scheme == "gathered":  # every query chunk runs over ALL gathered keys of the sequence at once
         flops_done = count_flops(mask_full, B, Sr, Sr, H, Hk, d, True, True)["canonical_128x128"]
     line = {
-        "metric": "fwd+bwd TFLOP/s on kept blocks (KV-ring context parallel)", "value": flops_done / (ms.item() * 1e-3) / 1e12,
+        "metric": ("fwd+bwd TFLOP/s on kept blocks (gathered-keys context parallel)" if args.cp_scheme == "gathered"
+                   else "fwd+bwd TFLOP/s on kept blocks (KV-ring context parallel)"),
+        "value": flops_done / (ms.item() * 1e-3) / 1e12,
         "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms.item(),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"ring: B=1 S={Sr} Hq=16 Hkv=1 d={d} W=1024 causal, bias (1,1,1,S)",
