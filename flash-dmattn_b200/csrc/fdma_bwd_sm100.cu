@@ -41,7 +41,7 @@ enum DbiasMode { kDbNone = 0, kDbColsum = 1, kDbDirect = 2, kDbAtomic = 3 };
 
 enum WaitCode {
   kWaitKv = 201, kWaitQdoEmpty = 202, kWaitQdoFull = 203, kWaitSFull = 204, kWaitDpFull = 205, kWaitPds = 206,
-  kWaitDqFull = 207, kWaitDqEmpty = 208, kWaitDsEmpty = 209, kWaitFinal = 210
+  kWaitDqFull = 207, kWaitDqEmpty = 208, kWaitDpFree = 209, kWaitFinal = 210
 };
 
 struct BwdKernelParams {
@@ -88,7 +88,7 @@ struct SmemB {
   static constexpr int kDqOff = kLdOff + kQStages * kLdBytes;      // [32 q][128 d] fp32 staging tile of the dQ writer
   static constexpr int kRedOff = kDqOff + 32 * kD * 4;
   static constexpr int kBarOff = kRedOff + kBN * 4;
-  static constexpr int kNumBars = 1 + 2 * kQStages + 2 + 1 + 1 + 1 + 1 + 2 + 1;
+  static constexpr int kNumBars = 1 + 2 * kQStages + 2 + 2 + 1 + 1 + 1 + 1;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kTotal = kMiscOff + 32;
   static constexpr int kAlloc = kTotal + 1024;
@@ -207,6 +207,11 @@ __device__ __forceinline__ uint16_t float_to_raw16(float x) {
 template <bool kBf16, bool kBcast>
 __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant__ BwdKernelParams p) {
   using L = SmemB;
+  // Row-broadcast kernel: the two softmax warpgroups are two teams that take alternate steps (all 64 queries of
+  // a step, in two passes of 32), so the fixed latencies of one team's step -- barrier round trips, TMEM loads and
+  // stores, the hand-over to the MMA warp -- overlap the other team's arithmetic. Per-query kernel: both warpgroups
+  // work on every step, 32 queries each.
+  constexpr bool kTeams = kBcast;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) &
                                                          ~static_cast<uintptr_t>(1023));
@@ -221,13 +226,12 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
   uint64_t* bar_kv = bars;
   uint64_t* bar_qdo_full = bars + 1;
   uint64_t* bar_qdo_empty = bar_qdo_full + kQStages;
-  uint64_t* bar_s_full = bar_qdo_empty + kQStages;  // [2]
-  uint64_t* bar_dp_full = bar_s_full + 2;
-  uint64_t* bar_pds = bar_dp_full + 1;
-  uint64_t* bar_dq_full = bar_pds + 1;
+  uint64_t* bar_dp_full = bar_qdo_empty + kQStages;
+  uint64_t* bar_pds = bar_dp_full + 2;              // bar_dp_full: [2], by step parity
+  uint64_t* bar_dq_full = bar_pds + 2;              // bar_pds: [2], one per softmax team (broadcast kernel)
   uint64_t* bar_dq_empty = bar_dq_full + 1;
-  uint64_t* bar_ds_empty = bar_dq_empty + 1;        // [2]
-  uint64_t* bar_final = bar_ds_empty + 2;
+  uint64_t* bar_dp_free = bar_dq_empty + 1;
+  uint64_t* bar_final = bar_dp_free + 1;
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + L::kMiscOff);
   volatile int* s_abort = reinterpret_cast<volatile int*>(smem + L::kMiscOff + 4);
   int* s_nsteps = reinterpret_cast<int*>(smem + L::kMiscOff + 8);
@@ -273,14 +277,13 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
       mbar_init(bar_qdo_full + i, 1);
       mbar_init(bar_qdo_empty + i, 1);
     }
-    mbar_init(bar_s_full + 0, 1);
-    mbar_init(bar_s_full + 1, 1);
-    mbar_init(bar_dp_full, 1);
-    mbar_init(bar_pds, 256);
+    mbar_init(bar_dp_full + 0, 1);
+    mbar_init(bar_dp_full + 1, 1);
+    mbar_init(bar_pds + 0, kTeams ? 4 : 8);  // one arrival per softmax warp that works on the step
+    mbar_init(bar_pds + 1, kTeams ? 4 : 8);
     mbar_init(bar_dq_full, 1);
-    mbar_init(bar_dq_empty, 128);
-    mbar_init(bar_ds_empty + 0, 1);
-    mbar_init(bar_ds_empty + 1, 1);
+    mbar_init(bar_dq_empty, 4);   // one arrival per dQ-writer warp
+    mbar_init(bar_dp_free, kTeams ? 4 : 8);
     mbar_init(bar_final, 1);
     fence_mbar_init();
   }
@@ -391,9 +394,8 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
             umma_ss(tmem_base + kColSt + (step & 1) * kBM, umma_desc_sw128(k_addr + ko, 16, 1024),
                     umma_desc_sw128(qa + qo, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
           }
-          umma_commit(bar_s_full + (step & 1));
         };
-        auto issue_dp = [&](int step) {  // dPt = V dO^T
+        auto issue_dp = [&](int step) {  // dPt = V dO^T; the commit covers S of the same step, issued just before
           const uint32_t ga = qdo_addr + (step % kQStages) * L::kStageBytes + L::kQBytes;
 #pragma unroll
           for (int kk = 0; kk < kD / 16; ++kk) {
@@ -402,7 +404,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
             umma_ss(tmem_base + kColDp, umma_desc_sw128(v_addr + ko, 16, 1024), umma_desc_sw128(ga + qo, 16, 1024),
                     idesc_s, kk > 0 ? 1u : 0u);
           }
-          umma_commit(bar_dp_full);
+          umma_commit(bar_dp_full + (step & 1));
         };
         FDMA_PROF_BEGIN();
         bool ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(0, mbar_wait(bar_kv, 0, ctl, kWaitKv)));
@@ -418,24 +420,27 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
             tc_fence_after_sync();
             issue_st(1);
           }
+          if (ok) ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(3, mbar_wait(bar_dp_free, 0, ctl, kWaitDpFree)));
+          if (ok) {
+            tc_fence_after_sync();
+            issue_dp(1);
+          }
         }
         for (int i = 0; i < n_steps && ok; ++i) {
-          ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(2, mbar_wait(bar_pds, i & 1, ctl, kWaitPds)));
+          ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(2, mbar_wait(bar_pds + (i & 1), (i >> 1) & 1, ctl, kWaitPds)));
           if (!ok) break;
           tc_fence_after_sync();
           const uint32_t stage_addr = qdo_addr + (i % kQStages) * L::kStageBytes;
           const uint32_t acc = i > 0 ? 1u : 0u;
-          // A operands from TMEM: queries 0-31 sit in columns [0,16) of the St / dPt block, queries 32-63 in
-          // columns [32,48) (each softmax warpgroup writes back into the columns it read).
-          // Order: dK first, because it frees the dPt columns for the next step's dP -- the product the softmax
-          // threads wait for next; dV, dQ and the S of step i+2 follow behind it.
+          // A operands from TMEM, 16-bit pairs: each softmax pass writes back into the 32 columns of the St block it
+          // read -- P^T of queries 0-31 in columns [0,16), their dS^T in [16,32); queries 32-63 in [32,48) and
+          // [48,64). dS^T does not go back into the dPt block, so dP of a later step never waits for the dK product.
 #pragma unroll
           for (int s = 0; s < 4; ++s) {
-            const uint32_t a_col = (s < 2 ? s * 8 : 32 + (s - 2) * 8);
-            umma_ts(tmem_base + kColDk, tmem_base + kColDp + a_col,
+            const uint32_t a_col = 16 + (s < 2 ? s * 8 : 32 + (s - 2) * 8);
+            umma_ts(tmem_base + kColDk, tmem_base + kColSt + (i & 1) * kBM + a_col,
                     umma_desc_sw128(stage_addr + s * 2048, kBM * 128, 1024), idesc_g, (acc || s > 0) ? 1u : 0u);
           }
-          if (i + 1 < n_steps) issue_dp(i + 1);
 #pragma unroll
           for (int s = 0; s < 4; ++s) {
             const uint32_t a_col = (s < 2 ? s * 8 : 32 + (s - 2) * 8);
@@ -456,13 +461,18 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
           }
           umma_commit(bar_dq_full);
           umma_commit(bar_qdo_empty + (i % kQStages));
-          umma_commit(bar_ds_empty + (i & 1));
           if (i + 2 < n_steps) {
             ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(1, mbar_wait(bar_qdo_full + ((i + 2) % kQStages),
                                                                      ((i + 2) / kQStages) & 1, ctl, kWaitQdoFull)));
             if (!ok) break;
             tc_fence_after_sync();
             issue_st(i + 2);
+            // dP of step i+2 goes out two steps ahead as well, as soon as the softmax threads have read dP of step
+            // i+1 out of the (single) dPt block -- which they do at the start of their step, long before this point.
+            ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(3, mbar_wait(bar_dp_free, (i + 1) & 1, ctl, kWaitDpFree)));
+            if (!ok) break;
+            tc_fence_after_sync();
+            issue_dp(i + 2);
           }
         }
         umma_commit(bar_final);
@@ -526,12 +536,14 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
           }
           continue;
         }
+        if (kTeams && (i & 1) != half) {  // the other team's step
+          ++i;
+          continue;
+        }
         group_touched = true;
         // ---- bias (log2 units) for this thread's key; masked elements get -inf, which turns into
         //      P = exp2(-inf) = 0 without any per-element select. Row-broadcast bias: one scalar per thread; the
         //      per-element array is only filled for per-query bias/mask and on tiles that cross the causal limit ----
-        const bool diag = causal && static_cast<int64_t>(ckey_wmax) > static_cast<int64_t>(q0) + coff;  // warp-uniform
-        const bool per_elem = !kBcast || diag;
         float bv = bv_h;
         if (kBcast) {
           if (!hoist) {
@@ -543,12 +555,6 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
               bv = p.bias ? raw16_to_float<kBf16>(reinterpret_cast<const uint16_t*>(
                                 p.bias)[b * p.bias_batch_stride + hb * p.bias_head_stride + key]) * kLog2e
                           : 0.f;
-          }
-          if (diag) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-              bias2[j] = make_float2(ckey - coff > q0 + 2 * j ? -CUDART_INF_F : bv,
-                                     ckey - coff > q0 + 2 * j + 1 ? -CUDART_INF_F : bv);
           }
         } else {
           if (!(group_inv && bias2_loaded)) {
@@ -577,7 +583,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
             }
             bias2[j] = make_float2(two[0], two[1]);
           }
-          if (diag) {
+          if (causal && static_cast<int64_t>(ckey_wmax) > static_cast<int64_t>(q0) + coff) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               if (ckey - coff > q0 + 2 * j) bias2[j].x = -CUDART_INF_F;
@@ -586,26 +592,49 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
           }
           }
         }
-        // LSE*log2e and D of the step's 64 queries arrive in shared memory with the Q/dO stage
-        const float* lrow = s_ld + (i % kQStages) * (2 * kBM) + half * 32;
-        const float* drow = lrow + kBM;
 
         // ---- P^T and dS^T in one pass: both accumulators are loaded together ----
-        // The stage barrier completed long ago (the MMA warp waited on it before issuing S); waiting on it here
-        // makes the bulk-copied LSE / D values visible to this thread. dP of step i is committed after S of
-        // step i was issued, so its barrier covers both accumulators.
-        ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(0, mbar_wait(bar_qdo_full + (i % kQStages), (i / kQStages) & 1,
-                                                                   ctl, kWaitQdoFull)));
-        if (!ok) break;
-        ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(2, mbar_wait(bar_dp_full, i & 1, ctl, kWaitDpFull)));
+        // Barriers that alternate between the teams come in pairs indexed by step parity, so that a team only ever
+        // waits on consecutive phases of a barrier. dP of step i is committed after S of step i was issued, so
+        // dp_full covers both accumulators. The dS^T buffer (i & 1) was last read by the dQ product of step i-2,
+        // issued before dP of step i: the tcgen05.commit behind dP covers every earlier MMA of the issuing thread, so
+        // dp_full(i) also says that buffer is free. The LSE / D values of the stage were bulk-copied under the
+        // stage barrier, which the MMA warp observed before it issued S and dP of this step; the per-query kernel
+        // waits on that barrier itself as well.
+        if (!kTeams) {
+          ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(0, mbar_wait(bar_qdo_full + (i % kQStages),
+                                                                     (i / kQStages) & 1, ctl, kWaitQdoFull)));
+          if (!ok) break;
+        }
+        ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(2, mbar_wait(bar_dp_full + (i & 1), (i >> 1) & 1, ctl, kWaitDpFull)));
         if (!ok) break;
         tc_fence_after_sync();
-        uint32_t dsk[16];
-        {
+        float step_sum = 0.f;
+#pragma unroll 1
+        for (int sub = 0; sub < (kTeams ? 2 : 1); ++sub) {
+          const int qh = kTeams ? sub : half;  // which 32 of the step's 64 queries
+          const int q0s = m * kBM + qh * 32;
+          // LSE*log2e and D of the step's 64 queries arrive in shared memory with the Q/dO stage
+          const float* lrow = s_ld + (i % kQStages) * (2 * kBM) + qh * 32;
+          const float* drow = lrow + kBM;
+          const bool diag = causal && static_cast<int64_t>(ckey_wmax) > static_cast<int64_t>(q0s) + coff;  // warp-uniform
+          const bool per_elem = !kBcast || diag;
+          if (kBcast && diag) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              bias2[j] = make_float2(ckey - coff > q0s + 2 * j ? -CUDART_INF_F : bv,
+                                     ckey - coff > q0s + 2 * j + 1 ? -CUDART_INF_F : bv);
+          }
+          uint32_t dsk[16];
           uint32_t rs[32], rp[32];
-          tmem_ld_x32(tmem_base + lane_addr + kColSt + (i & 1) * kBM + half * 32, rs);
-          tmem_ld_x32(tmem_base + lane_addr + kColDp + half * 32, rp);
+          tmem_ld_x32(tmem_base + lane_addr + kColSt + (i & 1) * kBM + qh * 32, rs);
+          tmem_ld_x32(tmem_base + lane_addr + kColDp + qh * 32, rp);
           tmem_wait_ld();
+          if (!kTeams || sub == 1) {
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_dp_free);  // the dPt block may be overwritten from here on
+          }
           // packed fp32x2 arithmetic: two queries per instruction
           float2 pp[16], dd[16];
           float2 part[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
@@ -635,24 +664,20 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
           float pv[32];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            rs[2 * j] = __float_as_uint(pp[j].x);
-            rs[2 * j + 1] = __float_as_uint(pp[j].y);
             pv[2 * j] = dd[j].x;
             pv[2 * j + 1] = dd[j].y;
           }
-          const float step_sum_packed = (part[0].x + part[0].y) + (part[1].x + part[1].y);
+          step_sum += (part[0].x + part[0].y) + (part[1].x + part[1].y);
           uint32_t pk[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            pk[j] = pack_16x2<kBf16>(__uint_as_float(rs[2 * j]), __uint_as_float(rs[2 * j + 1]));
+            pk[j] = pack_16x2<kBf16>(pp[j].x, pp[j].y);
             dsk[j] = pack_16x2<kBf16>(pv[2 * j], pv[2 * j + 1]);
           }
-          tmem_st_x16(tmem_base + lane_addr + kColSt + (i & 1) * kBM + half * 32, pk);
-          tmem_st_x16(tmem_base + lane_addr + kColDp + half * 32, dsk);
-          const float step_sum = step_sum_packed;
-          if (mode == kDbColsum) {
-            colsum += step_sum;
-          } else if (mode == kDbDirect) {
+          // back into the 32 columns just read: P^T pairs in the first 16, dS^T pairs in the last 16
+          tmem_st_x16(tmem_base + lane_addr + kColSt + (i & 1) * kBM + qh * 32, pk);
+          tmem_st_x16(tmem_base + lane_addr + kColSt + (i & 1) * kBM + qh * 32 + 16, dsk);
+          if (mode == kDbDirect) {  // only reached by the per-query kernel (one pass: q0s == q0)
             if (direct_group) {
 #pragma unroll
               for (int j = 0; j < 32; ++j) dacc[j] += pv[j];
@@ -660,37 +685,40 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
               uint16_t* dst = dbias16 + b * p.dbias_batch_stride + h * p.dbias_head_stride + key;
 #pragma unroll
               for (int j = 0; j < 32; ++j)
-                if (q0 + j < Sq) dst[static_cast<int64_t>(q0 + j) * p.dbias_row_stride] = float_to_raw16<kBf16>(pv[j]);
+                if (q0s + j < Sq) dst[static_cast<int64_t>(q0s + j) * p.dbias_row_stride] = float_to_raw16<kBf16>(pv[j]);
             }
-          } else if (mode == kDbAtomic && key_ok) {
+          } else if (mode == kDbAtomic && key_ok && p.dbias_rows != 1) {
             const int b2 = p.dbias_b == 1 ? 0 : b;
             const int h2 = h / (p.h / p.dbias_h);
             float* base = p.dbias_acc + (static_cast<int64_t>(b2) * p.dbias_h + h2) * p.dbias_rows * p.dbias_keys + key;
-            if (p.dbias_rows == 1) {
-              atomicAdd(base, step_sum);
-            } else {
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (q0 + j < Sq && pv[j] != 0.f) atomicAdd(base + static_cast<int64_t>(q0 + j) * p.dbias_keys, pv[j]);
+            for (int j = 0; j < 32; ++j)
+              if (q0s + j < Sq && pv[j] != 0.f) atomicAdd(base + static_cast<int64_t>(q0s + j) * p.dbias_keys, pv[j]);
+          }
+          // ---- dS^T tile to shared memory for the dQ MMA: row = key, 64 queries x 2 B = 128 B, 128-byte swizzle ----
+          {
+            unsigned char* rowp = s_ds + (i & 1) * L::kDsBytes + krow * 128;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const int chunk = (qh * 4 + c) ^ (krow & 7);
+              *reinterpret_cast<uint4*>(rowp + chunk * 16) = make_uint4(dsk[c * 4], dsk[c * 4 + 1], dsk[c * 4 + 2], dsk[c * 4 + 3]);
             }
           }
         }
-        // ---- dS^T tile to shared memory for the dQ MMA: row = key, 64 queries x 2 B = 128 B, 128-byte swizzle ----
-        ok = __all_sync(0xffffffffu,
-                        FDMA_PROF_WAIT(3, mbar_wait(bar_ds_empty + (i & 1), ((i >> 1) & 1) ^ 1, ctl, kWaitDsEmpty)));
-        if (!ok) break;
-        {
-          unsigned char* rowp = s_ds + (i & 1) * L::kDsBytes + krow * 128;
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const int chunk = (half * 4 + c) ^ (krow & 7);
-            *reinterpret_cast<uint4*>(rowp + chunk * 16) = make_uint4(dsk[c * 4], dsk[c * 4 + 1], dsk[c * 4 + 2], dsk[c * 4 + 3]);
-          }
+        if (mode == kDbColsum) {
+          colsum += step_sum;
+        } else if (mode == kDbAtomic && key_ok && p.dbias_rows == 1) {
+          const int b2 = p.dbias_b == 1 ? 0 : b;
+          const int h2 = h / (p.h / p.dbias_h);
+          atomicAdd(p.dbias_acc + (static_cast<int64_t>(b2) * p.dbias_h + h2) * p.dbias_keys + key, step_sum);
         }
         tmem_wait_st();
         fence_proxy_async_smem();
         tc_fence_before_sync();
-        mbar_arrive(bar_pds);
+        // One arrival per warp: single-thread arrivals of a whole warpgroup on one barrier word serialise in the
+        // shared-memory pipe.
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_pds + (i & 1));
         ++i;
       }
       if (direct_group && ok && key < p.dbias_keys) {  // one store per (query, key) after the whole head group
@@ -783,7 +811,8 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         tmem_ld_x32(tmem_base + lane_addr + kColDq + 32, r1);
         tmem_wait_ld();
         tc_fence_before_sync();
-        mbar_arrive(bar_dq_empty);  // dQ^T columns may be overwritten by the next step from here on
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_dq_empty);  // dQ^T columns may be overwritten by the next step from here on
         float* gdst = p.dq_acc + ((static_cast<int64_t>(b) * p.h + h) * Sq + m * kBM) * kD;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
@@ -909,6 +938,8 @@ BwdPlan plan(const fdma_bwd_params& bp) {
   } else {
     pl.dbias_mode = kDbAtomic;
   }
+  // per-(query, key) dBias is written by the per-query kernel, whose softmax threads keep one query range per step
+  if (pl.dbias_mode == kDbDirect) pl.bcast = false;
   size_t o = 0;
   const size_t rows = static_cast<size_t>(p.b) * p.h * pl.sq_r;
   pl.lse2_off = o; o += align256(rows * 4);
