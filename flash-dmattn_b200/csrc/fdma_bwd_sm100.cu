@@ -907,12 +907,13 @@ struct BwdPlan {
   size_t lse2_off, dsum_off, dq_off, act_off, dbias_off, part_off, dbpart_off, total;
 };
 
-// Query-range splits per key tile. A grid of (key tiles x kv heads x batch) CTAs that cannot fill the GPU twice is
-// cut along the query dimension until about eight CTAs per SM exist, so that the causal imbalance between key
-// tiles evens out; every split keeps at least 32 steps.
+// Query-range splits per key tile. A grid of (key tiles x kv heads x batch) CTAs that cannot fill the GPU twice
+// (eight times when causal masking makes the CTAs unequal) is cut along the query dimension until about eight CTAs
+// per SM exist, so that the causal imbalance between key tiles evens out; every split keeps at least 32 steps.
 int pick_nsplit(const fdma_fwd_params& p) {
   const int64_t ctas = static_cast<int64_t>((p.seqlen_k + kBN - 1) / kBN) * p.h_k * p.b;
-  if (ctas >= 2 * 148) return 1;
+  const bool causal = p.is_causal != 0 && p.seqlen_q > 1;
+  if (ctas >= (causal ? 8 : 2) * 148) return 1;
   const int64_t steps = static_cast<int64_t>((p.seqlen_q + kBM - 1) / kBM) * (p.h / p.h_k);
   const int64_t want = (8 * 148 + ctas - 1) / ctas;
   const int64_t cap = std::max<int64_t>(1, steps / 32);
