@@ -69,9 +69,13 @@ struct RowPtrs {
 };
 
 __device__ __forceinline__ RowPtrs locate(const fdma_mask_params& p, int64_t row, int elem_bytes) {
-  const int r = static_cast<int>(row % p.out_rows);
-  const int h = static_cast<int>((row / p.out_rows) % p.out_h);
-  const int b = static_cast<int>(row / (static_cast<int64_t>(p.out_rows) * p.out_h));
+  // 32-bit divisions (row counts are validated to fit): 64-bit ones cost several hundred instructions per row
+  const uint32_t row32 = static_cast<uint32_t>(row);
+  const uint32_t bh = row32 / static_cast<uint32_t>(p.out_rows);
+  const int r = static_cast<int>(row32 - bh * static_cast<uint32_t>(p.out_rows));
+  const uint32_t b32 = bh / static_cast<uint32_t>(p.out_h);
+  const int h = static_cast<int>(bh - b32 * static_cast<uint32_t>(p.out_h));
+  const int64_t b = b32;
   RowPtrs rp;
   rp.bias = static_cast<const char*>(p.bias) +
             (b * p.bias_batch_stride + h * p.bias_head_stride + r * p.bias_row_stride) * elem_bytes;
@@ -244,19 +248,23 @@ __global__ void __launch_bounds__(kThreads) topk_mask_kernel(const fdma_mask_par
 // ---------------------------------------------------------------------------------------------------------
 template <int DT>
 __device__ __forceinline__ uint32_t key_pair16(uint32_t u) {
-  // per half: negative -> ~u, non-negative -> u | 0x8000; NaN (either sign) -> 0xFFFF
+  // per half: negative -> ~u, non-negative -> u | 0x8000; NaN (either sign) -> 0xFFFF. Plain 32-bit operations on
+  // both halves at once (the SIMD-in-a-word compare intrinsics expand to several instructions each).
   constexpr uint32_t kExp = (DT == FDMA_BF16) ? 0x7F807F80u : 0x7C007C00u;
-  const uint32_t neg = __vcmpgtu2(u, 0x7FFF7FFFu);             // 0xFFFF where the sign bit is set
-  const uint32_t key = u ^ (neg | 0x80008000u);                 // ~u for negatives, u ^ 0x8000 == u | 0x8000 otherwise
-  const uint32_t nan = __vcmpgtu2(u & 0x7FFF7FFFu, kExp);       // magnitude above infinity
+  const uint32_t neg = ((u >> 15) & 0x00010001u) * 0xFFFFu;     // 0xFFFF in every half whose sign bit is set
+  const uint32_t key = u ^ (neg | 0x80008000u);
+  // a magnitude above infinity makes (magnitude + 0x7FFF - infinity) reach bit 15 of its half; the sum stays below
+  // 0x10000, so nothing carries into the other half
+  const uint32_t t = (u & 0x7FFF7FFFu) + (0x7FFF7FFFu - kExp);
+  const uint32_t nan = ((t >> 15) & 0x00010001u) * 0xFFFFu;
   return key | nan;
 }
 
 template <int DT, int CHUNKS>
-__global__ void __launch_bounds__(kThreads) topk16_reg_kernel(const fdma_mask_params p) {
+__global__ void __launch_bounds__(kThreads, CHUNKS <= 4 ? 3 : 1) topk16_reg_kernel(const fdma_mask_params p) {
   using KT = KeyTraits<DT>;
   __shared__ int s_hist[kWarps][256];
-  __shared__ int s_scan[kWarps];
+  __shared__ int s_scan[CHUNKS * kWarps];
   __shared__ uint32_t s_prefix;
   __shared__ int s_need;
   __shared__ int s_eq_total;
@@ -322,7 +330,7 @@ __global__ void __launch_bounds__(kThreads) topk16_reg_kernel(const fdma_mask_pa
     if (c * kChunk + tid * kPerThread < n) {
 #pragma unroll
       for (int w = 0; w < 4; ++w) {
-        atomicAdd(&s_hist[warp][(kw[c][w] >> 8) & 0xFFu], 1);
+        atomicAdd(&s_hist[warp][__byte_perm(kw[c][w], 0, 0x4441)], 1);
         atomicAdd(&s_hist[warp][kw[c][w] >> 24], 1);
       }
     }
@@ -379,74 +387,100 @@ __global__ void __launch_bounds__(kThreads) topk16_reg_kernel(const fdma_mask_pa
 #pragma unroll
       for (int w = 0; w < 4; ++w) {
         const uint32_t x = kw[c][w];
-        if (((x >> 8) & 0xFFu) == hi) atomicAdd(&s_hist[warp][x & 0xFFu], 1);
-        if ((x >> 24) == hi) atomicAdd(&s_hist[warp][(x >> 16) & 0xFFu], 1);
+        if (__byte_perm(x, 0, 0x4441) == hi) atomicAdd(&s_hist[warp][x & 0xFFu], 1);
+        if ((x >> 24) == hi) atomicAdd(&s_hist[warp][__byte_perm(x, 0, 0x4442)], 1);
       }
     }
   }
   select_digit(0);
   const uint32_t thr = s_prefix;
-  const uint32_t thr2 = thr | (thr << 16);
   const int need_eq = s_need;
   const bool all_eq = need_eq >= s_eq_total;
+  const bool check_min = thr <= min_key;  // only then can a selected key hold the value min_dtype
 
-  // ---- write pass ----
-  int base_eq = 0;
-#pragma unroll
-  for (int c = 0; c < CHUNKS; ++c) {
+  // ---- write pass: two output bytes per packed word (bit 0 = low key, bit 8 = high key) ----
+  auto emit = [&](int c, uint32_t (&ob)[4]) {
     const int k = c * kChunk + tid * kPerThread;
-    const bool in = k < n;
-    uint32_t sel[4];
-    int eq_cnt = 0;
+    if (k >= n) return;
+    if (check_min) {  // a value equal to min_dtype is never marked
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      const uint32_t gt = __vcmpgtu2(kw[c][w], thr2);
-      const uint32_t eq = __vcmpeq2(kw[c][w], thr2);
-      sel[w] = all_eq ? (gt | eq) : gt;
-      eq_cnt += __popc(eq) >> 4;
+      for (int w = 0; w < 4; ++w) {
+        if ((kw[c][w] & 0xFFFFu) == min_key) ob[w] &= ~1u;
+        if ((kw[c][w] >> 16) == min_key) ob[w] &= ~0x100u;
+      }
     }
-    if (!all_eq) {  // ties at the threshold: the lowest key indices win; rank them with a block-wide running count
-      int incl = in ? eq_cnt : 0;
-      const int mine = incl;
+    uint2 o;
+    o.x = ob[0] | (ob[1] << 16);
+    o.y = ob[2] | (ob[3] << 16);
+    *reinterpret_cast<uint2*>(rp.out + k) = o;
+  };
+  if (all_eq) {  // every key equal to the threshold is kept
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      uint32_t ob[4];
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const uint32_t lo = kw[c][w] & 0xFFFFu, hi2 = kw[c][w] >> 16;
+        ob[w] = (lo >= thr ? 1u : 0u) | (hi2 >= thr ? 0x100u : 0u);
+      }
+      emit(c, ob);
+    }
+  } else {
+    // ties at the threshold: the lowest key indices win. Keys are ranked chunk by chunk, thread by thread; one
+    // block-wide scan of the per-(chunk, thread) tie counts gives every thread the rank of its first tie.
+    int excl[CHUNKS];
+    uint32_t has_eq = 0;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      int cnt = 0;
+      if (c * kChunk + tid * kPerThread < n) {
+#pragma unroll
+        for (int w = 0; w < 4; ++w)
+          cnt += ((kw[c][w] & 0xFFFFu) == thr ? 1 : 0) + ((kw[c][w] >> 16) == thr ? 1 : 0);
+      }
+      if (cnt) has_eq |= 1u << c;
+      int incl = cnt;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const int v = __shfl_up_sync(0xffffffffu, incl, o);
         if (lane >= o) incl += v;
       }
-      if (lane == 31) s_scan[warp] = incl;
-      __syncthreads();
+      excl[c] = incl - cnt;
+      if (lane == 31) s_scan[c * kWarps + warp] = incl;
+    }
+    __syncthreads();
+    int base = 0;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      uint32_t ob[4];
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const uint32_t lo = kw[c][w] & 0xFFFFu, hi2 = kw[c][w] >> 16;
+        ob[w] = (lo > thr ? 1u : 0u) | (hi2 > thr ? 0x100u : 0u);
+      }
       int warp_base = 0, total = 0;
 #pragma unroll
       for (int w = 0; w < kWarps; ++w) {
-        const int v = s_scan[w];
+        const int v = s_scan[c * kWarps + w];
         if (w < warp) warp_base += v;
         total += v;
       }
-      int rank = base_eq + warp_base + incl - mine;
-      base_eq += total;
-      __syncthreads();
-      if (mine > 0) {
+      if ((has_eq >> c) & 1u) {
+        int rank = base + warp_base + excl[c];
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
-          const uint32_t eq = __vcmpeq2(kw[c][w], thr2);
-          if (eq & 0x0000FFFFu) {
-            if (rank < need_eq) sel[w] |= 0x0000FFFFu;
+          if ((kw[c][w] & 0xFFFFu) == thr) {
+            if (rank < need_eq) ob[w] |= 1u;
             ++rank;
           }
-          if (eq & 0xFFFF0000u) {
-            if (rank < need_eq) sel[w] |= 0xFFFF0000u;
+          if ((kw[c][w] >> 16) == thr) {
+            if (rank < need_eq) ob[w] |= 0x100u;
             ++rank;
           }
         }
       }
-    }
-    if (in) {
-#pragma unroll
-      for (int w = 0; w < 4; ++w) sel[w] &= __vcmpne2(kw[c][w], min2);  // a value equal to min_dtype is never marked
-      uint2 o;
-      o.x = __byte_perm(sel[0], sel[1], 0x6420) & 0x01010101u;
-      o.y = __byte_perm(sel[2], sel[3], 0x6420) & 0x01010101u;
-      *reinterpret_cast<uint2*>(rp.out + k) = o;
+      base += total;
+      emit(c, ob);
     }
   }
   __syncthreads();  // the shared selection state is rewritten at the top of the next row
