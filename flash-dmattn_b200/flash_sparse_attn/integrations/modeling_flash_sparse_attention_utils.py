@@ -1,11 +1,17 @@
-"""Dense (no padding, no packing) branch of the reference's HuggingFace glue
+"""The reference's HuggingFace glue
 (flash_sparse_attn/integrations/modeling_flash_sparse_attention_utils.py:425-596): recast fp32 activations to the
 model's half-precision dtype (:321-339), build the top-`window_size` mask from the bias only when the key length
 exceeds the window (:570-583), and call `flash_sparse_attn_func`.
 
-The reference's two other branches -- a 2-D padding mask (unpad -> varlen kernel -> pad, :511-536) and packed
-sequences given by position ids or cu_seqlens (:538-565) -- end in its varlen kernels, which this package does not
-build; they raise NotImplementedError here instead of silently attending across examples.
+A 2-D padding mask (batch, seq_len) is handled without un-padding: the reference gathers the valid tokens, runs its
+variable-length kernel with no bias and no dynamic mask, and pads the result with zeros (:511-536, `_upad_input`
+:144-220). The same numbers come out of the dense operator when the padding mask is passed as a row-broadcast key
+mask (B, 1, 1, Sk) -- valid tokens keep their order, so the causal test on padded positions equals the causal test
+on gathered positions (for query_length < key_length under the left padding the reference assumes, :209-211) -- and
+the padded query rows are zeroed afterwards. Few valid keys -> `flash_sparse_attn_func` takes its gathered-keys route.
+
+Packed sequences given by position ids or cu_seqlens (:538-565) end in the reference's varlen kernels, which this
+package does not build; they raise NotImplementedError here instead of silently attending across examples.
 """
 import os
 from typing import Optional
@@ -58,16 +64,36 @@ def _flash_sparse_attention_forward(
     """query/key/value (B, S, H, d). Returns (B, Sq, H, d). Same argument list as the reference function."""
     if attention_mask is not None and attention_mask.dim() == 2 and attention_bias is not None:
         raise ValueError("If shape of attention_mask is (batch_size, seq_len), attention_bias has to be None.")
-    if attention_mask is not None and attention_mask.dim() == 2:
-        raise NotImplementedError("2-D padding masks need the variable-length kernels, which are not built")
+    padded = attention_mask is not None and attention_mask.dim() == 2
     packed = all(x is not None for x in (cu_seq_lens_q, cu_seq_lens_k, max_length_q, max_length_k))
-    if packed or _is_packed_sequence(position_ids, query_states.size(0)):
+    if not padded and (packed or _is_packed_sequence(position_ids, query_states.size(0))):
         raise NotImplementedError("packed sequences need the variable-length kernels, which are not built")
 
     query_states, key_states, value_states, attention_bias = fsa_peft_integration_check(
         query_states, key_states, value_states, attention_bias, target_dtype)
     if deterministic is None:
         deterministic = os.getenv("FLASH_SPARSE_ATTENTION_DETERMINISTIC", "0") == "1"
+
+    if padded:
+        # static caches: k/v may be longer than the mask (reference :187-190)
+        seq_len = attention_mask.shape[-1]
+        if key_states.shape[1] > seq_len:
+            key_states, value_states = key_states[:, :seq_len], value_states[:, :seq_len]
+        key_valid = attention_mask.to(torch.bool)
+        if query_length == key_states.shape[1]:
+            query_valid = key_valid
+        elif query_length == 1:
+            query_valid = None
+        else:
+            query_valid = key_valid[:, -query_length:]  # left padding, as the reference assumes
+        out = flash_sparse_attn_func(
+            query_states, key_states, value_states, key_valid[:, None, None, :], None,
+            softmax_scale=softmax_scale, is_causal=is_causal and query_length != 1,
+            softcap=softcap, deterministic=deterministic)
+        out = out[0] if isinstance(out, tuple) else out
+        if query_valid is not None:
+            out = torch.where(query_valid[:, :, None, None], out, torch.zeros((), dtype=out.dtype, device=out.device))
+        return out
 
     if attention_bias is not None and window_size is not None and key_length > window_size:
         attention_mask = create_mask(

@@ -47,14 +47,67 @@ def test_forward_matches_oracle(dev, window, fp32_in):
     check("out", out.cpu(), ref, dtype)
 
 
+@pytest.mark.parametrize("side", ["right", "left"])
+@pytest.mark.parametrize("lengths", [(256, 100, 37), (256, 256, 200)])
+def test_padding_mask_matches_unpadded_attention(dev, side, lengths):
+    """2-D padding mask: every example must equal plain causal attention over its own valid tokens (what the
+    reference computes by un-padding, flash_sparse_attn/integrations/modeling_flash_sparse_attention_utils.py:511-536),
+    padded rows zero; gradients of valid tokens likewise, of padded tokens zero."""
+    from flash_sparse_attn.integrations import flash_sparse_attention_forward
+
+    B, S, H, Hk, d = len(lengths), 256, 4, 2, 64
+    dtype = torch.bfloat16
+    q, k, v, _, dout = oracle.make_inputs(B, S, S, H, Hk, d, (B, Hk, 1, S), seed=21, dtype=dtype)
+    pad = torch.zeros(B, S, dtype=torch.bool)
+    for b, n in enumerate(lengths):
+        if side == "right":
+            pad[b, :n] = True
+        else:
+            pad[b, S - n:] = True
+    qd, kd, vd = (t.to(dev).requires_grad_(True) for t in (q, k, v))
+    module = _Attn(dtype).to(dev)
+    out, _ = flash_sparse_attention_forward(module, qd.transpose(1, 2), kd.transpose(1, 2), vd.transpose(1, 2),
+                                            pad.to(dev), None, scaling=d ** -0.5)
+    assert out.shape == (B, S, H, d)
+    out.backward(dout.to(dev))
+    for b, n in enumerate(lengths):
+        sel = pad[b]
+        r_out, _, r_dq, r_dk, r_dv, _ = oracle.attention_forward_backward(
+            q[b:b + 1, sel], k[b:b + 1, sel], v[b:b + 1, sel], None, None, dout[b:b + 1, sel], d ** -0.5, True)
+        check(f"out[{b}]", out[b:b + 1, sel.to(dev)].detach().cpu(), r_out, dtype)
+        check(f"dq[{b}]", qd.grad[b:b + 1, sel.to(dev)].cpu(), r_dq, dtype)
+        check(f"dk[{b}]", kd.grad[b:b + 1, sel.to(dev)].cpu(), r_dk, dtype)
+        check(f"dv[{b}]", vd.grad[b:b + 1, sel.to(dev)].cpu(), r_dv, dtype)
+        if n < S:
+            assert out[b, ~sel.to(dev)].abs().max().item() == 0.0
+            for g in (qd.grad, kd.grad, vd.grad):
+                assert g[b, ~sel.to(dev)].abs().max().item() == 0.0
+
+
+def test_padding_mask_single_query(dev):
+    """Decode step with a padded cache: one query per example, keys limited to the example's valid ones."""
+    from flash_sparse_attn.integrations import flash_sparse_attention_forward
+
+    B, S, H, Hk, d = 2, 384, 4, 2, 128
+    dtype = torch.bfloat16
+    q, k, v, _, _ = oracle.make_inputs(B, 1, S, H, Hk, d, (B, Hk, 1, S), seed=22, dtype=dtype)
+    pad = torch.ones(B, S, dtype=torch.bool)
+    pad[1, :150] = False
+    module = _Attn(dtype).to(dev)
+    out, _ = flash_sparse_attention_forward(module, q.to(dev).transpose(1, 2), k.to(dev).transpose(1, 2),
+                                            v.to(dev).transpose(1, 2), pad.to(dev), None, scaling=d ** -0.5)
+    for b in range(B):
+        sel = pad[b]
+        ref = oracle.attention_forward(q[b:b + 1], k[b:b + 1, sel], v[b:b + 1, sel], None, None, d ** -0.5, False)[0]
+        check(f"out[{b}]", out[b:b + 1].cpu(), ref, dtype)
+
+
 def test_unsupported_branches_raise(dev):
     from flash_sparse_attn.integrations import flash_sparse_attention_forward
 
     module = _Attn(torch.bfloat16).to(dev)
     q = torch.zeros(1, 2, 16, 64, device=dev, dtype=torch.bfloat16)
     pad = torch.ones(1, 16, dtype=torch.bool, device=dev)
-    with pytest.raises(NotImplementedError):
-        flash_sparse_attention_forward(module, q, q, q, pad, None)
     with pytest.raises(ValueError):
         flash_sparse_attention_forward(module, q, q, q, pad, torch.zeros(1, 2, 1, 16, device=dev, dtype=torch.bfloat16))
     packed = torch.cat([torch.arange(8), torch.arange(8)])[None].to(dev)
