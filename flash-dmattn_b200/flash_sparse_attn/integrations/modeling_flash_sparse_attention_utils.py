@@ -10,8 +10,11 @@ mask (B, 1, 1, Sk) -- valid tokens keep their order, so the causal test on padde
 on gathered positions (for query_length < key_length under the left padding the reference assumes, :209-211) -- and
 the padded query rows are zeroed afterwards. Few valid keys -> `flash_sparse_attn_func` takes its gathered-keys route.
 
-Packed sequences given by position ids or cu_seqlens (:538-565) end in the reference's varlen kernels, which this
-package does not build; they raise NotImplementedError here instead of silently attending across examples.
+Packed sequences given by position ids or cu_seqlens (:538-565, `_prepare_from_posids` :270-302) go through the
+reference's varlen kernel as well; here the flattened tokens run as ONE sequence under a per-query visibility mask
+(same example, and causal inside the example with the bottom-right alignment of its own lengths), which the
+full-range kernels skip tile by tile. The mask takes Tq x Tk bytes, so totals above `_PACKED_MASK_LIMIT` elements
+raise NotImplementedError rather than allocate it.
 """
 import os
 from typing import Optional
@@ -37,6 +40,34 @@ def _is_packed_sequence(position_ids: Optional[torch.Tensor], batch_size: int) -
         return False
     expected = torch.arange(position_ids.shape[1], device=position_ids.device) + position_ids.min()
     return not bool((position_ids[0] == expected).all())
+
+
+_PACKED_MASK_LIMIT = 1 << 28  # elements of the (Tq, Tk) visibility mask built for packed sequences
+
+
+def _packed_visibility(cu_q: torch.Tensor, cu_k: torch.Tensor, total_q: int, total_k: int, causal: bool,
+                       device) -> torch.Tensor:
+    """(total_q, total_k) bool: query token i sees key token j iff both lie in the same example and, when causal,
+    j_local <= i_local + len_k - len_q (the varlen kernels' bottom-right alignment per example). Tokens past the
+    last boundary see nothing."""
+    if total_q * total_k > _PACKED_MASK_LIMIT:
+        raise NotImplementedError(
+            f"packed sequences of {total_q} x {total_k} tokens need the variable-length kernels, which are not built")
+    cu_q = cu_q.to(device=device, dtype=torch.int64)
+    cu_k = cu_k.to(device=device, dtype=torch.int64)
+    n = cu_q.numel() - 1
+    tq = torch.arange(total_q, device=device)
+    tk = torch.arange(total_k, device=device)
+    sq = torch.bucketize(tq, cu_q[1:], right=True)   # example of each token; == n past the last boundary
+    sk = torch.bucketize(tk, cu_k[1:], right=True)
+    visible = (sq[:, None] == sk[None, :]) & (sq[:, None] < n) & (tq[:, None] >= cu_q[0]) & (tk[None, :] >= cu_k[0])
+    if causal:
+        sq_c = sq.clamp(max=n - 1)
+        local_q = tq - cu_q[sq_c]
+        local_k = tk - cu_k[sk.clamp(max=n - 1)]
+        shift = (cu_k[1:] - cu_k[:-1] - (cu_q[1:] - cu_q[:-1]))[sq_c]
+        visible &= local_k[None, :] <= (local_q + shift)[:, None]
+    return visible
 
 
 def _flash_sparse_attention_forward(
@@ -65,14 +96,29 @@ def _flash_sparse_attention_forward(
     if attention_mask is not None and attention_mask.dim() == 2 and attention_bias is not None:
         raise ValueError("If shape of attention_mask is (batch_size, seq_len), attention_bias has to be None.")
     padded = attention_mask is not None and attention_mask.dim() == 2
-    packed = all(x is not None for x in (cu_seq_lens_q, cu_seq_lens_k, max_length_q, max_length_k))
-    if not padded and (packed or _is_packed_sequence(position_ids, query_states.size(0))):
-        raise NotImplementedError("packed sequences need the variable-length kernels, which are not built")
+    packed_kwargs = all(x is not None for x in (cu_seq_lens_q, cu_seq_lens_k, max_length_q, max_length_k))
+    packed = not padded and (packed_kwargs or _is_packed_sequence(position_ids, query_states.size(0)))
 
     query_states, key_states, value_states, attention_bias = fsa_peft_integration_check(
         query_states, key_states, value_states, attention_bias, target_dtype)
     if deterministic is None:
         deterministic = os.getenv("FLASH_SPARSE_ATTENTION_DETERMINISTIC", "0") == "1"
+
+    if packed:
+        if cu_seq_lens_q is None or cu_seq_lens_k is None:  # boundaries from the position ids (reference :241-251)
+            flat = position_ids.reshape(-1)
+            starts = (flat == 0).nonzero().view(-1).to(torch.int64)
+            cu_seq_lens_q = cu_seq_lens_k = torch.cat(
+                (starts, torch.tensor([flat.numel()], dtype=torch.int64, device=flat.device)))
+        B = query_states.size(0)
+        q1 = query_states.reshape(1, -1, query_states.size(-2), query_states.size(-1))
+        k1 = key_states.reshape(1, -1, key_states.size(-2), key_states.size(-1))
+        v1 = value_states.reshape(1, -1, value_states.size(-2), value_states.size(-1))
+        visible = _packed_visibility(cu_seq_lens_q, cu_seq_lens_k, q1.size(1), k1.size(1), is_causal, q1.device)
+        out = flash_sparse_attn_func(q1, k1, v1, visible[None, None], None, softmax_scale=softmax_scale,
+                                     is_causal=False, softcap=softcap, deterministic=deterministic)
+        out = out[0] if isinstance(out, tuple) else out
+        return out.view(B, -1, out.size(-2), out.size(-1))
 
     if padded:
         # static caches: k/v may be longer than the mask (reference :187-190)

@@ -102,8 +102,43 @@ def test_padding_mask_single_query(dev):
         check(f"out[{b}]", out[b:b + 1].cpu(), ref, dtype)
 
 
+@pytest.mark.parametrize("how", ["position_ids", "cu_seqlens"])
+def test_packed_sequences_match_per_example_attention(dev, how):
+    """Packed examples in one row (reference: flash_sparse_attn/integrations/modeling_flash_sparse_attention_utils.py
+    :538-565): each example must equal causal attention over its own tokens, values and gradients."""
+    from flash_sparse_attn.integrations import flash_sparse_attention_forward
+
+    lens = (200, 180, 132)
+    S, H, Hk, d = sum(lens), 4, 2, 64
+    dtype = torch.bfloat16
+    q, k, v, _, dout = oracle.make_inputs(1, S, S, H, Hk, d, (1, Hk, 1, S), seed=23, dtype=dtype)
+    qd, kd, vd = (t.to(dev).requires_grad_(True) for t in (q, k, v))
+    module = _Attn(dtype).to(dev)
+    kw = {}
+    if how == "position_ids":
+        kw["position_ids"] = torch.cat([torch.arange(n) for n in lens])[None].to(dev)
+    else:
+        cu = torch.tensor([0, 200, 380, 512], dtype=torch.int32, device=dev)
+        kw.update(cu_seq_lens_q=cu, cu_seq_lens_k=cu, max_length_q=200, max_length_k=200)
+    out, _ = flash_sparse_attention_forward(module, qd.transpose(1, 2), kd.transpose(1, 2), vd.transpose(1, 2),
+                                            None, None, scaling=d ** -0.5, **kw)
+    assert out.shape == (1, S, H, d)
+    out.backward(dout.to(dev))
+    lo = 0
+    for n in lens:
+        sl = slice(lo, lo + n)
+        r_out, _, r_dq, r_dk, r_dv, _ = oracle.attention_forward_backward(
+            q[:, sl], k[:, sl], v[:, sl], None, None, dout[:, sl], d ** -0.5, True)
+        check(f"out[{lo}]", out[:, sl].detach().cpu(), r_out, dtype)
+        check(f"dq[{lo}]", qd.grad[:, sl].cpu(), r_dq, dtype)
+        check(f"dk[{lo}]", kd.grad[:, sl].cpu(), r_dk, dtype)
+        check(f"dv[{lo}]", vd.grad[:, sl].cpu(), r_dv, dtype)
+        lo += n
+
+
 def test_unsupported_branches_raise(dev):
     from flash_sparse_attn.integrations import flash_sparse_attention_forward
+    from flash_sparse_attn.integrations import modeling_flash_sparse_attention_utils as glue
 
     module = _Attn(torch.bfloat16).to(dev)
     q = torch.zeros(1, 2, 16, 64, device=dev, dtype=torch.bfloat16)
@@ -111,5 +146,9 @@ def test_unsupported_branches_raise(dev):
     with pytest.raises(ValueError):
         flash_sparse_attention_forward(module, q, q, q, pad, torch.zeros(1, 2, 1, 16, device=dev, dtype=torch.bfloat16))
     packed = torch.cat([torch.arange(8), torch.arange(8)])[None].to(dev)
-    with pytest.raises(NotImplementedError):
-        flash_sparse_attention_forward(module, q, q, q, None, None, position_ids=packed)
+    limit, glue._PACKED_MASK_LIMIT = glue._PACKED_MASK_LIMIT, 100
+    try:
+        with pytest.raises(NotImplementedError):
+            flash_sparse_attention_forward(module, q, q, q, None, None, position_ids=packed)
+    finally:
+        glue._PACKED_MASK_LIMIT = limit
