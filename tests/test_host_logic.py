@@ -152,3 +152,23 @@ def test_head_dim_routing_and_compaction_eligibility():
             iface.set_compaction("sometimes")
     finally:
         torch.Tensor.is_cuda = orig
+
+
+def test_packed_visibility_matches_brute_force():
+    """Visibility of packed examples (HF glue): same example, and causal with each example's own bottom-right
+    alignment (reference: the varlen call of modeling_flash_sparse_attention_utils.py:538-565)."""
+    import torch
+    from flash_sparse_attn.integrations.modeling_flash_sparse_attention_utils import _packed_visibility
+
+    cu_q = torch.tensor([0, 3, 5, 9])
+    cu_k = torch.tensor([0, 4, 9, 12])
+    for causal in (False, True):
+        got = _packed_visibility(cu_q, cu_k, 10, 13, causal, "cpu")   # one token past the last boundary on each side
+        want = torch.zeros(10, 13, dtype=torch.bool)
+        for s in range(3):
+            lq, lk = int(cu_q[s + 1] - cu_q[s]), int(cu_k[s + 1] - cu_k[s])
+            for i in range(lq):
+                for j in range(lk):
+                    if not causal or j <= i + lk - lq:
+                        want[cu_q[s] + i, cu_k[s] + j] = True
+        assert torch.equal(got, want)
