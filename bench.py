@@ -695,7 +695,7 @@ def run_decode(args, rank: int, world: int, local_rank: int):
         "config": {"workload": f"decode: B={B} per GPU, Sq=1, Sk={Sk}, Hq={H}, Hkv={Hk}, d={d}, W={w}, non-causal",
                    "bytes_per_step": total_bytes, "l2": "K/V cache far larger than L2"},
         "decode_kernel_ms": kernel_ms,
-        "roofline": {"bound": "hbm", "kernel": "decode_pipe_kernel",
+        "roofline": {"bound": "hbm", "kernel": "decode_mma_kernel",
                      "achieved": total_bytes / world / (kernel_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                      "frac": total_bytes / world / (kernel_ms * 1e-3) / 1e9 / peak, "peak_source": "of " + src,
                      "traffic": None},

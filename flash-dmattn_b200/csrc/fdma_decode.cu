@@ -43,6 +43,7 @@ struct DecodeParams {
   int64_t v_batch_stride, v_row_stride, v_head_stride;
   int64_t mask_batch_stride, mask_head_stride, bias_batch_stride, bias_head_stride;
   int b, seqlen_k, h, h_k, h_mask, h_bias, group, nsplit;
+  int heads_per_cta;  // query heads that share one pass over the rows (decode_mma_kernel reads it at run time)
   float scale_log2;
 };
 
@@ -205,14 +206,15 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(const DecodeParams p) 
   }
 }
 
-// ---- pipelined variant for G * rows-per-batch == 32 (G = 4: 8 rows, G = 8: 4 rows), head dim <= 128 ------------
+// ---- pipelined tensor-core variant: head dim 64 / 128, up to 8 query heads per kv head ----------------------------
 // Same scan / queue / partial scheme as decode_kernel, with two changes that matter when the kernel is bound by the
-// latency of scattered row reads:
-//  * rows travel global -> shared memory with cp.async into a ring of kPipeStages batches per warp, so the next
-//    batches of K / V rows are in flight (holding no registers) while the current one is computed;
-//  * the rows x G scores of a batch are reduced across lanes with one halving butterfly (31 shuffles for 32 sums
-//    instead of 5 per sum), leaving score (row t, head g) in lane t * G + g; that lane alone evaluates the exp2, and the
-//    probabilities and rescale factors reach the other lanes through shared memory.
+// latency of scattered row reads and by instruction issue:
+//  * rows travel global -> shared memory with cp.async into a ring of batches (8 K rows + 8 V rows) per warp, so the
+//    next batch is in flight (holding no registers) while the current one is computed;
+//  * the G query heads that share the rows are the M rows of mma.sync.m16n8k16 (rows >= G are zero): S = Q K^T and
+//    O += P V of a batch take 4 + 4 ldmatrix and 8 + 16 mma per 8 keys instead of per-lane dot products, a cross-lane
+//    butterfly and per-lane value accumulation (which cost about 110 instructions per key). Shared-memory rows are
+//    padded by 16 bytes so that the eight rows of an ldmatrix tile fall into different banks.
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem))),
                "l"(gmem)
@@ -224,29 +226,56 @@ __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-constexpr int kPipeStages = 2;  // row batches per warp: one being computed, the other in flight (3 measured the same)
-
-template <int EPL, int G>
-struct PipeSmem {
-  static constexpr int D = 32 * EPL;
-  static constexpr int kRows = 32 / G;                      // rows per batch
-  static constexpr int kStageBytes = 2 * kRows * D * 2;     // K rows then V rows, 16-bit
-  static constexpr int kWarpBytes = kPipeStages * kStageBytes;
+template <int D>
+struct MmaSmem {
+  static constexpr int kRows = 8;
+  static constexpr int kRowBytes = D * 2 + 16;
+  static constexpr int kStageBytes = 2 * kRows * kRowBytes;  // K rows then V rows
+  static constexpr int kStages = 2;                          // row batches per warp: one computed, one in flight (3: slower)
+  static constexpr int kWarpBytes = kStages * kStageBytes;
   static constexpr int kTotal = kWarps * kWarpBytes;
 };
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+// Rows 8-15 of every product here are zero (A rows 8-15 are zero), so all accumulators share one pair of registers
+// (z0, z1) for them.
+template <bool kBf16>
+__device__ __forceinline__ void mma_16816(float& c0, float& c1, float& z0, float& z1, uint32_t a0, uint32_t a2,
+                                          uint32_t b0, uint32_t b1) {
+  if (kBf16)
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%5}, {%7,%8}, {%0,%1,%2,%3};"
+                 : "+f"(c0), "+f"(c1), "+f"(z0), "+f"(z1) : "r"(a0), "r"(0u), "r"(a2), "r"(b0), "r"(b1));
+  else
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%5}, {%7,%8}, {%0,%1,%2,%3};"
+                 : "+f"(c0), "+f"(c1), "+f"(z0), "+f"(z1) : "r"(a0), "r"(0u), "r"(a2), "r"(b0), "r"(b1));
+}
+template <bool kBf16>
+__device__ __forceinline__ uint32_t pack_pair(float lo, float hi) {
+  if (kBf16) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
+  const __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
 
-template <int EPL, int G, bool kBf16>
-__global__ void __launch_bounds__(kThreads, 2) decode_pipe_kernel(const DecodeParams p) {
-  using L = PipeSmem<EPL, G>;
-  constexpr int D = L::D, R = L::kRows;
+template <int D, bool kBf16>
+__global__ void __launch_bounds__(kThreads, 2) decode_mma_kernel(const DecodeParams p) {
+  using L = MmaSmem<D>;
+  constexpr int R = L::kRows;
+  const int G = p.heads_per_cta;                            // 1, 2, 4 or 8 query heads share the rows
   constexpr int kChunksPerRow = D / 8;                      // 16-byte pieces of a row
   constexpr int kRowsPerCopy = 32 / kChunksPerRow;          // rows covered by one warp-wide cp.async
   extern __shared__ __align__(16) unsigned char s_rows[];
   __shared__ int s_queue[kWarps][kQueue];
   __shared__ float s_qbias[kWarps][kQueue];
-  __shared__ float s_pbias[kWarps][kPipeStages][R];         // bias of the rows of each stage
-  __shared__ __align__(16) float s_prob[kWarps][32];        // probabilities of the batch, index t * G + g
-  __shared__ __align__(16) float s_corr[kWarps][G];         // rescale factor of the running state per head
+  __shared__ float s_pbias[kWarps][L::kStages][R];         // bias of the rows of each stage
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int split = blockIdx.x, b = blockIdx.z;
   const int h0 = blockIdx.y * G;
@@ -260,33 +289,26 @@ __global__ void __launch_bounds__(kThreads, 2) decode_pipe_kernel(const DecodePa
   const uint16_t* vbase = reinterpret_cast<const uint16_t*>(p.v) + b * p.v_batch_stride + hk * p.v_head_stride;
   unsigned char* my_rows = s_rows + warp * L::kWarpBytes;
 
-  float qv[G][EPL];
+  // Fragments of mma.sync.m16n8k16 (row.col): the M = 16 rows are the query heads (rows >= G are zero), so a
+  // lane's quad index g = lane >> 2 is its head and lanes of quads >= G carry zeros.
+  //   A: a0 = (row g, k = 2c, 2c+1), a2 = (row g, k + 8), a1 / a3 = rows g + 8 (always zero here)   [c = lane & 3]
+  //   B: b0 = (k = 2c, 2c+1; n = g), b1 = (k + 8; n = g)
+  //   C: c0, c1 = (row g, n = 2c, 2c+1), c2, c3 = rows g + 8 (unused)
+  const int quad = lane >> 2, c2 = (lane & 3) * 2;
+  uint32_t qa[D / 16][2];
+  {
+    const uint16_t* qp = reinterpret_cast<const uint16_t*>(p.q) + b * p.q_batch_stride + (h0 + min(quad, G - 1)) * p.q_head_stride;
 #pragma unroll
-  for (int g = 0; g < G; ++g) {
-    const uint16_t* qp = reinterpret_cast<const uint16_t*>(p.q) + b * p.q_batch_stride + (h0 + g) * p.q_head_stride + lane * EPL;
-#pragma unroll
-    for (int e = 0; e < EPL; ++e) qv[g][e] = raw_to_f<kBf16>(qp[e]) * p.scale_log2;
-  }
-  float acc[G][EPL];
-#pragma unroll
-  for (int g = 0; g < G; ++g)
-#pragma unroll
-    for (int e = 0; e < EPL; ++e) acc[g][e] = 0.f;
-  float my_m = -CUDART_INF_F, my_l = 0.f;                   // running max / sum of head my_g (same in all its lanes)
-
-  auto load_elems = [&](const unsigned char* row, float (&out)[EPL]) {
-    if (EPL == 4) {
-      const uint2 r = *reinterpret_cast<const uint2*>(row + lane * 8);
-      out[0] = raw_to_f<kBf16>(static_cast<uint16_t>(r.x & 0xFFFFu));
-      out[1] = raw_to_f<kBf16>(static_cast<uint16_t>(r.x >> 16));
-      out[2] = raw_to_f<kBf16>(static_cast<uint16_t>(r.y & 0xFFFFu));
-      out[3] = raw_to_f<kBf16>(static_cast<uint16_t>(r.y >> 16));
-    } else {
-      const uint32_t r = *reinterpret_cast<const uint32_t*>(row + lane * 4);
-      out[0] = raw_to_f<kBf16>(static_cast<uint16_t>(r & 0xFFFFu));
-      out[1] = raw_to_f<kBf16>(static_cast<uint16_t>(r >> 16));
+    for (int ks = 0; ks < D / 16; ++ks) {
+      qa[ks][0] = quad < G ? *reinterpret_cast<const uint32_t*>(qp + ks * 16 + c2) : 0u;
+      qa[ks][1] = quad < G ? *reinterpret_cast<const uint32_t*>(qp + ks * 16 + 8 + c2) : 0u;
     }
-  };
+  }
+  float o[D / 8][2];                                         // O[head g][d = nt * 8 + 2c, +1]
+#pragma unroll
+  for (int nt = 0; nt < D / 8; ++nt) o[nt][0] = o[nt][1] = 0.f;
+  float z0 = 0.f, z1 = 0.f;                                  // rows 8-15 of every accumulator: always zero
+  float my_m = -CUDART_INF_F, my_l = 0.f;                   // running max / sum of head g (same in the quad's lanes)
 
   // queue entries [first, first + n) -> stage: start the row copies, remember the rows' biases
   auto issue = [&](int first, int n, int stage) {
@@ -297,75 +319,55 @@ __global__ void __launch_bounds__(kThreads, 2) decode_pipe_kernel(const DecodePa
       const int t = r0 + sub;
       if (t < R) {
         const int64_t key = s_queue[warp][first + min(t, n - 1)];
-        cp_async16(dst + t * (D * 2) + chunk * 16, kbase + key * p.k_row_stride + chunk * 8);
-        cp_async16(dst + (R + t) * (D * 2) + chunk * 16, vbase + key * p.v_row_stride + chunk * 8);
+        cp_async16(dst + t * L::kRowBytes + chunk * 16, kbase + key * p.k_row_stride + chunk * 8);
+        cp_async16(dst + (R + t) * L::kRowBytes + chunk * 16, vbase + key * p.v_row_stride + chunk * 8);
       }
     }
     cp_async_commit();
     if (lane < R) s_pbias[warp][stage][lane] = lane < n ? s_qbias[warp][first + lane] : -CUDART_INF_F;
   };
 
-  // the rows of `stage` have landed: scores, online softmax, value accumulation
+  // the rows of `stage` have landed: S = Q K^T on the tensor cores (rows = heads, columns = the 8 keys), online
+  // softmax on the accumulator fragment, which is also the A fragment of O += P V (keys 8-15 of its k = 16 are zero)
   auto consume = [&](int stage) {
     __syncwarp();
-    const unsigned char* src = my_rows + stage * L::kStageBytes;
-    float v[32];
+    const uint32_t kaddr = static_cast<uint32_t>(__cvta_generic_to_shared(my_rows + stage * L::kStageBytes)) +
+                           (lane & 7) * L::kRowBytes + (lane >> 3) * 16;
+    const uint32_t vaddr = kaddr + R * L::kRowBytes;
+    float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-    for (int t = 0; t < R; ++t) {
-      float kr[EPL];
-      load_elems(src + t * (D * 2), kr);
-#pragma unroll
-      for (int g = 0; g < G; ++g) {
-        float d = 0.f;
-#pragma unroll
-        for (int e = 0; e < EPL; ++e) d = fmaf(qv[g][e], kr[e], d);
-        v[t * G + g] = d;
-      }
+    for (int ks2 = 0; ks2 < D / 32; ++ks2) {  // one ldmatrix.x4 = the B fragments of two k-steps
+      uint32_t bf[4];
+      ldmatrix_x4(bf, kaddr + ks2 * 64);
+      mma_16816<kBf16>(s0, s1, z0, z1, qa[2 * ks2][0], qa[2 * ks2][1], bf[0], bf[1]);
+      mma_16816<kBf16>(s0, s1, z0, z1, qa[2 * ks2 + 1][0], qa[2 * ks2 + 1][1], bf[2], bf[3]);
     }
-    // halving butterfly: after the step with offset o a lane keeps the half selected by its bit o
-#pragma unroll
-    for (int o = 16, n = 32; o > 0; o >>= 1, n >>= 1) {
-      const bool upper = (lane & o) != 0;
-#pragma unroll
-      for (int i = 0; i < n / 2; ++i) {
-        const float send = upper ? v[i] : v[i + n / 2];
-        const float keep = upper ? v[i + n / 2] : v[i];
-        v[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
-      }
-    }
-    const int my_t = lane / G;
-    const float sc = v[0] + s_pbias[warp][stage][my_t];     // -inf for the padding rows of a short batch
-    float mx = sc;
-#pragma unroll
-    for (int o = G; o < 32; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    const float sc0 = fmaf(s0, p.scale_log2, s_pbias[warp][stage][c2]);      // -inf for padding rows
+    const float sc1 = fmaf(s1, p.scale_log2, s_pbias[warp][stage][c2 + 1]);
+    float mx = fmaxf(sc0, sc1);
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
     const float m_new = fmaxf(my_m, mx);
-    const float pw = m_new == -CUDART_INF_F ? 0.f : exp2f(sc - m_new);
+    const float p0 = m_new == -CUDART_INF_F ? 0.f : exp2f(sc0 - m_new);
+    const float p1 = m_new == -CUDART_INF_F ? 0.f : exp2f(sc1 - m_new);
     const float corr = my_m == -CUDART_INF_F ? 0.f : exp2f(my_m - m_new);
-    float psum = pw;
-#pragma unroll
-    for (int o = G; o < 32; o <<= 1) psum += __shfl_xor_sync(0xffffffffu, psum, o);
+    float psum = p0 + p1;
+    psum += __shfl_xor_sync(0xffffffffu, psum, 1);
+    psum += __shfl_xor_sync(0xffffffffu, psum, 2);
     my_l = my_l * corr + psum;
     my_m = m_new;
-    s_prob[warp][lane] = pw;
-    if (lane < G) s_corr[warp][lane] = corr;
-    __syncwarp();
-    float cg[G];
+    const uint32_t pa = pack_pair<kBf16>(p0, p1);
 #pragma unroll
-    for (int g = 0; g < G; ++g) cg[g] = s_corr[warp][g];
+    for (int nt = 0; nt < D / 8; ++nt) {
+      o[nt][0] *= corr;
+      o[nt][1] *= corr;
+    }
 #pragma unroll
-    for (int g = 0; g < G; ++g)
+    for (int nt4 = 0; nt4 < D / 32; ++nt4) {  // one transposed ldmatrix.x4 = the B fragments of four d-tiles
+      uint32_t bf[4];
+      ldmatrix_x4_trans(bf, vaddr + nt4 * 64);
 #pragma unroll
-      for (int e = 0; e < EPL; ++e) acc[g][e] *= cg[g];
-#pragma unroll
-    for (int t = 0; t < R; ++t) {
-      float vr[EPL];
-      load_elems(src + (R + t) * (D * 2), vr);
-#pragma unroll
-      for (int g = 0; g < G; ++g) {
-        const float pg = s_prob[warp][t * G + g];
-#pragma unroll
-        for (int e = 0; e < EPL; ++e) acc[g][e] = fmaf(pg, vr[e], acc[g][e]);
-      }
+      for (int j = 0; j < 4; ++j) mma_16816<kBf16>(o[nt4 * 4 + j][0], o[nt4 * 4 + j][1], z0, z1, pa, 0u, bf[j], 0u);
     }
     __syncwarp();
   };
@@ -466,29 +468,28 @@ __global__ void __launch_bounds__(kThreads, 2) decode_pipe_kernel(const DecodePa
     if (n > 0) {
       issue(head, n, st_w);
       head += n;
-      st_w = st_w + 1 == kPipeStages ? 0 : st_w + 1;
+      st_w = st_w + 1 == L::kStages ? 0 : st_w + 1;
       ++pend;
     }
-    if (pend == kPipeStages || (n == 0 && pend > 0)) {
-      static_assert(kPipeStages <= 3, "add a wait for deeper rings");
+    if (pend == L::kStages || (n == 0 && pend > 0)) {
+      static_assert(L::kStages <= 3, "add a wait for deeper rings");
       if (pend >= 3) cp_async_wait<2>();  // all but the newest (pend - 1) groups have landed
       else if (pend == 2) cp_async_wait<1>();
       else cp_async_wait<0>();
       consume(st_r);
-      st_r = st_r + 1 == kPipeStages ? 0 : st_r + 1;
+      st_r = st_r + 1 == L::kStages ? 0 : st_r + 1;
       --pend;
     }
     if (n == 0 && pend == 0) break;
   }
 
-  // one partial per warp; lane g (row 0 of the butterfly layout) holds head g's running max and sum
+  // one partial per warp and head: the quad of head g holds O[g][:] (two floats per d-tile and lane), m and l
   const int P = p.nsplit * kWarps;
+  if (quad < G) {
+    float* dst = p.partial + ((static_cast<int64_t>(b) * p.h + h0 + quad) * P + split * kWarps + warp) * (D + 2);
 #pragma unroll
-  for (int g = 0; g < G; ++g) {
-    float* dst = p.partial + ((static_cast<int64_t>(b) * p.h + h0 + g) * P + split * kWarps + warp) * (D + 2);
-#pragma unroll
-    for (int e = 0; e < EPL; ++e) dst[lane * EPL + e] = acc[g][e];
-    if (lane == g) {
+    for (int nt = 0; nt < D / 8; ++nt) *reinterpret_cast<float2*>(dst + nt * 8 + c2) = make_float2(o[nt][0], o[nt][1]);
+    if ((lane & 3) == 0) {
       dst[D] = my_m;
       dst[D + 1] = my_l;
     }
@@ -563,16 +564,6 @@ int group_size(const fdma_fwd_params& p) {
   return 1;
 }
 
-template <int EPL, int G, bool kBf16>
-int launch_pipe(const DecodeParams& dp, dim3 grid, cudaStream_t stream) {
-  using L = PipeSmem<EPL, G>;
-  auto kern = decode_pipe_kernel<EPL, G, kBf16>;
-  const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
-  if (e != cudaSuccess) return static_cast<int>(e);
-  kern<<<grid, kThreads, L::kTotal, stream>>>(dp);
-  return static_cast<int>(cudaGetLastError());
-}
-
 // cp.async moves 16-byte pieces: K / V bases and row strides must keep rows 16-byte aligned
 bool pipe_ok(const DecodeParams& dp) {
   auto a16 = [](const void* x) { return (reinterpret_cast<uintptr_t>(x) & 15u) == 0; };
@@ -586,11 +577,25 @@ bool pipe_ok(const DecodeParams& dp) {
   return a16(dp.k) && a16(dp.v);
 }
 
+template <int D, bool kBf16>
+int launch_mma(const DecodeParams& dp, dim3 grid, cudaStream_t stream) {
+  using L = MmaSmem<D>;
+  auto kern = decode_mma_kernel<D, kBf16>;
+  const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  kern<<<grid, kThreads, L::kTotal, stream>>>(dp);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// the A fragments are read from Q with 32-bit loads
+bool mma_ok(const DecodeParams& dp) {
+  return pipe_ok(dp) && (reinterpret_cast<uintptr_t>(dp.q) & 3u) == 0 && dp.q_batch_stride % 2 == 0 &&
+         dp.q_head_stride % 2 == 0;
+}
+
 template <int EPL, bool kBf16>
 int launch_epl(const DecodeParams& dp, int G, dim3 grid, cudaStream_t stream) {
-  // (G = 8 at head dim 128 would spill at the register budget of three CTAs per SM: it stays on decode_kernel)
-  if (EPL <= 4 && G == 4 && pipe_ok(dp)) return launch_pipe<(EPL <= 4 ? EPL : 4), 4, kBf16>(dp, grid, stream);
-  if (EPL <= 2 && G == 8 && pipe_ok(dp)) return launch_pipe<(EPL <= 2 ? EPL : 2), 8, kBf16>(dp, grid, stream);
+  if (EPL <= 4 && G <= 8 && mma_ok(dp)) return launch_mma<(EPL <= 4 ? 32 * EPL : 128), kBf16>(dp, grid, stream);
   switch (G) {
     case 1: decode_kernel<EPL, 1, kBf16><<<grid, kThreads, 0, stream>>>(dp); break;
     case 2: decode_kernel<EPL, 2, kBf16><<<grid, kThreads, 0, stream>>>(dp); break;
@@ -644,7 +649,7 @@ int decode_fwd(const fdma_fwd_params& p, cudaStream_t stream) {
   dp.mask_batch_stride = p.mask_batch_stride; dp.mask_head_stride = p.mask_head_stride;
   dp.bias_batch_stride = p.bias_batch_stride; dp.bias_head_stride = p.bias_head_stride;
   dp.b = p.b; dp.seqlen_k = p.seqlen_k; dp.h = p.h; dp.h_k = p.h_k; dp.h_mask = p.h_mask; dp.h_bias = p.h_bias;
-  dp.group = p.h / p.h_k; dp.nsplit = ns;
+  dp.group = p.h / p.h_k; dp.nsplit = ns; dp.heads_per_cta = G;
   dp.scale_log2 = p.softmax_scale * 1.4426950408889634f;
   dim3 grid(ns, p.h / G, p.b);
   const bool bf = p.dtype == FDMA_BF16;

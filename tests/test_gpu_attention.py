@@ -270,9 +270,12 @@ DECODE_CASES = [
     ((2, 1, 9000, 8, 1, 256), "bcast", "topk", 64, "auto"),       # MQA, d=256, group of 8 -> fallback, very sparse
     ((2, 1, 2048, 8, 4, 256), "bcast", "topk", 700, "decode"),    # d=256, group of 2
     ((1, 1, 40, 2, 2, 128), "none", "none", 0, "decode"),         # shorter than one chunk per warp
-    ((2, 1, 20000, 8, 2, 128), "bcast", "topk", 1501, "decode"),  # group of 4: pipelined kernel, many drains, short tail batch
-    ((1, 1, 3000, 8, 1, 64), "bcast", "topk", 333, "decode"),     # group of 8 at d=64: pipelined kernel, 4-row batches
+    ((2, 1, 20000, 8, 2, 128), "bcast", "topk", 1501, "decode"),  # group of 4: many ring drains, short tail batch
+    ((1, 1, 3000, 8, 1, 64), "bcast", "topk", 333, "decode"),     # group of 8 at d=64
     ((1, 1, 1000, 4, 1, 64), "b1h1", "none", 0, "decode"),        # group of 4 at d=64, every key kept
+    ((2, 1, 6000, 8, 1, 128), "bcast", "topk", 777, "decode"),    # group of 8 at d=128: all eight rows of the quad layout
+    ((2, 1, 3000, 4, 2, 128), "bcast", "topk", 250, "decode"),    # group of 2 at d=128
+    ((1, 1, 2500, 3, 3, 128), "bcast", "topk", 90, "decode"),     # no grouping (MHA) at d=128, short tail batches
 ]
 
 
