@@ -35,6 +35,7 @@ constexpr int kBM = 64;   // query rows per step
 constexpr int kQStages = 3;
 constexpr int kThreads = 512;
 constexpr int kMaxAct = 4096;  // bytes of the per-CTA tile-activity table
+constexpr int kDetFracBits = 40;  // deterministic dQ: |dQ / scale| < 2^23, resolution 2^-40
 constexpr float kLog2e = 1.4426950408889634f;
 
 enum DbiasMode { kDbNone = 0, kDbColsum = 1, kDbDirect = 2, kDbAtomic = 3 };
@@ -50,7 +51,8 @@ struct BwdKernelParams {
   const void* bias;
   const float* lse2;   // (B,H,Sq_r) LSE * log2(e); +inf for empty and padded rows
   const float* dsum;   // (B,H,Sq_r) D = rowsum(dO o O)
-  float* dq_acc;       // (B,H,Sq,128) fp32, zeroed by the launcher
+  float* dq_acc;       // (B,H,Sq,128) fp32, zeroed by the launcher; deterministic kernels: the same shape in 64-bit
+                       // fixed point (kDetFracBits fractional bits), whose sums do not depend on the order of addition
   void* dk;
   void* dv;
   void* dbias;         // direct / column-sum modes: the output tensor
@@ -178,6 +180,34 @@ __global__ void bwd_convert_dq_kernel(const float* __restrict__ acc, void* __res
   }
 }
 
+// Deterministic mode: 64-bit fixed-point accumulator -> 16-bit dQ.
+template <bool kBf16>
+__global__ void bwd_convert_dq_fixed_kernel(const long long* __restrict__ acc, void* __restrict__ dq, int64_t n_vec,
+                                            int Sq, int H, int64_t sb, int64_t sr, int64_t sh, float scale) {
+  const float unit = scale * (1.0f / static_cast<float>(1ll << kDetFracBits));
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n_vec;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t e = i * 8;
+    const int dd = static_cast<int>(e % kD);
+    const int q = static_cast<int>((e / kD) % Sq);
+    const int h = static_cast<int>((e / (static_cast<int64_t>(kD) * Sq)) % H);
+    const int b = static_cast<int>(e / (static_cast<int64_t>(kD) * Sq * H));
+    float x[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const longlong2 v = *reinterpret_cast<const longlong2*>(acc + e + 2 * j);
+      x[2 * j] = __ll2float_rn(v.x) * unit;
+      x[2 * j + 1] = __ll2float_rn(v.y) * unit;
+    }
+    uint4 o;
+    o.x = pack_16x2<kBf16>(x[0], x[1]);
+    o.y = pack_16x2<kBf16>(x[2], x[3]);
+    o.z = pack_16x2<kBf16>(x[4], x[5]);
+    o.w = pack_16x2<kBf16>(x[6], x[7]);
+    *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(dq) + b * sb + q * sr + h * sh + dd) = o;
+  }
+}
+
 // fp32 (nb,nh,nr,nk) contiguous -> strided 16-bit dbias
 template <bool kBf16>
 __global__ void bwd_convert_dbias_kernel(const float* __restrict__ acc, void* __restrict__ out, int nb, int nh,
@@ -204,7 +234,7 @@ __device__ __forceinline__ uint16_t float_to_raw16(float x) {
   return static_cast<uint16_t>(pack_16x2<kBf16>(x, 0.f) & 0xFFFFu);
 }
 
-template <bool kBf16, bool kBcast>
+template <bool kBf16, bool kBcast, bool kDet>
 __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant__ BwdKernelParams p) {
   using L = SmemB;
   // Row-broadcast kernel: the two softmax warpgroups are two teams that take alternate steps (all 64 queries of
@@ -814,6 +844,38 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_dq_empty);  // dQ^T columns may be overwritten by the next step from here on
         float* gdst = p.dq_acc + ((static_cast<int64_t>(b) * p.h + h) * Sq + m * kBM) * kD;
+        if constexpr (kDet) {
+          // 64-bit fixed point: integer sums are the same in any order. 16 queries fill the staging tile.
+          long long* s_dq64 = reinterpret_cast<long long*>(s_dq);
+          long long* gdst64 = reinterpret_cast<long long*>(p.dq_acc) +
+                              ((static_cast<int64_t>(b) * p.h + h) * Sq + m * kBM) * kD;
+          constexpr float kFix = static_cast<float>(1ll << kDetFracBits);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            if (tid == 384) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            named_bar_sync(2, 128);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const uint32_t raw = c < 2 ? r0[(c & 1) * 16 + j] : r1[(c & 1) * 16 + j];
+              s_dq64[j * kD + dl] = __float2ll_rn(__uint_as_float(raw) * kFix);
+            }
+            fence_proxy_async_smem();
+            named_bar_sync(3, 128);
+            if (tid == 384) {
+              const int rows = min(16, Sq - (m * kBM + c * 16));
+              if (rows > 0) {
+                asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.u64 [%0], [%1], %2;"
+                             :
+                             : "l"(reinterpret_cast<uint64_t>(gdst64 + c * 16 * kD)), "r"(smem_u32(s_dq)),
+                               "r"(static_cast<uint32_t>(rows * kD * 8))
+                             : "memory");
+              }
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+          }
+          ++i;
+          continue;
+        }
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           if (tid == 384) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // staging tile free again
@@ -945,7 +1007,7 @@ BwdPlan plan(const fdma_bwd_params& bp) {
   const size_t rows = static_cast<size_t>(p.b) * p.h * pl.sq_r;
   pl.lse2_off = o; o += align256(rows * 4);
   pl.dsum_off = o; o += align256(rows * 4);
-  pl.dq_off = o;   o += align256(static_cast<size_t>(p.b) * p.seqlen_q * p.h * kD * 4);
+  pl.dq_off = o;   o += align256(static_cast<size_t>(p.b) * p.seqlen_q * p.h * kD * (bp.deterministic ? 8 : 4));
   pl.act_off = o;
   if (pl.needs_act)
     o += align256(static_cast<size_t>(p.b) * p.h_mask * ((p.seqlen_q + 127) / 128) * ((p.seqlen_k + 127) / 128));
@@ -996,7 +1058,7 @@ int launch(const fdma_bwd_params& bp, const BwdPlan& pl, cudaStream_t stream) {
   float* lse2 = reinterpret_cast<float*>(ws + pl.lse2_off);
   float* dsum = reinterpret_cast<float*>(ws + pl.dsum_off);
   float* dq_acc = reinterpret_cast<float*>(ws + pl.dq_off);
-  const size_t dq_bytes = static_cast<size_t>(p.b) * p.seqlen_q * p.h * kD * 4;
+  const size_t dq_bytes = static_cast<size_t>(p.b) * p.seqlen_q * p.h * kD * (bp.deterministic ? 8 : 4);
   cudaError_t e = cudaMemsetAsync(dq_acc, 0, dq_bytes, stream);
   if (e != cudaSuccess) return static_cast<int>(e);
   {
@@ -1054,7 +1116,8 @@ int launch(const fdma_bwd_params& bp, const BwdPlan& pl, cudaStream_t stream) {
   kp.scale_log2 = p.softmax_scale * kLog2e;
   kp.scale = p.softmax_scale;
 
-  auto kern = pl.bcast ? bwd_kernel<kBf16, true> : bwd_kernel<kBf16, false>;
+  auto kern = bp.deterministic ? (pl.bcast ? bwd_kernel<kBf16, true, true> : bwd_kernel<kBf16, false, true>)
+                               : (pl.bcast ? bwd_kernel<kBf16, true, false> : bwd_kernel<kBf16, false, false>);
   e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemB::kAlloc);
   if (e != cudaSuccess) return static_cast<int>(e);
   dim3 grid(((p.seqlen_k + kBN - 1) / kBN) * pl.nsplit, p.h_k, p.b);
@@ -1089,8 +1152,13 @@ int launch(const fdma_bwd_params& bp, const BwdPlan& pl, cudaStream_t stream) {
   {
     const int64_t n_vec = static_cast<int64_t>(p.b) * p.seqlen_q * p.h * kD / 8;
     const unsigned g = static_cast<unsigned>(std::min<int64_t>((n_vec + 255) / 256, 148 * 32));
-    bwd_convert_dq_kernel<kBf16><<<g, 256, 0, stream>>>(dq_acc, bp.dq, n_vec, p.seqlen_q, p.h, bp.dq_batch_stride,
-                                                        bp.dq_row_stride, bp.dq_head_stride, p.softmax_scale);
+    if (bp.deterministic)
+      bwd_convert_dq_fixed_kernel<kBf16><<<g, 256, 0, stream>>>(reinterpret_cast<const long long*>(dq_acc), bp.dq,
+                                                              n_vec, p.seqlen_q, p.h, bp.dq_batch_stride,
+                                                              bp.dq_row_stride, bp.dq_head_stride, p.softmax_scale);
+    else
+      bwd_convert_dq_kernel<kBf16><<<g, 256, 0, stream>>>(dq_acc, bp.dq, n_vec, p.seqlen_q, p.h, bp.dq_batch_stride,
+                                                          bp.dq_row_stride, bp.dq_head_stride, p.softmax_scale);
     e = cudaGetLastError();
     if (e != cudaSuccess) return static_cast<int>(e);
   }

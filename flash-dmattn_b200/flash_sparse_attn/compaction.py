@@ -196,7 +196,8 @@ def compact_forward(q: torch.Tensor, ck: CompactKeys, softmax_scale: float, is_c
 
 
 def compact_backward(dout, q, ck: CompactKeys, out, lse, softmax_scale: float, is_causal: bool, k_shape,
-                     bias_shape=None, causal_shift: Optional[int] = None, scatter: bool = True):
+                     bias_shape=None, causal_shift: Optional[int] = None, scatter: bool = True,
+                     deterministic: bool = False):
     """Backward over gathered keys, gradients scattered back to full shapes: returns dq, dk, dv (shape k_shape) and
     dbias (shape bias_shape, or None). Dimensions the bias broadcast over are summed. scatter=False returns the
     gradients of the gathered tensors themselves (dq, dk_c, dv_c, dbias_c)."""
@@ -223,6 +224,7 @@ def compact_backward(dout, q, ck: CompactKeys, out, lse, softmax_scale: float, i
             bp.dbias = dbias_c.data_ptr()
             bp.dbias_batch_stride, bp.dbias_head_stride, bp.dbias_row_stride = dbias_c.stride()[:3]
             bp.dbias_b, bp.dbias_h, bp.dbias_rows, bp.dbias_keys = dbias_c.shape
+        bp.deterministic = 1 if deterministic else 0
         ws_bytes = lib.fdma_bwd_workspace_bytes(ctypes.byref(bp))
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev) if ws_bytes else None
         if ws is not None:
@@ -252,13 +254,14 @@ def compact_backward(dout, q, ck: CompactKeys, out, lse, softmax_scale: float, i
 
 class _CompactAttnFunc(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, mask, bias, softmax_scale, is_causal, capacity, trusted):
+    def forward(ctx, q, k, v, mask, bias, softmax_scale, is_causal, capacity, trusted, deterministic=False):
         q = q if q.stride(-1) == 1 else q.contiguous()
         ck = compact_keys(k, v, mask, bias, capacity, check_capacity=not trusted)
         out, lse = compact_forward(q, ck, softmax_scale, is_causal)
         saved = [q, ck.key, ck.value, ck.mask, ck.key_pos, out, lse] + ([ck.bias] if ck.bias is not None else [])
         ctx.save_for_backward(*saved)
         ctx.has_bias = ck.bias is not None
+        ctx.deterministic = bool(deterministic)
         ctx.meta = (softmax_scale, is_causal, ck.seqlen_k, tuple(k.shape), tuple(bias.shape) if bias is not None else None)
         return out
 
@@ -269,8 +272,9 @@ class _CompactAttnFunc(torch.autograd.Function):
         bias_c = saved[7] if ctx.has_bias else None
         softmax_scale, is_causal, Sk, k_shape, bias_shape = ctx.meta
         ck = CompactKeys(k_c, v_c, mask_c, bias_c, key_pos, None, Sk)
-        dq, dk, dv, dbias = compact_backward(dout, q, ck, out, lse, softmax_scale, is_causal, k_shape, bias_shape)
-        return dq, dk, dv, None, dbias, None, None, None, None
+        dq, dk, dv, dbias = compact_backward(dout, q, ck, out, lse, softmax_scale, is_causal, k_shape, bias_shape,
+                                             deterministic=ctx.deterministic)
+        return dq, dk, dv, None, dbias, None, None, None, None, None
 
 
 def flash_sparse_attn_compact_func(
@@ -283,6 +287,7 @@ def flash_sparse_attn_compact_func(
     is_causal: Optional[bool] = None,
     capacity: Optional[int] = None,
     _trusted_capacity: bool = False,
+    deterministic: bool = False,
 ):
     """Same result as `flash_sparse_attn_func(query, key, value, attn_mask, attn_bias, softmax_scale, is_causal)`
     for a row-broadcast mask ({B|1}, {Hk|1}, 1, Sk) and bias ({B|1}, {H|Hk|1}, 1, Sk), computed over the kept keys
@@ -293,4 +298,4 @@ def flash_sparse_attn_compact_func(
     if attn_bias is not None and attn_bias.shape[-1] not in (1, key.shape[1]) and attn_bias.shape[-1] < key.shape[1]:
         raise RuntimeError("attn_bias has fewer keys than key")
     return _CompactAttnFunc.apply(query, key, value, attn_mask, attn_bias, softmax_scale, is_causal, capacity,
-                                  _trusted_capacity and capacity is not None)
+                                  _trusted_capacity and capacity is not None, bool(deterministic))

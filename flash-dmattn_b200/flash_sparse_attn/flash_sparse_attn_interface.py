@@ -408,7 +408,7 @@ def flash_sparse_attn_func(
         from .compaction import flash_sparse_attn_compact_func
 
         return flash_sparse_attn_compact_func(query, key, value, attn_mask, attn_bias, softmax_scale, is_causal, cap,
-                                              _trusted_capacity=True)
+                                              _trusted_capacity=True, deterministic=bool(deterministic))
     return FlashDMAttnFunc.apply(
         query, key, value, attn_mask, attn_bias, softmax_scale, is_causal, softcap, deterministic,
         return_attn_probs, torch.is_grad_enabled(),

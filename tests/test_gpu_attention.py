@@ -213,6 +213,38 @@ def test_tcgen05_backward_fp16_and_run_to_run_spread(dev, kernel_path):
     assert torch.equal(a[2], b[2]) and torch.equal(a[3], b[3])  # dK, dV have a fixed accumulation order
 
 
+@pytest.mark.parametrize("bias_kind,mask_kind", [("bcast", "topk"), ("perq", "randq")])
+def test_tcgen05_backward_deterministic(dev, kernel_path, bias_kind, mask_kind):
+    """deterministic=True (reference: per-split dQ buffers, csrc/flash_sparse_attn/flash_api.cpp:960-965): the d = 128
+    tensor-core backward accumulates dQ in 64-bit fixed point, so repeated runs give bit-identical gradients, and
+    the values still meet the oracle tolerance. 16 key tiles x 4 kv heads of CTAs add into every dQ tile."""
+    from flash_sparse_attn import flash_sparse_attn_func
+
+    kernel_path("tcgen05")
+    dtype = torch.bfloat16
+    q, k, v, mask, bias, dout = build_case(dev, 1, 2048, 2048, 8, 4, 128, bias_kind, mask_kind, 600, dtype, seed=5)
+    ref = oracle.attention_forward_backward(q, k, v, mask, bias, dout, None, True)
+
+    def run():
+        ql, kl, vl, bl = (t.detach().clone().requires_grad_(True) for t in (q, k, v, bias))
+        out = flash_sparse_attn_func(ql, kl, vl, attn_mask=mask, attn_bias=bl, is_causal=True, deterministic=True)
+        out.backward(dout)
+        return out.detach(), ql.grad, kl.grad, vl.grad, bl.grad
+
+    first = run()
+    torch.cuda.synchronize()
+    _kernel_status_ok()
+    check("out", first[0], ref[0], dtype)
+    check("dq", first[1], ref[2], dtype)
+    check("dk", first[2], ref[3], dtype, reduced=True)
+    check("dv", first[3], ref[4], dtype, reduced=True)
+    check("dbias", first[4], ref[5], dtype, reduced=True)
+    for _ in range(3):
+        again = run()
+        for name, a, b in zip(("out", "dq", "dk", "dv", "dbias"), first, again):
+            assert torch.equal(a, b), f"{name} differs between runs"
+
+
 TC_BWD256_CASES = [
     ((1, 384, 640, 4, 1, 256), "bcast", "topk", 200, True),     # MQA as in BASELINE config 5, Sq < Sk
     ((2, 300, 300, 4, 2, 256), "bcast", "block", 100, True),    # ragged, GQA, whole key tiles without a kept key
