@@ -162,6 +162,37 @@ __global__ void bwd256_convert_dq_kernel(const float* __restrict__ acc, void* __
   }
 }
 
+// Deterministic mode: the accumulator holds 64-bit fixed point (kDetFracBits256 fractional bits) instead of fp32.
+constexpr int kDetFracBits256 = 40;
+template <bool kBf16>
+__global__ void bwd256_convert_dq_fixed_kernel(const long long* __restrict__ acc, void* __restrict__ dq, int64_t n_vec,
+                                               int Sq, int H, int64_t sb, int64_t sr, int64_t sh, float scale) {
+  const float unit = scale * (1.0f / static_cast<float>(1ll << kDetFracBits256));
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n_vec;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t e = i * 8;
+    const int dd = static_cast<int>(e % 128);
+    const int q = static_cast<int>((e / 128) % Sq);
+    const int dh = static_cast<int>((e / (static_cast<int64_t>(128) * Sq)) % 2);
+    const int h = static_cast<int>((e / (static_cast<int64_t>(256) * Sq)) % H);
+    const int b = static_cast<int>(e / (static_cast<int64_t>(256) * Sq * H));
+    float x[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const longlong2 v = *reinterpret_cast<const longlong2*>(acc + e + 2 * j);
+      x[2 * j] = __ll2float_rn(v.x) * unit;
+      x[2 * j + 1] = __ll2float_rn(v.y) * unit;
+    }
+    uint4 o;
+    o.x = pack_16x2<kBf16>(x[0], x[1]);
+    o.y = pack_16x2<kBf16>(x[2], x[3]);
+    o.z = pack_16x2<kBf16>(x[4], x[5]);
+    o.w = pack_16x2<kBf16>(x[6], x[7]);
+    *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(dq) + b * sb + static_cast<int64_t>(q) * sr + h * sh +
+                              dh * 128 + dd) = o;
+  }
+}
+
 // Sum of the query-range partials of dK or dV: part [nsplit][B][h_k][keys_r][256] fp32 -> 16-bit (B, Sk, h_k, 256).
 template <bool kBf16>
 __global__ void __launch_bounds__(256) bwd256_reduce_dkv_kernel(const float* __restrict__ part, void* __restrict__ dst,
@@ -210,7 +241,7 @@ __global__ void __launch_bounds__(256) bwd256_reduce_dbias_kernel(const float* _
   reinterpret_cast<uint16_t*>(dst)[b * sb + hk * sh + key] = f_to_raw16<kBf16>(acc);
 }
 
-template <bool kBf16>
+template <bool kBf16, bool kDet>
 __global__ void __launch_bounds__(kThreads, 1) bwd256_kernel(const __grid_constant__ Bwd256Params p) {
   using L = Smem256;
   extern __shared__ unsigned char smem_dyn[];
@@ -612,6 +643,37 @@ __global__ void __launch_bounds__(kThreads, 1) bwd256_kernel(const __grid_consta
             mbar_arrive(bar_dq_empty);
           }
           float* gdst = p.dq_acc + (((static_cast<int64_t>(b) * p.h + h) * 2 + dh) * Sq + m * kBM) * 128;
+          if constexpr (kDet) {
+            // 64-bit fixed point: integer sums are the same in any order. 8 queries fill the staging tile.
+            long long* s_dq64 = reinterpret_cast<long long*>(s_dq);
+            long long* gdst64 = reinterpret_cast<long long*>(p.dq_acc) +
+                                (((static_cast<int64_t>(b) * p.h + h) * 2 + dh) * Sq + m * kBM) * 128;
+            constexpr float kFix = static_cast<float>(1ll << kDetFracBits256);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              if (tid == 384) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+              named_bar_sync(2, 128);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const uint32_t raw = c < 4 ? r0[(c & 3) * 8 + j] : r1[(c & 3) * 8 + j];
+                s_dq64[j * 128 + dl] = __float2ll_rn(__uint_as_float(raw) * kFix);
+              }
+              fence_proxy_async_smem();
+              named_bar_sync(3, 128);
+              if (tid == 384) {
+                const int rows = min(8, Sq - (m * kBM + c * 8));
+                if (rows > 0) {
+                  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.u64 [%0], [%1], %2;"
+                               :
+                               : "l"(reinterpret_cast<uint64_t>(gdst64 + c * 8 * 128)), "r"(smem_u32(s_dq)),
+                                 "r"(static_cast<uint32_t>(rows * 128 * 8))
+                               : "memory");
+                }
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+              }
+            }
+            continue;
+          }
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             if (tid == 384) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // staging tile free again
@@ -675,7 +737,7 @@ Plan256 plan256(const fdma_bwd_params& bp) {
   const size_t rows = static_cast<size_t>(p.b) * p.h * pl.sq_r;
   pl.lse2_off = o; o += align256(rows * 4);
   pl.dsum_off = o; o += align256(rows * 4);
-  pl.dq_off = o;   o += align256(static_cast<size_t>(p.b) * p.seqlen_q * p.h * kD * 4);
+  pl.dq_off = o;   o += align256(static_cast<size_t>(p.b) * p.seqlen_q * p.h * kD * (bp.deterministic ? 8 : 4));
   pl.part_off = pl.dbpart_off = o;
   if (pl.nsplit > 1) {
     const size_t keys_r = round_up(p.seqlen_k, kBN);
@@ -719,7 +781,8 @@ int launch256(const fdma_bwd_params& bp, const Plan256& pl, cudaStream_t stream)
   float* lse2 = reinterpret_cast<float*>(ws + pl.lse2_off);
   float* dsum = reinterpret_cast<float*>(ws + pl.dsum_off);
   float* dq_acc = reinterpret_cast<float*>(ws + pl.dq_off);
-  cudaError_t e = cudaMemsetAsync(dq_acc, 0, static_cast<size_t>(p.b) * p.seqlen_q * p.h * kD * 4, stream);
+  cudaError_t e = cudaMemsetAsync(dq_acc, 0, static_cast<size_t>(p.b) * p.seqlen_q * p.h * kD * (bp.deterministic ? 8 : 4),
+                                  stream);
   if (e != cudaSuccess) return static_cast<int>(e);
   {
     const int64_t warps = static_cast<int64_t>(p.b) * p.h * pl.sq_r;
@@ -762,7 +825,7 @@ int launch256(const fdma_bwd_params& bp, const Plan256& pl, cudaStream_t stream)
   kp.scale_log2 = p.softmax_scale * kLog2e;
   kp.scale = p.softmax_scale;
 
-  auto kern = bwd256_kernel<kBf16>;
+  auto kern = bp.deterministic ? bwd256_kernel<kBf16, true> : bwd256_kernel<kBf16, false>;
   e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem256::kAlloc);
   if (e != cudaSuccess) return static_cast<int>(e);
   dim3 grid(((p.seqlen_k + kBN - 1) / kBN) * pl.nsplit, p.h_k, p.b);
@@ -796,7 +859,12 @@ int launch256(const fdma_bwd_params& bp, const Plan256& pl, cudaStream_t stream)
   }
   const int64_t n_vec = static_cast<int64_t>(p.b) * p.seqlen_q * p.h * kD / 8;
   const unsigned g = static_cast<unsigned>(std::min<int64_t>((n_vec + 255) / 256, 148 * 32));
-  bwd256_convert_dq_kernel<kBf16><<<g, 256, 0, stream>>>(dq_acc, bp.dq, n_vec, p.seqlen_q, p.h, bp.dq_batch_stride,
+  if (bp.deterministic)
+    bwd256_convert_dq_fixed_kernel<kBf16><<<g, 256, 0, stream>>>(reinterpret_cast<const long long*>(dq_acc), bp.dq, n_vec,
+                                                               p.seqlen_q, p.h, bp.dq_batch_stride, bp.dq_row_stride,
+                                                               bp.dq_head_stride, p.softmax_scale);
+  else
+    bwd256_convert_dq_kernel<kBf16><<<g, 256, 0, stream>>>(dq_acc, bp.dq, n_vec, p.seqlen_q, p.h, bp.dq_batch_stride,
                                                            bp.dq_row_stride, bp.dq_head_stride, p.softmax_scale);
   return static_cast<int>(cudaGetLastError());
 }

@@ -119,9 +119,9 @@ typedef struct fdma_bwd_params {
   int64_t dbias_batch_stride, dbias_head_stride, dbias_row_stride;
   int32_t dbias_b, dbias_h, dbias_rows; /* extents of dbias dims 0..2 (1 where bias is broadcast) */
   int32_t dbias_keys;                   /* extent of the key dimension of dbias (>= Sk)          */
-  int32_t deterministic;                /* flash_api.cpp:809. Non-zero: the head-dim-128 tensor-core backward sums dQ in
+  int32_t deterministic;                /* flash_api.cpp:809. Non-zero: the tensor-core backward kernels sum dQ in
                                            64-bit fixed point (order-independent, bit-identical between runs; about 40 %
-                                           slower); the other backward kernels accumulate dQ with fp32 atomics either way.
+                                           slower); the CUDA-core backward accumulates dQ with fp32 atomics either way.
                                            dK, dV and dBias (except dBias shared across batch / kv heads) have a fixed
                                            summation order in both modes */
   int32_t reserved;

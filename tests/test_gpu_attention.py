@@ -213,16 +213,16 @@ def test_tcgen05_backward_fp16_and_run_to_run_spread(dev, kernel_path):
     assert torch.equal(a[2], b[2]) and torch.equal(a[3], b[3])  # dK, dV have a fixed accumulation order
 
 
-@pytest.mark.parametrize("bias_kind,mask_kind", [("bcast", "topk"), ("perq", "randq")])
-def test_tcgen05_backward_deterministic(dev, kernel_path, bias_kind, mask_kind):
-    """deterministic=True (reference: per-split dQ buffers, csrc/flash_sparse_attn/flash_api.cpp:960-965): the d = 128
-    tensor-core backward accumulates dQ in 64-bit fixed point, so repeated runs give bit-identical gradients, and
-    the values still meet the oracle tolerance. 16 key tiles x 4 kv heads of CTAs add into every dQ tile."""
+@pytest.mark.parametrize("d,bias_kind,mask_kind", [(128, "bcast", "topk"), (128, "perq", "randq"), (256, "bcast", "topk")])
+def test_tcgen05_backward_deterministic(dev, kernel_path, d, bias_kind, mask_kind):
+    """deterministic=True (reference: per-split dQ buffers, csrc/flash_sparse_attn/flash_api.cpp:960-965): the
+    tensor-core backward kernels accumulate dQ in 64-bit fixed point, so repeated runs give bit-identical gradients,
+    and the values still meet the oracle tolerance. 16 key tiles x 4 kv heads of CTAs add into every dQ tile."""
     from flash_sparse_attn import flash_sparse_attn_func
 
     kernel_path("tcgen05")
     dtype = torch.bfloat16
-    q, k, v, mask, bias, dout = build_case(dev, 1, 2048, 2048, 8, 4, 128, bias_kind, mask_kind, 600, dtype, seed=5)
+    q, k, v, mask, bias, dout = build_case(dev, 1, 2048, 2048, 8, 4, d, bias_kind, mask_kind, 600, dtype, seed=5)
     ref = oracle.attention_forward_backward(q, k, v, mask, bias, dout, None, True)
 
     def run():
