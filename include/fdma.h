@@ -121,9 +121,10 @@ typedef struct fdma_bwd_params {
   int32_t dbias_keys;                   /* extent of the key dimension of dbias (>= Sk)          */
   int32_t deterministic;                /* flash_api.cpp:809. Non-zero: the tensor-core backward kernels sum dQ in
                                            64-bit fixed point (order-independent, bit-identical between runs; about 40 %
-                                           slower); the CUDA-core backward accumulates dQ with fp32 atomics either way.
-                                           dK, dV and dBias (except dBias shared across batch / kv heads) have a fixed
-                                           summation order in both modes */
+                                           slower). The CUDA-core backward computes each dQ row in one warp (fixed order) but
+                                           sums dK, dV and dBias with fp32 atomics. On the tensor-core kernels dK, dV and
+                                           dBias (except dBias shared across batch / kv heads) have a fixed summation
+                                           order in both modes */
   int32_t reserved;
 } fdma_bwd_params;
 
