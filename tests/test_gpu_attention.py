@@ -190,6 +190,9 @@ TC_BWD_CASES = [
     ((2, 256, 256, 2, 2, 128), "b1h1", "none", 0, False),       # bias shared by the batch
     ((1, 512, 512, 4, 2, 128), "perq", "randqh", 0, False),     # per-query-head mask, tiles empty for some heads
     ((1, 1, 700, 8, 2, 128), "bcast", "topk", 100, False),      # single query row
+    ((1, 64, 256, 2, 2, 128), "bcast", "topk", 100, True),      # one step per CTA: only one softmax team ever works
+    ((1, 128, 256, 2, 2, 128), "bcast", "topk", 100, False),    # two steps per CTA
+    ((1, 192, 320, 2, 2, 128), "bcast", "topk", 90, False),     # three steps per CTA: odd count, teams uneven
 ]
 
 
