@@ -60,35 +60,45 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 // CTA can run its tear-down (TMEM free) instead of hanging the device.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s: far above any legitimate wait in these kernels
 
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtl& ctl, int code) {
-  const uint32_t addr = smem_u32(bar);
-  uint32_t done = 0;
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t addr, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred P1;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, P1;\n\t"
+      "}\n"
+      : "=r"(done)
+      : "r"(addr), "r"(parity)
+      : "memory");
+  return done;
+}
+// Most waits in these kernels find their barrier already complete: the first attempt is straight-line code, the
+// polling loop with its time limit follows only when it fails.
+__device__ __forceinline__ bool mbar_wait_slow(uint32_t addr, uint32_t parity, volatile int* abort_flag, int* status,
+                                            int code) {
   uint64_t t0 = 0;
   uint32_t spins = 0;
   while (true) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred P1;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, P1;\n\t"
-        "}\n"
-        : "=r"(done)
-        : "r"(addr), "r"(parity)
-        : "memory");
-    if (done) return true;
+    if (mbar_try_wait(addr, parity)) return true;
     ++spins;
     if ((spins & 63u) == 0u) {
-      if (*ctl.abort_flag) return false;
+      if (*abort_flag) return false;
       uint64_t now = globaltimer_ns();
       if (t0 == 0) {
         t0 = now;
       } else if (now - t0 > kWaitLimitNs) {
-        atomicCAS(ctl.status, 0, code);
-        *ctl.abort_flag = 1;
+        atomicCAS(status, 0, code);
+        *abort_flag = 1;
         return false;
       }
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtl& ctl, int code) {
+  const uint32_t addr = smem_u32(bar);
+  if (mbar_try_wait(addr, parity)) return true;
+  return mbar_wait_slow(addr, parity, ctl.abort_flag, ctl.status, code);
 }
 
 // ---------------------------------------------------------------------------------------------
