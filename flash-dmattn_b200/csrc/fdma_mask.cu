@@ -261,7 +261,7 @@ __device__ __forceinline__ uint32_t key_pair16(uint32_t u) {
 }
 
 template <int DT, int CHUNKS>
-__global__ void __launch_bounds__(kThreads, CHUNKS <= 4 ? 3 : 1) topk16_reg_kernel(const fdma_mask_params p) {
+__global__ void __launch_bounds__(kThreads, CHUNKS <= 4 ? 4 : 1) topk16_reg_kernel(const fdma_mask_params p) {
   using KT = KeyTraits<DT>;
   __shared__ int s_hist[kWarps][256];
   __shared__ int s_scan[CHUNKS * kWarps];
