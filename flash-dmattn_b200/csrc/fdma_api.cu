@@ -13,9 +13,12 @@ namespace fdma {
 
 namespace {
 
-__device__ int g_kernel_status = 0;
+// Per-device status block: [0] the code of the first bounded wait that gave up (0 = none), [2..3] the address of a
+// page-locked host int that mirrors it (so the host can poll without synchronising).
+__device__ __align__(16) int g_kernel_status[4] = {0, 0, 0, 0};
 std::mutex g_status_mutex;
 int* g_status_ptr[64] = {nullptr};
+volatile int* g_status_host[64] = {nullptr};
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -120,9 +123,49 @@ int* kernel_status_ptr() {
   if (!g_status_ptr[dev]) {
     void* ptr = nullptr;
     if (cudaGetSymbolAddress(&ptr, g_kernel_status) != cudaSuccess) return nullptr;
+    // Host mirror: 4 bytes of mapped page-locked memory per device (host memory, allocated once). If it cannot be
+    // had, the mirror stays off and only fdma_last_kernel_status sees a timeout.
+    int* host = nullptr;
+    void* host_dev = nullptr;
+    if (cudaHostAlloc(reinterpret_cast<void**>(&host), sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable) ==
+            cudaSuccess &&
+        cudaHostGetDevicePointer(&host_dev, host, 0) == cudaSuccess) {
+      *host = 0;
+      if (cudaMemcpy(static_cast<int*>(ptr) + 2, &host_dev, sizeof(void*), cudaMemcpyHostToDevice) == cudaSuccess)
+        g_status_host[dev] = host;
+    } else {
+      (void)cudaGetLastError();
+    }
     g_status_ptr[dev] = static_cast<int*>(ptr);
   }
   return g_status_ptr[dev];
+}
+
+int export_softmax_d(const fdma_bwd_params& bp, const float* dsum, int sq_r, cudaStream_t stream) {
+  if (!bp.softmax_d) return 0;
+  const fdma_fwd_params& p = bp.f;
+  const size_t rows = static_cast<size_t>(p.b) * p.h;
+  const size_t r128 = static_cast<size_t>(round_up(p.seqlen_q, 128));
+  cudaError_t e = cudaSuccess;
+  if (r128 > static_cast<size_t>(p.seqlen_q)) e = cudaMemsetAsync(bp.softmax_d, 0, rows * r128 * sizeof(float), stream);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  e = cudaMemcpy2DAsync(bp.softmax_d, r128 * sizeof(float), dsum, static_cast<size_t>(sq_r) * sizeof(float),
+                        static_cast<size_t>(p.seqlen_q) * sizeof(float), rows, cudaMemcpyDeviceToDevice, stream);
+  return static_cast<int>(e);
+}
+
+int sm_count() {
+  static std::mutex mu;
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
 }
 
 }  // namespace fdma
@@ -199,9 +242,14 @@ int fdma_bwd(const fdma_bwd_params* pp, void* stream_) {
 }
 
 int fdma_create_mask(const fdma_mask_params* p, void* stream_) {
-  if (!p || !p->bias || !p->out) return FDMA_ERR_BAD_ARG;
+  if (!p || !p->bias || (!p->out && !p->key_pos)) return FDMA_ERR_BAD_ARG;
   if (p->out_b < 0 || p->out_h < 0 || p->out_rows < 0 || p->keys < 0) return FDMA_ERR_BAD_ARG;
   if (p->kind != FDMA_MASK_TOPK && p->kind != FDMA_MASK_RELU) return FDMA_ERR_BAD_ARG;
+  if (p->key_pos) {  // position output: top-k selection without block smoothing, every selection must fit
+    if (!p->count || p->capacity <= 0) return FDMA_ERR_BAD_ARG;
+    if (p->kind != FDMA_MASK_TOPK || p->block_size > 1) return FDMA_ERR_UNSUPPORTED;
+    if (p->window <= 0 || p->capacity < (p->window < p->keys ? p->window : p->keys)) return FDMA_ERR_BAD_ARG;
+  }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (p->kind == FDMA_MASK_TOPK && p->window <= 0) {
     const size_t n = static_cast<size_t>(p->out_b) * p->out_h * p->out_rows * p->keys;
@@ -213,6 +261,15 @@ int fdma_create_mask(const fdma_mask_params* p, void* stream_) {
 void fdma_time_next_kernel(void* start_event, void* stop_event) {
   t_ev_start = static_cast<cudaEvent_t>(start_event);
   t_ev_stop = static_cast<cudaEvent_t>(stop_event);
+}
+
+int fdma_poll_kernel_status(int32_t* detail) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  volatile int* host = g_status_host[dev];
+  const int v = host ? *host : 0;
+  if (detail) *detail = v;
+  return v != 0 ? FDMA_ERR_TIMEOUT : 0;
 }
 
 int fdma_last_kernel_status(void* stream_, int32_t* detail) {
@@ -229,6 +286,8 @@ int fdma_last_kernel_status(void* stream_, int32_t* detail) {
     if (e != cudaSuccess) return static_cast<int>(e);
     e = cudaStreamSynchronize(stream);
     if (e != cudaSuccess) return static_cast<int>(e);
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64 && g_status_host[dev]) *g_status_host[dev] = 0;
     return FDMA_ERR_TIMEOUT;
   }
   return 0;

@@ -166,7 +166,8 @@ __global__ void bwd256_convert_dq_kernel(const float* __restrict__ acc, void* __
 constexpr int kDetFracBits256 = 40;
 template <bool kBf16>
 __global__ void bwd256_convert_dq_fixed_kernel(const long long* __restrict__ acc, void* __restrict__ dq, int64_t n_vec,
-                                               int Sq, int H, int64_t sb, int64_t sr, int64_t sh, float scale) {
+                                               int Sq, int H, int64_t sb, int64_t sr, int64_t sh, float scale,
+                                               const float* __restrict__ dsum, int sq_r) {
   const float unit = scale * (1.0f / static_cast<float>(1ll << kDetFracBits256));
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n_vec;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -182,6 +183,12 @@ __global__ void bwd256_convert_dq_fixed_kernel(const long long* __restrict__ acc
       const longlong2 v = *reinterpret_cast<const longlong2*>(acc + e + 2 * j);
       x[2 * j] = __ll2float_rn(v.x) * unit;
       x[2 * j + 1] = __ll2float_rn(v.y) * unit;
+    }
+    // Fixed point cannot carry NaN / Inf. A non-finite dO or O element makes D = rowsum(dO o O) of its row
+    // non-finite, and with it every dS of the row: such rows come out as NaN, as the fp32 path would give.
+    if (!isfinite(dsum[(static_cast<int64_t>(b) * H + h) * sq_r + q])) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = __int_as_float(0x7FC00000);
     }
     uint4 o;
     o.x = pack_16x2<kBf16>(x[0], x[1]);
@@ -720,9 +727,9 @@ struct Plan256 {
 // query dimension until about eight CTAs per SM exist; every split keeps at least 32 steps.
 int pick_nsplit256(const fdma_fwd_params& p) {
   const int64_t ctas = static_cast<int64_t>((p.seqlen_k + kBN - 1) / kBN) * p.h_k * p.b;
-  if (ctas >= 2 * 148) return 1;
+  if (ctas >= 2 * sm_count()) return 1;
   const int64_t steps = static_cast<int64_t>((p.seqlen_q + kBM - 1) / kBM) * (p.h / p.h_k);
-  const int64_t want = (8 * 148 + ctas - 1) / ctas;
+  const int64_t want = (8 * sm_count() + ctas - 1) / ctas;
   const int64_t cap = std::max<int64_t>(1, steps / 32);
   return static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(std::min(want, cap), 64)));
 }
@@ -792,6 +799,8 @@ int launch256(const fdma_bwd_params& bp, const Plan256& pl, cudaStream_t stream)
         p.o_head_stride, bp.do_batch_stride, bp.do_row_stride, bp.do_head_stride);
     e = cudaGetLastError();
     if (e != cudaSuccess) return static_cast<int>(e);
+    st = export_softmax_d(bp, dsum, pl.sq_r, stream);
+    if (st) return st;
   }
   kp.mask = static_cast<const uint8_t*>(p.mask);
   kp.bias = p.bias;
@@ -840,7 +849,7 @@ int launch256(const fdma_bwd_params& bp, const Plan256& pl, cudaStream_t stream)
   if (pl.nsplit > 1) {
     const int keys_r = static_cast<int>(round_up(p.seqlen_k, kBN));
     const int64_t n_vec = static_cast<int64_t>(p.b) * p.h_k * p.seqlen_k * (kD / 8);
-    const unsigned g = static_cast<unsigned>(std::min<int64_t>((n_vec + 255) / 256, 148 * 32));
+    const unsigned g = static_cast<unsigned>(std::min<int64_t>((n_vec + 255) / 256, sm_count() * 32));
     for (int which = 0; which < 2; ++which) {  // 0: dV, 1: dK
       const float* part = kp.dkv_part + static_cast<size_t>(which) * pl.nsplit * p.b * p.h_k * keys_r * kD;
       bwd256_reduce_dkv_kernel<kBf16><<<g, 256, 0, stream>>>(
@@ -858,11 +867,11 @@ int launch256(const fdma_bwd_params& bp, const Plan256& pl, cudaStream_t stream)
     if (e != cudaSuccess) return static_cast<int>(e);
   }
   const int64_t n_vec = static_cast<int64_t>(p.b) * p.seqlen_q * p.h * kD / 8;
-  const unsigned g = static_cast<unsigned>(std::min<int64_t>((n_vec + 255) / 256, 148 * 32));
+  const unsigned g = static_cast<unsigned>(std::min<int64_t>((n_vec + 255) / 256, sm_count() * 32));
   if (bp.deterministic)
     bwd256_convert_dq_fixed_kernel<kBf16><<<g, 256, 0, stream>>>(reinterpret_cast<const long long*>(dq_acc), bp.dq, n_vec,
                                                                p.seqlen_q, p.h, bp.dq_batch_stride, bp.dq_row_stride,
-                                                               bp.dq_head_stride, p.softmax_scale);
+                                                               bp.dq_head_stride, p.softmax_scale, dsum, pl.sq_r);
   else
     bwd256_convert_dq_kernel<kBf16><<<g, 256, 0, stream>>>(dq_acc, bp.dq, n_vec, p.seqlen_q, p.h, bp.dq_batch_stride,
                                                            bp.dq_row_stride, bp.dq_head_stride, p.softmax_scale);

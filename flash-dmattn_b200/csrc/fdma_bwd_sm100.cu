@@ -183,7 +183,8 @@ __global__ void bwd_convert_dq_kernel(const float* __restrict__ acc, void* __res
 // Deterministic mode: 64-bit fixed-point accumulator -> 16-bit dQ.
 template <bool kBf16>
 __global__ void bwd_convert_dq_fixed_kernel(const long long* __restrict__ acc, void* __restrict__ dq, int64_t n_vec,
-                                            int Sq, int H, int64_t sb, int64_t sr, int64_t sh, float scale) {
+                                            int Sq, int H, int64_t sb, int64_t sr, int64_t sh, float scale,
+                                            const float* __restrict__ dsum, int sq_r) {
   const float unit = scale * (1.0f / static_cast<float>(1ll << kDetFracBits));
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n_vec;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -198,6 +199,12 @@ __global__ void bwd_convert_dq_fixed_kernel(const long long* __restrict__ acc, v
       const longlong2 v = *reinterpret_cast<const longlong2*>(acc + e + 2 * j);
       x[2 * j] = __ll2float_rn(v.x) * unit;
       x[2 * j + 1] = __ll2float_rn(v.y) * unit;
+    }
+    // Fixed point cannot carry NaN / Inf. A non-finite dO or O element makes D = rowsum(dO o O) of its row
+    // non-finite, and with it every dS of the row: such rows come out as NaN, as the fp32 path would give.
+    if (!isfinite(dsum[(static_cast<int64_t>(b) * H + h) * sq_r + q])) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = __int_as_float(0x7FC00000);
     }
     uint4 o;
     o.x = pack_16x2<kBf16>(x[0], x[1]);
@@ -975,9 +982,9 @@ struct BwdPlan {
 int pick_nsplit(const fdma_fwd_params& p) {
   const int64_t ctas = static_cast<int64_t>((p.seqlen_k + kBN - 1) / kBN) * p.h_k * p.b;
   const bool causal = p.is_causal != 0 && p.seqlen_q > 1;
-  if (ctas >= (causal ? 8 : 2) * 148) return 1;
+  if (ctas >= (causal ? 8 : 2) * sm_count()) return 1;
   const int64_t steps = static_cast<int64_t>((p.seqlen_q + kBM - 1) / kBM) * (p.h / p.h_k);
-  const int64_t want = (8 * 148 + ctas - 1) / ctas;
+  const int64_t want = (8 * sm_count() + ctas - 1) / ctas;
   const int64_t cap = std::max<int64_t>(1, steps / 32);
   return static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(std::min(want, cap), 64)));
 }
@@ -1069,6 +1076,8 @@ int launch(const fdma_bwd_params& bp, const BwdPlan& pl, cudaStream_t stream) {
         p.o_head_stride, bp.do_batch_stride, bp.do_row_stride, bp.do_head_stride);
     e = cudaGetLastError();
     if (e != cudaSuccess) return static_cast<int>(e);
+    st = export_softmax_d(bp, dsum, pl.sq_r, stream);
+    if (st) return st;
   }
   kp.act = nullptr;
   if (pl.needs_act) {
@@ -1132,7 +1141,7 @@ int launch(const fdma_bwd_params& bp, const BwdPlan& pl, cudaStream_t stream) {
   if (pl.nsplit > 1) {
     const int keys_r = static_cast<int>(round_up(p.seqlen_k, kBN));
     const int64_t n_vec = static_cast<int64_t>(p.b) * p.h_k * p.seqlen_k * (kD / 8);
-    const unsigned g = static_cast<unsigned>(std::min<int64_t>((n_vec + 255) / 256, 148 * 32));
+    const unsigned g = static_cast<unsigned>(std::min<int64_t>((n_vec + 255) / 256, sm_count() * 32));
     for (int which = 0; which < 2; ++which) {  // 0: dV, 1: dK
       const float* part = kp.dkv_part + static_cast<size_t>(which) * pl.nsplit * p.b * p.h_k * keys_r * kD;
       bwd_reduce_dkv_kernel<kBf16><<<g, 256, 0, stream>>>(
@@ -1151,11 +1160,12 @@ int launch(const fdma_bwd_params& bp, const BwdPlan& pl, cudaStream_t stream) {
   }
   {
     const int64_t n_vec = static_cast<int64_t>(p.b) * p.seqlen_q * p.h * kD / 8;
-    const unsigned g = static_cast<unsigned>(std::min<int64_t>((n_vec + 255) / 256, 148 * 32));
+    const unsigned g = static_cast<unsigned>(std::min<int64_t>((n_vec + 255) / 256, sm_count() * 32));
     if (bp.deterministic)
       bwd_convert_dq_fixed_kernel<kBf16><<<g, 256, 0, stream>>>(reinterpret_cast<const long long*>(dq_acc), bp.dq,
                                                               n_vec, p.seqlen_q, p.h, bp.dq_batch_stride,
-                                                              bp.dq_row_stride, bp.dq_head_stride, p.softmax_scale);
+                                                              bp.dq_row_stride, bp.dq_head_stride, p.softmax_scale,
+                                                              dsum, pl.sq_r);
     else
       bwd_convert_dq_kernel<kBf16><<<g, 256, 0, stream>>>(dq_acc, bp.dq, n_vec, p.seqlen_q, p.h, bp.dq_batch_stride,
                                                           bp.dq_row_stride, bp.dq_head_stride, p.softmax_scale);
@@ -1164,7 +1174,7 @@ int launch(const fdma_bwd_params& bp, const BwdPlan& pl, cudaStream_t stream) {
   }
   if (pl.dbias_mode == kDbAtomic) {
     const int64_t ndb = static_cast<int64_t>(bp.dbias_b) * bp.dbias_h * bp.dbias_rows * bp.dbias_keys;
-    const unsigned g = static_cast<unsigned>(std::min<int64_t>((ndb + 255) / 256, 148 * 32));
+    const unsigned g = static_cast<unsigned>(std::min<int64_t>((ndb + 255) / 256, sm_count() * 32));
     bwd_convert_dbias_kernel<kBf16><<<g, 256, 0, stream>>>(kp.dbias_acc, bp.dbias, bp.dbias_b, bp.dbias_h,
                                                            bp.dbias_rows, bp.dbias_keys, bp.dbias_batch_stride,
                                                            bp.dbias_head_stride, bp.dbias_row_stride);

@@ -534,7 +534,7 @@ int pick_splits(const fdma_fwd_params& p, int ctas_per_split) {
   // ceil(splits * ctas_per_split / slots) rounds of 1 / splits of the work each: pick the split count with the
   // smallest product (a small charge per split covers the extra partials). Every split keeps at least four
   // 512-key pieces per warp... unless the row is shorter than that.
-  const int slots = 148 * 2;
+  const int slots = sm_count() * 2;
   const int max_by_len = std::max(1, (p.seqlen_k + 512 * kWarps * 4 - 1) / (512 * kWarps * 4));
   const int limit = std::min(max_by_len, 32);
   int best = 1;

@@ -744,12 +744,9 @@ int launch(const fdma_fwd_params& p, const FwdPlan& pl, cudaStream_t stream) {
   }
 
   auto kern = fwd_kernel<D, kBf16, kBcast>;
-  static bool attr_set = false;  // per template instantiation; setting it twice is harmless
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    attr_set = true;
-  }
+  // The attribute belongs to the (function, device) pair: set it on every call, whichever device is current.
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc);
+  if (e != cudaSuccess) return static_cast<int>(e);
   dim3 grid((p.seqlen_q + kNQ * kBM - 1) / (kNQ * kBM), p.h, p.b);
   cudaEvent_t ev0, ev1;
   take_timing_events(&ev0, &ev1);

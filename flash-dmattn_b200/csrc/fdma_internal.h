@@ -46,6 +46,13 @@ int create_mask(const fdma_mask_params& p, cudaStream_t stream);
 // Device address of the current device's kernel status word (written by bounded waits that give up).
 int* kernel_status_ptr();
 
+// Copies D = rowsum(dO o O) from a kernel's scratch layout (B*H rows of `sq_r` floats, zeros beyond Sq) into the
+// caller's optional fdma_bwd_params::softmax_d (B, H, round_up(Sq,128)); no-op when that pointer is null.
+int export_softmax_d(const fdma_bwd_params& bp, const float* dsum, int sq_r, cudaStream_t stream);
+
+// Number of SMs of the current device (cudaDevAttrMultiProcessorCount, cached per device).
+int sm_count();
+
 // Events registered by fdma_time_next_kernel for this host thread (both null when none); take_* clears them.
 void take_timing_events(cudaEvent_t* start, cudaEvent_t* stop);
 

@@ -82,8 +82,21 @@ __device__ __forceinline__ RowPtrs locate(const fdma_mask_params& p, int64_t row
   rp.pm = p.premask ? static_cast<const uint8_t*>(p.premask) + b * p.pm_batch_stride + h * p.pm_head_stride +
                           r * p.pm_row_stride
                     : nullptr;
-  rp.out = static_cast<uint8_t*>(p.out) + row * p.keys;
+  rp.out = p.out ? static_cast<uint8_t*>(p.out) + row * p.keys : nullptr;
   return rp;
+}
+
+// Position output of a row, after its selected keys were written to slots [0, total): the row's count, INT32_MAX in
+// the unused slots, and the optional slot mask (slot < count).
+__device__ __forceinline__ void finish_positions(const fdma_mask_params& p, int64_t row, int total, int tid,
+                                                 int nthreads) {
+  if (tid == 0) p.count[row] = total;
+  int32_t* prow = p.key_pos + row * p.capacity;
+  uint8_t* mrow = p.slot_mask ? static_cast<uint8_t*>(p.slot_mask) + row * p.capacity : nullptr;
+  for (int s = tid; s < p.capacity; s += nthreads) {
+    if (s >= total) prow[s] = 0x7FFFFFFF;
+    if (mrow) mrow[s] = s < total ? 1 : 0;
+  }
 }
 
 template <int DT, bool STAGED>
@@ -183,7 +196,7 @@ __global__ void __launch_bounds__(kThreads) topk_mask_kernel(const fdma_mask_par
   const bool all_eq = need_eq >= s_eq_total;
 
   // Write pass, kPerThread consecutive keys per thread, ties ranked by a block-wide running count.
-  int base_eq = 0;
+  int base_eq = 0, base_sel = 0;
   for (int c0 = 0; c0 < n; c0 += kChunk) {
     const int k0 = c0 + tid * kPerThread;
     uint32_t keys[kPerThread];
@@ -226,17 +239,51 @@ __global__ void __launch_bounds__(kThreads) topk_mask_kernel(const fdma_mask_par
       }
       o[j] = (sel && key != min_key) ? 1 : 0;
     }
-    if (k0 + kPerThread <= n && ((reinterpret_cast<uintptr_t>(rp.out + k0) & 7u) == 0)) {
-      uint2 v;
-      v.x = o[0] | (o[1] << 8) | (o[2] << 16) | (o[3] << 24);
-      v.y = o[4] | (o[5] << 8) | (o[6] << 16) | (o[7] << 24);
-      *reinterpret_cast<uint2*>(rp.out + k0) = v;
-    } else {
+    if (rp.out) {
+      if (k0 + kPerThread <= n && ((reinterpret_cast<uintptr_t>(rp.out + k0) & 7u) == 0)) {
+        uint2 v;
+        v.x = o[0] | (o[1] << 8) | (o[2] << 16) | (o[3] << 24);
+        v.y = o[4] | (o[5] << 8) | (o[6] << 16) | (o[7] << 24);
+        *reinterpret_cast<uint2*>(rp.out + k0) = v;
+      } else {
 #pragma unroll
-      for (int j = 0; j < kPerThread; ++j)
-        if (k0 + j < n) rp.out[k0 + j] = o[j];
+        for (int j = 0; j < kPerThread; ++j)
+          if (k0 + j < n) rp.out[k0 + j] = o[j];
+      }
+    }
+    if (p.key_pos) {  // ascending positions of the selected keys: block-wide running count of selections
+      int cnt = 0;
+#pragma unroll
+      for (int j = 0; j < kPerThread; ++j) cnt += (k0 + j < n && o[j]) ? 1 : 0;
+      int incl = cnt;
+#pragma unroll
+      for (int s = 1; s < 32; s <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, s);
+        if (lane >= s) incl += v;
+      }
+      if (lane == 31) s_scan[warp] = incl;
+      __syncthreads();
+      int warp_base = 0, total = 0;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) {
+        const int v = s_scan[w];
+        if (w < warp) warp_base += v;
+        total += v;
+      }
+      int slot = base_sel + warp_base + incl - cnt;
+      int32_t* prow = p.key_pos + static_cast<int64_t>(blockIdx.x) * p.capacity;
+#pragma unroll
+      for (int j = 0; j < kPerThread; ++j) {
+        if (k0 + j < n && o[j]) {
+          if (slot < p.capacity) prow[slot] = k0 + j;
+          ++slot;
+        }
+      }
+      base_sel += total;
+      __syncthreads();
     }
   }
+  if (p.key_pos) finish_positions(p, blockIdx.x, base_sel, tid, kThreads);
 }
 
 
@@ -260,7 +307,8 @@ __device__ __forceinline__ uint32_t key_pair16(uint32_t u) {
   return key | nan;
 }
 
-template <int DT, int CHUNKS>
+// kPos: also (or, with a null `out`, only) writes the ascending positions of the selected keys.
+template <int DT, int CHUNKS, bool kPos>
 __global__ void __launch_bounds__(kThreads, CHUNKS <= 4 ? 4 : 1) topk16_reg_kernel(const fdma_mask_params p) {
   using KT = KeyTraits<DT>;
   __shared__ int s_hist[kWarps][256];
@@ -399,6 +447,9 @@ __global__ void __launch_bounds__(kThreads, CHUNKS <= 4 ? 4 : 1) topk16_reg_kern
   const bool check_min = thr <= min_key;  // only then can a selected key hold the value min_dtype
 
   // ---- write pass: two output bytes per packed word (bit 0 = low key, bit 8 = high key) ----
+  uint32_t selbits[(CHUNKS + 3) / 4];
+#pragma unroll
+  for (int i = 0; i < (CHUNKS + 3) / 4; ++i) selbits[i] = 0u;
   auto emit = [&](int c, uint32_t (&ob)[4]) {
     const int k = c * kChunk + tid * kPerThread;
     if (k >= n) return;
@@ -412,7 +463,11 @@ __global__ void __launch_bounds__(kThreads, CHUNKS <= 4 ? 4 : 1) topk16_reg_kern
     uint2 o;
     o.x = ob[0] | (ob[1] << 16);
     o.y = ob[2] | (ob[3] << 16);
-    *reinterpret_cast<uint2*>(rp.out + k) = o;
+    if (!kPos || rp.out) *reinterpret_cast<uint2*>(rp.out + k) = o;
+    if (kPos) {  // bit j of the chunk's byte = key k + j selected
+      const uint32_t b8 = (((o.x & 0x01010101u) * 0x01020408u) >> 24) | ((((o.y & 0x01010101u) * 0x01020408u) >> 24) << 4);
+      selbits[c >> 2] |= b8 << ((c & 3) * 8);
+    }
   };
   if (all_eq) {  // every key equal to the threshold is kept
 #pragma unroll
@@ -483,6 +538,47 @@ __global__ void __launch_bounds__(kThreads, CHUNKS <= 4 ? 4 : 1) topk16_reg_kern
       emit(c, ob);
     }
   }
+  if (kPos) {
+    // ascending positions: selections are counted chunk by chunk, thread by thread, with one block-wide scan
+    __syncthreads();  // s_scan may still be read by the tie ranking above
+    int excl[CHUNKS];
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      const int cnt = __popc((selbits[c >> 2] >> ((c & 3) * 8)) & 0xFFu);
+      int incl = cnt;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+      }
+      excl[c] = incl - cnt;
+      if (lane == 31) s_scan[c * kWarps + warp] = incl;
+    }
+    __syncthreads();
+    int32_t* prow = p.key_pos + row * p.capacity;
+    int base = 0;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      int warp_base = 0, total = 0;
+#pragma unroll
+      for (int w = 0; w < kWarps; ++w) {
+        const int v = s_scan[c * kWarps + w];
+        if (w < warp) warp_base += v;
+        total += v;
+      }
+      uint32_t bits = (selbits[c >> 2] >> ((c & 3) * 8)) & 0xFFu;
+      int slot = base + warp_base + excl[c];
+      const int k = c * kChunk + tid * kPerThread;
+      while (bits) {
+        const int j = __ffs(bits) - 1;
+        bits &= bits - 1;
+        if (slot < p.capacity) prow[slot] = k + j;
+        ++slot;
+      }
+      base += total;
+    }
+    finish_positions(p, row, base, tid, kThreads);
+  }
   __syncthreads();  // the shared selection state is rewritten at the top of the next row
   }  // row loop
 }
@@ -497,17 +593,22 @@ bool reg_path_ok(const fdma_mask_params& p) {
     if (reinterpret_cast<uintptr_t>(p.premask) & 7u) return false;
     if (p.pm_batch_stride % 8 || p.pm_head_stride % 8 || p.pm_row_stride % 8) return false;
   }
-  return (reinterpret_cast<uintptr_t>(p.out) & 7u) == 0;
+  return (reinterpret_cast<uintptr_t>(p.out) & 7u) == 0;  // a null `out` (positions only) passes
 }
 
+template <int DT, bool kPos>
+void launch_reg_p(const fdma_mask_params& p, unsigned rows, cudaStream_t stream) {
+  const int chunks = (p.keys + kChunk - 1) / kChunk;
+  if (chunks <= 1) topk16_reg_kernel<DT, 1, kPos><<<rows, kThreads, 0, stream>>>(p);
+  else if (chunks <= 2) topk16_reg_kernel<DT, 2, kPos><<<rows, kThreads, 0, stream>>>(p);
+  else if (chunks <= 4) topk16_reg_kernel<DT, 4, kPos><<<rows, kThreads, 0, stream>>>(p);
+  else if (chunks <= 8) topk16_reg_kernel<DT, 8, kPos><<<rows, kThreads, 0, stream>>>(p);
+  else topk16_reg_kernel<DT, 16, kPos><<<rows, kThreads, 0, stream>>>(p);
+}
 template <int DT>
 void launch_reg(const fdma_mask_params& p, unsigned rows, cudaStream_t stream) {
-  const int chunks = (p.keys + kChunk - 1) / kChunk;
-  if (chunks <= 1) topk16_reg_kernel<DT, 1><<<rows, kThreads, 0, stream>>>(p);
-  else if (chunks <= 2) topk16_reg_kernel<DT, 2><<<rows, kThreads, 0, stream>>>(p);
-  else if (chunks <= 4) topk16_reg_kernel<DT, 4><<<rows, kThreads, 0, stream>>>(p);
-  else if (chunks <= 8) topk16_reg_kernel<DT, 8><<<rows, kThreads, 0, stream>>>(p);
-  else topk16_reg_kernel<DT, 16><<<rows, kThreads, 0, stream>>>(p);
+  if (p.key_pos) launch_reg_p<DT, true>(p, rows, stream);
+  else launch_reg_p<DT, false>(p, rows, stream);
 }
 
 template <int DT>
@@ -574,7 +675,7 @@ int launch_mask(const fdma_mask_params& p, cudaStream_t stream) {
   if (p.block_size > 1) {
     const int nblk = (p.keys + p.block_size - 1) / p.block_size;
     const int64_t warps = rows * nblk;
-    const unsigned g = static_cast<unsigned>(std::min<int64_t>((warps + 7) / 8, 148 * 32));
+    const unsigned g = static_cast<unsigned>(std::min<int64_t>((warps + 7) / 8, sm_count() * 32));
     block_smooth_kernel<<<g, 256, 0, stream>>>(static_cast<uint8_t*>(p.out), rows, p.keys, p.block_size);
     e = cudaGetLastError();
   }

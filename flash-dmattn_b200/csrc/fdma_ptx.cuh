@@ -12,9 +12,11 @@ namespace fdma {
 // Bounded waits report through a per-device status word in global memory (first writer wins) and a
 // CTA-wide abort flag in shared memory that makes every other wait of the CTA give up as well.
 // ---------------------------------------------------------------------------------------------
+constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s: far above any legitimate wait in these kernels
+
 struct WaitCtl {
   volatile int* abort_flag;  // shared memory, one per CTA
-  int* status;               // global memory, one per device
+  int* status;               // global memory, one per device: [0] code, [2..3] address of the host-visible mirror
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -56,10 +58,9 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
                : "memory");
 }
 // Bounded wait. Returns false if the CTA-wide abort flag is (or becomes) set. A wait that lasts longer
-// than `kWaitLimitNs` records `code` in the status word, sets the abort flag and returns false, so the
-// CTA can run its tear-down (TMEM free) instead of hanging the device.
-constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s: far above any legitimate wait in these kernels
-
+// than the limit (`kWaitLimitNs`, or the one given to mbar_wait_limit) records `code` in the status word and in its
+// host-visible mirror, sets the abort flag and returns false, so the CTA can run its tear-down (TMEM free) instead
+// of hanging the device.
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t addr, uint32_t parity) {
   uint32_t done;
   asm volatile(
@@ -75,8 +76,18 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t addr, uint32_t parity
 }
 // Most waits in these kernels find their barrier already complete: the first attempt is straight-line code, the
 // polling loop with its time limit follows only when it fails.
+__device__ __forceinline__ void record_wait_timeout(int* status, int code) {
+  if (atomicCAS(status, 0, code) == 0) {
+    // first writer: mirror the code into page-locked host memory, where the host can see it without a sync
+    int* host = *reinterpret_cast<int* volatile*>(status + 2);
+    if (host) {
+      *reinterpret_cast<volatile int*>(host) = code;
+      __threadfence_system();
+    }
+  }
+}
 __device__ __forceinline__ bool mbar_wait_slow(uint32_t addr, uint32_t parity, volatile int* abort_flag, int* status,
-                                            int code) {
+                                            int code, uint64_t limit_ns) {
   uint64_t t0 = 0;
   uint32_t spins = 0;
   while (true) {
@@ -87,8 +98,8 @@ __device__ __forceinline__ bool mbar_wait_slow(uint32_t addr, uint32_t parity, v
       uint64_t now = globaltimer_ns();
       if (t0 == 0) {
         t0 = now;
-      } else if (now - t0 > kWaitLimitNs) {
-        atomicCAS(status, 0, code);
+      } else if (now - t0 > limit_ns) {
+        record_wait_timeout(status, code);
         *abort_flag = 1;
         return false;
       }
@@ -98,7 +109,14 @@ __device__ __forceinline__ bool mbar_wait_slow(uint32_t addr, uint32_t parity, v
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtl& ctl, int code) {
   const uint32_t addr = smem_u32(bar);
   if (mbar_try_wait(addr, parity)) return true;
-  return mbar_wait_slow(addr, parity, ctl.abort_flag, ctl.status, code);
+  return mbar_wait_slow(addr, parity, ctl.abort_flag, ctl.status, code, kWaitLimitNs);
+}
+// Same wait with a caller-chosen limit (the self-test uses a short one).
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, const WaitCtl& ctl, int code,
+                                                uint64_t limit_ns) {
+  const uint32_t addr = smem_u32(bar);
+  if (mbar_try_wait(addr, parity)) return true;
+  return mbar_wait_slow(addr, parity, ctl.abort_flag, ctl.status, code, limit_ns);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -181,6 +181,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
     dsum = fmaf(g, to_f32(op[i]), dsum);
   }
   const float D = warp_sum(dsum);
+  if (bp.softmax_d && lane == 0)
+    bp.softmax_d[(static_cast<int64_t>(c.b) * p.h + c.h) * ((p.seqlen_q + 127) / 128 * 128) + c.q] = D;
   __syncwarp();
   const float lse = p.lse[(static_cast<int64_t>(c.b) * p.h + c.h) * p.seqlen_q + c.q];
   const T* kbase = static_cast<const T*>(p.k) + c.b * p.k_batch_stride + c.hk * p.k_head_stride;
@@ -317,6 +319,10 @@ int simt_bwd_t(const fdma_bwd_params& bp, cudaStream_t stream) {
     e = cudaMemsetAsync(ws, 0, lay.total, stream);
     if (e != cudaSuccess) return static_cast<int>(e);
   }
+  if (bp.softmax_d && p.seqlen_q % 128 != 0) {  // padding columns read as zero
+    e = cudaMemsetAsync(bp.softmax_d, 0, static_cast<size_t>(p.b) * p.h * round_up(p.seqlen_q, 128) * sizeof(float), stream);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
   float* dk_acc = reinterpret_cast<float*>(ws + lay.dk_off);
   float* dv_acc = reinterpret_cast<float*>(ws + lay.dv_off);
   float* db_acc = bp.dbias ? reinterpret_cast<float*>(ws + lay.dbias_off) : nullptr;
@@ -329,7 +335,7 @@ int simt_bwd_t(const fdma_bwd_params& bp, cudaStream_t stream) {
   }
   const int64_t nkv = static_cast<int64_t>(p.b) * p.seqlen_k * p.h_k * p.d;
   if (nkv > 0) {
-    const unsigned g = static_cast<unsigned>(std::min<int64_t>((nkv + 255) / 256, 148 * 16));
+    const unsigned g = static_cast<unsigned>(std::min<int64_t>((nkv + 255) / 256, sm_count() * 16));
     convert_kv_grad_kernel<T><<<g, 256, 0, stream>>>(dk_acc, static_cast<T*>(bp.dk), p.b, p.seqlen_k, p.h_k, p.d,
                                                      bp.dk_batch_stride, bp.dk_row_stride, bp.dk_head_stride);
     convert_kv_grad_kernel<T><<<g, 256, 0, stream>>>(dv_acc, static_cast<T*>(bp.dv), p.b, p.seqlen_k, p.h_k, p.d,
@@ -338,7 +344,7 @@ int simt_bwd_t(const fdma_bwd_params& bp, cudaStream_t stream) {
   if (bp.dbias) {
     const int64_t ndb = static_cast<int64_t>(bp.dbias_b) * bp.dbias_h * bp.dbias_rows * bp.dbias_keys;
     if (ndb > 0) {
-      const unsigned g = static_cast<unsigned>(std::min<int64_t>((ndb + 255) / 256, 148 * 16));
+      const unsigned g = static_cast<unsigned>(std::min<int64_t>((ndb + 255) / 256, sm_count() * 16));
       convert_dbias_kernel<T><<<g, 256, 0, stream>>>(db_acc, static_cast<T*>(bp.dbias), bp.dbias_b, bp.dbias_h,
                                                      bp.dbias_rows, bp.dbias_keys, bp.dbias_batch_stride,
                                                      bp.dbias_head_stride, bp.dbias_row_stride);

@@ -1,19 +1,23 @@
 // fdma_fwd_static_scratch: the forward pass for hosts that cannot hand the library a scratch buffer.
 //
-// fdma_fwd needs caller-provided scratch when the mask differs per query row (one activity byte per 128x128 tile,
-// written by a small pre-kernel and read by the attention kernel). Some hosts have no way to provide it at call
+// fdma_fwd needs caller-provided scratch in two cases: when the mask differs per query row (one activity byte per
+// 128x128 tile, written by a small pre-kernel and read by the attention kernel), and for single-query (decode) calls
+// (per-split partial results that a merge kernel combines). Some hosts have no way to provide it at call
 // time: an engine whose device memory is carved up once at start-up and that exposes no allocator to its
 // operators, or a latency-critical loop in which cudaMalloc (which may synchronise the whole device) is off
 // limits. For them this entry point keeps the scratch in a fixed array that is part of the library image.
 //
 // Properties a caller has to know
-//  * Limit: kStaticScratchBytes (1 MiB) of scratch, i.e. B * h_mask * ceil(Sq/128) * ceil(Sk/128) <= 1048576 tiles;
-//    larger problems are refused with FDMA_ERR_TOO_LARGE before anything is launched.
+//  * Limit: kStaticScratchBytes (1 MiB) of scratch, compared with fdma_fwd_workspace_bytes(p): for a per-query mask
+//    B * h_mask * ceil(Sq/128) * ceil(Sk/128) activity bytes; for a single-query call the decode partials
+//    B * H * splits * 8 * (d + 2) * 4 bytes. Larger problems are refused with FDMA_ERR_TOO_LARGE before anything is
+//    launched.
 //  * Cost: every GPU on which the library is loaded holds this 1 MiB until the process exits.
 //  * The first call on each device looks up the array's device address (one cudaGetSymbolAddress); make that first
 //    call outside any stream capture. No call allocates or frees memory.
-//  * All calls on a device share the one array, and it keeps whatever the previous call left in it. The pre-kernel
-//    rewrites every byte the attention kernel later reads, so nothing needs clearing between calls -- but two calls
+//  * All calls on a device share the one array, and it keeps whatever the previous call left in it. Every byte a
+//    call later reads it has written itself first (the activity pre-kernel covers all tiles, every decode warp
+//    writes its own partial), so nothing needs clearing between calls -- but two calls
 //    whose GPU work overlaps (different streams, or different host threads) race on it. Serialise them.
 #include <cuda_runtime.h>
 

@@ -36,6 +36,7 @@ class BwdParams(Structure):
         + [(f"{t}_{s}_stride", c_int64) for t in ("dq", "dk", "dv") for s in ("batch", "row", "head")]
         + [(f"dbias_{s}_stride", c_int64) for s in ("batch", "head", "row")]
         + [(n, c_int32) for n in ("dbias_b", "dbias_h", "dbias_rows", "dbias_keys", "deterministic", "reserved")]
+        + [("softmax_d", c_void_p)]
     )
 
 
@@ -46,6 +47,7 @@ class MaskParams(Structure):
         + [(f"pm_{s}_stride", c_int64) for s in ("batch", "head", "row")]
         + [(n, c_int32) for n in ("out_b", "out_h", "out_rows", "keys", "window", "dtype", "kind", "block_size")]
         + [("min_value", c_float)]
+        + [("key_pos", c_void_p), ("count", c_void_p), ("slot_mask", c_void_p), ("capacity", c_int32), ("reserved", c_int32)]
     )
 
 
@@ -59,12 +61,15 @@ EXPORTED_SYMBOLS = (
     "fdma_bwd",
     "fdma_create_mask",
     "fdma_last_kernel_status",
+    "fdma_poll_kernel_status",
+    "fdma_selftest_wait_timeout",
     "fdma_time_next_kernel",
     "fdma_fwd_static_scratch",
     "fdma_static_scratch_limit",
     "fdma_compact_index",
     "fdma_gather_rows",
     "fdma_scatter_rows",
+    "fdma_merge_partials",
 )
 
 
@@ -89,6 +94,16 @@ class RowsParams(ctypes.Structure):
         ("dst_batch_stride", c_int64), ("dst_row_stride", c_int64), ("dst_head_stride", c_int64),
         ("b", c_int32), ("heads", c_int32), ("h_pos", c_int32), ("rows_full", c_int32),
         ("capacity", c_int32), ("row_elems", c_int32), ("dtype", c_int32), ("reserved_", c_int32),
+    ]
+
+
+class MergeParams(ctypes.Structure):
+    """fdma_merge_params of include/fdma.h."""
+
+    _fields_ = [
+        ("acc", c_void_p), ("lse_acc", c_void_p), ("part", c_void_p), ("lse_part", c_void_p),
+        ("part_batch_stride", c_int64), ("part_row_stride", c_int64), ("part_head_stride", c_int64),
+        ("b", c_int32), ("seqlen_q", c_int32), ("h", c_int32), ("d", c_int32), ("dtype", c_int32), ("reserved", c_int32),
     ]
 
 
@@ -121,6 +136,10 @@ def load():
     lib.fdma_create_mask.argtypes = [POINTER(MaskParams), c_void_p]
     lib.fdma_last_kernel_status.restype = c_int
     lib.fdma_last_kernel_status.argtypes = [c_void_p, POINTER(c_int32)]
+    lib.fdma_poll_kernel_status.restype = c_int
+    lib.fdma_poll_kernel_status.argtypes = [POINTER(c_int32)]
+    lib.fdma_selftest_wait_timeout.restype = c_int
+    lib.fdma_selftest_wait_timeout.argtypes = [ctypes.c_uint32, c_void_p, c_void_p]
     lib.fdma_fwd_static_scratch.restype = c_int
     lib.fdma_fwd_static_scratch.argtypes = [POINTER(FwdParams), c_void_p]
     lib.fdma_static_scratch_limit.restype = c_size_t
@@ -130,6 +149,8 @@ def load():
     lib.fdma_gather_rows.argtypes = [POINTER(RowsParams), c_void_p]
     lib.fdma_scatter_rows.restype = c_int
     lib.fdma_scatter_rows.argtypes = [POINTER(RowsParams), c_void_p]
+    lib.fdma_merge_partials.restype = c_int
+    lib.fdma_merge_partials.argtypes = [POINTER(MergeParams), c_void_p]
     lib.fdma_time_next_kernel.restype = None
     lib.fdma_time_next_kernel.argtypes = [c_void_p, c_void_p]
     _lib = lib

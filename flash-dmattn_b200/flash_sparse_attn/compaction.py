@@ -12,16 +12,17 @@ The reference's CUDA backend has no such path; its Triton prototype gathers the 
 way (flash_sparse_attn/flash_dmattn_triton.py:49-211). `flash_sparse_attn_func` takes this route by itself for the
 mask shapes it fits (see `set_compaction`); `flash_sparse_attn_compact_func` asks for it explicitly.
 """
-from typing import NamedTuple, Optional
+from typing import NamedTuple, Optional, Tuple
 
 import ctypes
 import torch
 
 from . import _lib
-from .flash_sparse_attn_interface import (_bsh, _check_inputs, _dtype_code, _fill_fwd, _stream_ptr, round_multiple)
+from .flash_sparse_attn_interface import (_bsh, _check_inputs, _dtype_code, _fill_fwd, _raise_if_kernel_timed_out,
+                                          _stream_ptr, round_multiple)
 
 __all__ = ["CompactKeys", "compact_keys", "index_kept_keys", "gather_kept_keys", "scatter_kept_rows",
-           "compact_forward", "compact_backward", "flash_sparse_attn_compact_func"]
+           "compact_forward", "compact_backward", "flash_sparse_attn_compact_func", "kept_keys_to_mask"]
 
 _TILE = 128
 
@@ -182,6 +183,7 @@ def compact_forward(q: torch.Tensor, ck: CompactKeys, softmax_scale: float, is_c
     B, Sq, H, d = q.shape
     dev = q.device
     with torch.cuda.device(dev):
+        _raise_if_kernel_timed_out(lib)
         out = torch.empty_like(q)
         lse = torch.empty((B, H, Sq), dtype=torch.float32, device=dev)
         p = _lib.FwdParams()
@@ -208,6 +210,7 @@ def compact_backward(dout, q, ck: CompactKeys, out, lse, softmax_scale: float, i
     dev = q.device
     dout = dout if dout.stride(-1) == 1 else dout.contiguous()
     with torch.cuda.device(dev):
+        _raise_if_kernel_timed_out(lib)
         dq = torch.empty_like(q)
         dk_c, dv_c = torch.empty_like(k_c), torch.empty_like(v_c)
         dbias_c = torch.empty_like(bias_c) if bias_c is not None else None
@@ -252,36 +255,121 @@ def compact_backward(dout, q, ck: CompactKeys, out, lse, softmax_scale: float, i
     return dq, dk, dv, dbias
 
 
+def kept_keys_to_mask(kept) -> torch.Tensor:
+    """Bool mask (Bm, Hm, 1, Sk) of a `KeptKeys` position list (for calls the gathered route does not serve)."""
+    Bm, Hm, cap = kept.key_pos.shape
+    Sk = kept.seqlen_k
+    mask = torch.zeros((Bm, Hm, 1, Sk + 1), dtype=torch.bool, device=kept.key_pos.device)
+    idx = kept.key_pos.clamp(max=Sk).to(torch.int64).unsqueeze(2)          # unused slots land in the spare column
+    mask.scatter_(-1, idx, torch.ones_like(idx, dtype=torch.bool))
+    return mask[..., :Sk]
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# The gathered route as custom ops (with fake kernels), so that torch.compile traces it like the dense operators.
+# ------------------------------------------------------------------------------------------------------------------
+@torch.library.custom_op("flash_sparse_attn::_index_kept_keys", mutates_args=(), device_types="cuda")
+def _index_kept_keys_op(mask_rows: torch.Tensor, capacity: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """mask_rows bool (Bm, Hm, Sk) -> key_pos (Bm, Hm, Wp) int32, count (Bm, Hm) int32, slot mask (Bm, Hm, 1, Wp)."""
+    m = mask_rows if mask_rows.stride(-1) == 1 else mask_rows.contiguous()
+    return index_kept_keys(m, capacity, check_capacity=False)
+
+
+@torch.library.register_fake("flash_sparse_attn::_index_kept_keys")
+def _index_kept_keys_fake(mask_rows, capacity):
+    Bm, Hm, _ = mask_rows.shape
+    cap = max(_TILE, round_multiple(int(capacity), _TILE))
+    dev = mask_rows.device
+    return (torch.empty((Bm, Hm, cap), dtype=torch.int32, device=dev),
+            torch.empty((Bm, Hm), dtype=torch.int32, device=dev),
+            torch.empty((Bm, Hm, 1, cap), dtype=torch.bool, device=dev))
+
+
+def _bias_c_shape(bias, key_pos, B):
+    Bc, Hc = _bias_layout(bias, key_pos, B)
+    return (Bc, Hc, 1, key_pos.shape[-1])
+
+
+@torch.library.custom_op("flash_sparse_attn::_compact_forward", mutates_args=(), device_types="cuda")
+def _compact_forward_op(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, bias: Optional[torch.Tensor],
+                        key_pos: torch.Tensor, slot_mask: torch.Tensor, softmax_scale: float, is_causal: bool,
+                        ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Gather K, V, bias at key_pos and run the forward over the gathered keys. Returns out, lse and the gathered
+    K, V, bias (an empty tensor without a bias), which the backward reuses."""
+    q = q if q.stride(-1) == 1 else q.contiguous()
+    k_c, v_c, bias_c = gather_kept_keys(k, v, bias, key_pos)
+    ck = CompactKeys(k_c, v_c, slot_mask, bias_c, key_pos, None, k.shape[1])
+    out, lse = compact_forward(q, ck, softmax_scale, is_causal)
+    if bias_c is None:
+        bias_c = torch.empty((0,), dtype=q.dtype, device=q.device)
+    return out, lse, k_c, v_c, bias_c
+
+
+@torch.library.register_fake("flash_sparse_attn::_compact_forward")
+def _compact_forward_fake(q, k, v, bias, key_pos, slot_mask, softmax_scale, is_causal):
+    B, Sq, H, d = q.shape
+    Hk, cap = k.shape[2], key_pos.shape[-1]
+    kc = torch.empty((B, cap, Hk, d), dtype=q.dtype, device=q.device)
+    bias_c = (torch.empty(_bias_c_shape(bias, key_pos, B), dtype=q.dtype, device=q.device) if bias is not None
+              else torch.empty((0,), dtype=q.dtype, device=q.device))
+    return (torch.empty_like(q), torch.empty((B, H, Sq), dtype=torch.float32, device=q.device), kc,
+            torch.empty_like(kc), bias_c)
+
+
+@torch.library.custom_op("flash_sparse_attn::_compact_backward", mutates_args=(), device_types="cuda")
+def _compact_backward_op(dout: torch.Tensor, q: torch.Tensor, k_c: torch.Tensor, v_c: torch.Tensor,
+                         bias_c: Optional[torch.Tensor], key_pos: torch.Tensor, slot_mask: torch.Tensor,
+                         out: torch.Tensor, lse: torch.Tensor, softmax_scale: float, is_causal: bool, seqlen_k: int,
+                         bias_b: int, bias_h: int, bias_keys: int, deterministic: bool,
+                         ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Backward over the gathered keys; dK, dV come back scattered to (B, seqlen_k, Hk, d) and dBias to
+    (bias_b, bias_h, 1, bias_keys) (an empty tensor without a bias)."""
+    B, cap, Hk, d = k_c.shape
+    ck = CompactKeys(k_c, v_c, slot_mask, bias_c, key_pos, None, seqlen_k)
+    dq, dk, dv, dbias = compact_backward(dout, q, ck, out, lse, softmax_scale, is_causal, (B, seqlen_k, Hk, d),
+                                         (bias_b, bias_h, 1, bias_keys) if bias_c is not None else None,
+                                         deterministic=deterministic)
+    if dbias is None:
+        dbias = torch.empty((0,), dtype=q.dtype, device=q.device)
+    return dq, dk, dv, dbias
+
+
+@torch.library.register_fake("flash_sparse_attn::_compact_backward")
+def _compact_backward_fake(dout, q, k_c, v_c, bias_c, key_pos, slot_mask, out, lse, softmax_scale, is_causal, seqlen_k,
+                           bias_b, bias_h, bias_keys, deterministic):
+    B, cap, Hk, d = k_c.shape
+    dk = torch.empty((B, seqlen_k, Hk, d), dtype=q.dtype, device=q.device)
+    dbias = (torch.empty((bias_b, bias_h, 1, bias_keys), dtype=q.dtype, device=q.device) if bias_c is not None
+             else torch.empty((0,), dtype=q.dtype, device=q.device))
+    return torch.empty_like(q), dk, torch.empty_like(dk), dbias
+
+
 class _CompactAttnFunc(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, mask, bias, softmax_scale, is_causal, capacity, trusted, deterministic=False):
-        q = q if q.stride(-1) == 1 else q.contiguous()
-        ck = compact_keys(k, v, mask, bias, capacity, check_capacity=not trusted)
-        out, lse = compact_forward(q, ck, softmax_scale, is_causal)
-        saved = [q, ck.key, ck.value, ck.mask, ck.key_pos, out, lse] + ([ck.bias] if ck.bias is not None else [])
-        ctx.save_for_backward(*saved)
-        ctx.has_bias = ck.bias is not None
+    def forward(ctx, q, k, v, bias, key_pos, slot_mask, softmax_scale, is_causal, deterministic):
+        out, lse, k_c, v_c, bias_c = torch.ops.flash_sparse_attn._compact_forward(
+            q, k, v, bias, key_pos, slot_mask, softmax_scale, is_causal)
+        ctx.save_for_backward(q, k_c, v_c, slot_mask, key_pos, out, lse, bias_c)
+        ctx.has_bias = bias is not None
         ctx.deterministic = bool(deterministic)
-        ctx.meta = (softmax_scale, is_causal, ck.seqlen_k, tuple(k.shape), tuple(bias.shape) if bias is not None else None)
+        ctx.meta = (softmax_scale, is_causal, k.shape[1], tuple(bias.shape) if bias is not None else (0, 0, 0, 0))
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        saved = ctx.saved_tensors
-        q, k_c, v_c, mask_c, key_pos, out, lse = saved[:7]
-        bias_c = saved[7] if ctx.has_bias else None
-        softmax_scale, is_causal, Sk, k_shape, bias_shape = ctx.meta
-        ck = CompactKeys(k_c, v_c, mask_c, bias_c, key_pos, None, Sk)
-        dq, dk, dv, dbias = compact_backward(dout, q, ck, out, lse, softmax_scale, is_causal, k_shape, bias_shape,
-                                             deterministic=ctx.deterministic)
-        return dq, dk, dv, None, dbias, None, None, None, None, None
+        q, k_c, v_c, slot_mask, key_pos, out, lse, bias_c = ctx.saved_tensors
+        softmax_scale, is_causal, Sk, bias_shape = ctx.meta
+        dq, dk, dv, dbias = torch.ops.flash_sparse_attn._compact_backward(
+            dout, q, k_c, v_c, bias_c if ctx.has_bias else None, key_pos, slot_mask, out, lse, softmax_scale,
+            is_causal, Sk, bias_shape[0], bias_shape[1], bias_shape[3], ctx.deterministic)
+        return dq, dk, dv, (dbias if ctx.has_bias else None), None, None, None, None, None
 
 
 def flash_sparse_attn_compact_func(
     query: torch.Tensor,
     key: torch.Tensor,
     value: torch.Tensor,
-    attn_mask: torch.Tensor,
+    attn_mask,
     attn_bias: Optional[torch.Tensor] = None,
     softmax_scale: Optional[float] = None,
     is_causal: Optional[bool] = None,
@@ -291,11 +379,27 @@ def flash_sparse_attn_compact_func(
 ):
     """Same result as `flash_sparse_attn_func(query, key, value, attn_mask, attn_bias, softmax_scale, is_causal)`
     for a row-broadcast mask ({B|1}, {Hk|1}, 1, Sk) and bias ({B|1}, {H|Hk|1}, 1, Sk), computed over the kept keys
-    only. `capacity` bounds the kept keys per mask row (e.g. the keep_window_size the mask was built with); when
-    omitted it is read back from the device. head_dim must be a multiple of 8."""
+    only. attn_mask is a bool tensor or the `KeptKeys` position list of `utils.mask.create_kept_keys` (then no bool
+    mask is read at all). `capacity` bounds the kept keys per row of a bool mask (e.g. the keep_window_size it was
+    built with); when omitted it is read back from the device. head_dim must be a multiple of 8."""
+    from .utils.mask import KeptKeys
+
     softmax_scale = query.shape[-1] ** (-0.5) if softmax_scale is None else softmax_scale
     is_causal = bool(is_causal) if is_causal is not None else False
-    if attn_bias is not None and attn_bias.shape[-1] not in (1, key.shape[1]) and attn_bias.shape[-1] < key.shape[1]:
+    B, Sk, Hk, _ = key.shape
+    if attn_bias is not None and attn_bias.shape[-1] not in (1, Sk) and attn_bias.shape[-1] < Sk:
         raise RuntimeError("attn_bias has fewer keys than key")
-    return _CompactAttnFunc.apply(query, key, value, attn_mask, attn_bias, softmax_scale, is_causal, capacity,
-                                  _trusted_capacity and capacity is not None, bool(deterministic))
+    if isinstance(attn_mask, KeptKeys):
+        if attn_mask.seqlen_k != Sk:
+            raise RuntimeError("the position list was built for a different number of keys")
+        key_pos, slot_mask = attn_mask.key_pos, attn_mask.slot_mask
+    else:
+        m = _row_mask(attn_mask, B, Hk, Sk)
+        trusted = _trusted_capacity and capacity is not None
+        if capacity is None:
+            capacity = int(m.sum(dim=-1, dtype=torch.int32).max().item())
+        key_pos, count, slot_mask = torch.ops.flash_sparse_attn._index_kept_keys(m, int(capacity))
+        if not trusted and int(count.max().item()) > key_pos.shape[-1]:
+            raise RuntimeError(f"a mask row keeps more than capacity={key_pos.shape[-1]} keys")
+    return _CompactAttnFunc.apply(query, key, value, attn_bias, key_pos, slot_mask, softmax_scale, is_causal,
+                                  bool(deterministic))

@@ -40,36 +40,68 @@ def set_compaction(mode: str) -> None:
 
 def _compaction_capacity(query, key, attn_mask, attn_bias, softcap, return_attn_probs) -> Optional[int]:
     """Slots per mask row if this call is to run over gathered keys, else None. Eligible: Sq > 1, head dim a
-    multiple of 8, mask ({B|1}, {Hk|1}, 1, >=Sk), bias absent or row-broadcast, no softcap / returned probabilities.
-    The bound on kept keys comes from the tag `create_mask` leaves on its result; an untagged (or since edited)
-    mask has its counts read back from the device, which synchronises the stream. A mask that keeps more than three
-    quarters of the keys is left to the tile-skipping path."""
+    multiple of 8, mask ({B|1}, {Hk|1}, 1, >=Sk) -- a bool tensor or the `KeptKeys` positions that
+    `utils.mask.create_kept_keys` returns --, bias absent or row-broadcast, no softcap / returned probabilities.
+    The slot count comes from the position list itself when there is one: passed in, or cached on the bool mask by
+    `create_mask` and still valid. Any other bool mask has its counts read back from the device, which
+    synchronises the stream. A mask that keeps more than three quarters of the keys is left to the tile-skipping
+    path."""
+    from .utils.mask import KeptKeys
+
     if _compaction != "auto" or attn_mask is None or softcap or return_attn_probs:
         return None
-    if torch.compiler.is_compiling():  # traced graphs keep to the registered custom ops
-        return None
-    if query.dim() != 4 or key.dim() != 4 or attn_mask.dim() != 4 or attn_mask.dtype != torch.bool:
+    if query.dim() != 4 or key.dim() != 4:
         return None
     B, Sq, H, d = query.shape
     Sk, Hk = key.shape[1], key.shape[2]
     if Sq <= 1 or d % 8 or not query.is_cuda:
-        return None
-    if attn_mask.shape[2] != 1 or attn_mask.shape[1] not in (1, Hk) or attn_mask.shape[0] not in (1, B):
-        return None
-    if attn_mask.shape[3] < Sk:
         return None
     if attn_bias is not None:
         if attn_bias.dim() != 4 or attn_bias.shape[2] != 1 or attn_bias.shape[3] < Sk:
             return None
         if attn_bias.shape[0] not in (1, B) or attn_bias.shape[1] not in (1, Hk, H):
             return None
-    tag = getattr(attn_mask, "_fdma_keep_bound", None)
-    if tag is not None and tag[1] == attn_mask._version:
-        bound = tag[0]
+    if isinstance(attn_mask, KeptKeys):
+        kp = attn_mask.key_pos
+        if attn_mask.seqlen_k != Sk or kp.shape[0] not in (1, B) or kp.shape[1] not in (1, Hk):
+            return None
+        cap = kp.shape[-1]
     else:
-        bound = int(attn_mask[..., :Sk].sum(dim=-1, dtype=torch.int32).max().item())
-    cap = max(_KEY_PAD, round_multiple(bound, _KEY_PAD))
+        if attn_mask.dim() != 4 or attn_mask.dtype != torch.bool:
+            return None
+        if attn_mask.shape[2] != 1 or attn_mask.shape[1] not in (1, Hk) or attn_mask.shape[0] not in (1, B):
+            return None
+        if attn_mask.shape[3] < Sk:
+            return None
+        kept = _cached_kept_keys(attn_mask, Sk)
+        if kept is not None:
+            cap = kept.key_pos.shape[-1]
+        else:
+            bound = int(attn_mask[..., :Sk].sum(dim=-1, dtype=torch.int32).max().item())
+            cap = max(_KEY_PAD, round_multiple(bound, _KEY_PAD))
     return cap if 4 * cap <= 3 * round_multiple(Sk, _KEY_PAD) else None
+
+
+def _cached_kept_keys(attn_mask, seqlen_k):
+    """The position list `create_mask` computed together with this bool mask, if the mask is unchanged since."""
+    if torch.compiler.is_compiling():  # Python attributes of tensors are not part of a traced graph
+        return None
+    tag = getattr(attn_mask, "_fdma_kept", None)
+    if tag is not None and tag[1] == attn_mask._version and tag[0].seqlen_k == seqlen_k:
+        return tag[0]
+    return None
+
+
+def _raise_if_kernel_timed_out(lib) -> None:
+    """A tcgen05 kernel whose bounded wait gave up leaves partly written results behind and a code in page-locked
+    host memory. Checked (one host load, no GPU work) at the entry of every operator call, so that the failure
+    surfaces at the next call at the latest instead of passing as valid data."""
+    if lib.fdma_poll_kernel_status(None) != 0:
+        detail = ctypes.c_int32(0)
+        lib.fdma_last_kernel_status(torch.cuda.current_stream().cuda_stream, ctypes.byref(detail))
+        raise RuntimeError(
+            f"an earlier attention kernel on this device gave up a bounded wait (code {detail.value}): "
+            f"{lib.fdma_strerror(-6).decode()}; results of calls since then are not valid")
 
 
 def _kernel_head_dim(d: int, needs_grad: bool) -> int:
@@ -213,6 +245,7 @@ def _flash_sparse_attn_forward(
     lib = _lib.load()
     B, Sq, H, d = q.shape
     with torch.cuda.device(q.device):
+        _raise_if_kernel_timed_out(lib)
         out = torch.empty_like(q)
         lse = torch.empty((B, H, Sq), dtype=torch.float32, device=q.device)
         p = _lib.FwdParams()
@@ -268,6 +301,7 @@ def _flash_sparse_attn_backward(
     B, Sq, H, d = q.shape
     lse = softmax_lse.contiguous()
     with torch.cuda.device(q.device):
+        _raise_if_kernel_timed_out(lib)
         bp = _lib.BwdParams()
         _fill_fwd(bp.f, q, k, v, mask, bias, out, lse, softmax_scale, is_causal)
         bp.dout = dout.data_ptr()
@@ -285,12 +319,14 @@ def _flash_sparse_attn_backward(
         else:
             bp.dbias = None
         bp.deterministic = 1 if deterministic else 0
+        # D = rowsum(dOut o Out), the `softmax_d` the reference's mha_bwd returns (flash_api.cpp:952, :1049)
+        softmax_d = torch.empty((B, H, round_multiple(Sq, 128)), dtype=torch.float32, device=q.device)
+        bp.softmax_d = softmax_d.data_ptr()
         ws_bytes = lib.fdma_bwd_workspace_bytes(ctypes.byref(bp))
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device) if ws_bytes else None
         if ws is not None:
             bp.f.workspace, bp.f.workspace_bytes = ws.data_ptr(), ws_bytes
         _lib.check(lib.fdma_bwd(ctypes.byref(bp), _stream_ptr(q.device)), "fdma_bwd")
-        softmax_d = torch.empty((B, H, round_multiple(Sq, 128)), dtype=torch.float32, device=q.device)
     return softmax_d
 
 
@@ -384,7 +420,8 @@ def flash_sparse_attn_func(
     (flash_sparse_attn/flash_sparse_attn_interface.py:610-684).
 
     query (B, Sq, H, d); key, value (B, Sk, Hk, d) with H % Hk == 0 (MQA/GQA); fp16 or bf16 on a B200.
-    attn_mask: bool ({B|1}, {H|Hk|1}, {Sq|1}, {Sk|1}), False = masked out; attn_bias: same broadcast rules,
+    attn_mask: bool ({B|1}, {H|Hk|1}, {Sq|1}, {Sk|1}), False = masked out (or the `KeptKeys` position list of
+    `utils.mask.create_kept_keys`, for a row-broadcast selection); attn_bias: same broadcast rules as the mask,
     dtype of query, added to the scaled scores before the softmax. is_causal aligns the causal mask to the
     bottom-right corner (key k visible to query q iff k <= q + Sk - Sq). Rows with no visible key return 0.
     softmax_scale defaults to d ** -0.5. softcap > 0 raises NotImplementedError. return_attn_probs=True returns
@@ -394,6 +431,8 @@ def flash_sparse_attn_func(
     A row-broadcast mask (one keep-set per batch and kv head) is run over its gathered kept keys, which gives the
     same result in far fewer key tiles when the kept keys are scattered; `set_compaction("off")` disables that.
     """
+    from .utils.mask import KeptKeys
+
     d = query.shape[-1]
     needs_grad = torch.is_grad_enabled() and any(t.requires_grad for t in (query, key, value))
     d_run = _kernel_head_dim(d, needs_grad) if query.dim() == 4 and not return_attn_probs else d
@@ -407,8 +446,14 @@ def flash_sparse_attn_func(
     if cap is not None:
         from .compaction import flash_sparse_attn_compact_func
 
-        return flash_sparse_attn_compact_func(query, key, value, attn_mask, attn_bias, softmax_scale, is_causal, cap,
-                                              _trusted_capacity=True, deterministic=bool(deterministic))
+        kept = attn_mask if isinstance(attn_mask, KeptKeys) else _cached_kept_keys(attn_mask, key.shape[1])
+        return flash_sparse_attn_compact_func(query, key, value, kept if kept is not None else attn_mask, attn_bias,
+                                              softmax_scale, is_causal, cap, _trusted_capacity=True,
+                                              deterministic=bool(deterministic))
+    if isinstance(attn_mask, KeptKeys):  # a call the gathered route does not serve: back to a bool mask
+        from .compaction import kept_keys_to_mask
+
+        attn_mask = kept_keys_to_mask(attn_mask)
     return FlashDMAttnFunc.apply(
         query, key, value, attn_mask, attn_bias, softmax_scale, is_causal, softcap, deterministic,
         return_attn_probs, torch.is_grad_enabled(),

@@ -67,30 +67,16 @@ def _default_bwd(dout, q, k, v, mask, bias, out, lse, scale, causal):
     return dq, dk, dv, dbias
 
 
-def _compact_pair_fns(capacity: int):
-    """Per-pair operators that gather the kept keys of the visiting chunk first (flash_sparse_attn/compaction.py):
-    a chunk pair is either fully visible or the causal diagonal of two equally long chunks, so plain causal
-    semantics on the chunk's own key positions apply. `capacity` bounds the kept keys of any chunk."""
-    from . import compaction
-
-    def fwd(q, k, v, mask, bias, scale, causal):
-        ck = compaction.compact_keys(k, v, mask, bias, capacity, check_capacity=False)
-        return compaction.compact_forward(q, ck, scale, causal)
-
-    def bwd(dout, q, k, v, mask, bias, out, lse, scale, causal):
-        ck = compaction.compact_keys(k, v, mask, bias, capacity, check_capacity=False)
-        return compaction.compact_backward(dout, q, ck, out, lse, scale, causal, tuple(k.shape),
-                                           tuple(bias.shape) if bias is not None else None)
-
-    return fwd, bwd
-
-
-def _chunk_capacity(mask: Optional[torch.Tensor], group, chunk: int) -> Optional[int]:
+def _chunk_capacity(mask: Optional[torch.Tensor], group, chunk: int, batch: int, heads_k: int) -> Optional[int]:
     """Largest number of kept keys in any chunk of any rank (one all-reduce and one read-back per call), rounded
-    up to 128 -- or None when gathering would not pay (no mask, CPU tensors, more than 3/4 of a chunk kept)."""
+    up to 128 -- or None when gathering does not apply or would not pay: no mask, CPU tensors, a mask with one row
+    per QUERY head (the gathered K/V are shared by the heads of a kv group, so its rows must be per kv head or
+    shared), more than 3/4 of a chunk kept."""
     from . import flash_sparse_attn_interface as iface
 
     if mask is None or not mask.is_cuda or iface._compaction != "auto":
+        return None
+    if mask.shape[0] not in (1, batch) or mask.shape[1] not in (1, heads_k):
         return None
     counts = mask.reshape(*mask.shape[:2], 2, chunk).sum(dim=-1, dtype=torch.int32).max().reshape(1)
     dist.all_reduce(counts, op=dist.ReduceOp.MAX, group=group)
@@ -111,6 +97,31 @@ def _pad_keys(t: Optional[torch.Tensor], keys: int) -> Optional[torch.Tensor]:
 def _neg_inf_lse(lse: torch.Tensor) -> torch.Tensor:
     """The operator reports rows without a visible key as LSE = +inf; for merging they weigh nothing."""
     return torch.where(torch.isposinf(lse), torch.full_like(lse, float("-inf")), lse)
+
+
+def _merge_on_device(o_acc, lse_acc, o_p, lse_p) -> bool:
+    """Folds the partial into the accumulators IN PLACE with one kernel (fdma_merge_partials). False when the
+    tensors do not fit that kernel (CPU tensors, other dtypes or strides): the caller then uses `_merge`."""
+    if not (o_acc.is_cuda and o_acc.is_contiguous() and lse_acc.is_contiguous() and lse_p.is_contiguous()):
+        return False
+    if o_p.dtype not in (torch.bfloat16, torch.float16) or o_p.stride(-1) != 1 or o_p.shape[-1] % 8 or o_p.shape[-1] > 256:
+        return False
+    if any(st % 8 for st in o_p.stride()[:3]) or o_p.data_ptr() % 16:
+        return False
+    import ctypes
+
+    from . import _lib
+
+    B, Sq, H, d = o_p.shape
+    mp = _lib.MergeParams()
+    mp.acc, mp.lse_acc, mp.part, mp.lse_part = o_acc.data_ptr(), lse_acc.data_ptr(), o_p.data_ptr(), lse_p.data_ptr()
+    mp.part_batch_stride, mp.part_row_stride, mp.part_head_stride = o_p.stride()[:3]
+    mp.b, mp.seqlen_q, mp.h, mp.d = B, Sq, H, d
+    mp.dtype = _lib.FDMA_BF16 if o_p.dtype == torch.bfloat16 else _lib.FDMA_FP16
+    with torch.cuda.device(o_acc.device):
+        _lib.check(_lib.load().fdma_merge_partials(ctypes.byref(mp), torch.cuda.current_stream().cuda_stream),
+                   "fdma_merge_partials")
+    return True
 
 
 def _merge(o_acc, lse_acc, o_p, lse_p):
@@ -180,10 +191,11 @@ class RingAttnFunc(torch.autograd.Function):
                 raise ValueError("ring attention takes query-broadcast mask/bias of local key length: (B|1, h, 1, 2C)")
         scale = d ** -0.5 if softmax_scale is None else softmax_scale
         causal = bool(is_causal)
+        cap = None  # slots per visiting chunk when the pairs run over gathered keys (compaction.py)
         if fwd_fn is _default_fwd and bwd_fn is _default_bwd and d % 8 == 0:
-            cap = _chunk_capacity(mask, group, C)
-            if cap is not None:
-                fwd_fn, bwd_fn = _compact_pair_fns(cap)
+            cap = _chunk_capacity(mask, group, C, B, k.shape[2])
+        if cap is not None:
+            from . import compaction
         payload = [torch.stack([k, v])]
         if bias is not None:
             payload.append(bias)
@@ -201,26 +213,37 @@ class RingAttnFunc(torch.autograd.Function):
             kv = ring.cur[0]
             b_cur = ring.cur[1] if bias is not None else None
             m_cur = ring.cur[-1].to(torch.bool) if mask is not None else None
+            gathered = {}  # kept keys of a visiting chunk: gathered once, used by both local query chunks
             for qs, ks, diag in _visible_pairs(q_chunks, zigzag_chunks(src, world), causal):
                 sl = slice(ks * C, (ks + 1) * C)
-                o_p, lse_p = fwd_fn(
-                    q_loc[qs], kv[0][:, sl], kv[1][:, sl],
-                    _pad_keys(m_cur[..., sl] if m_cur is not None else None, C),
-                    _pad_keys(b_cur[..., sl] if b_cur is not None else None, C), scale, diag)
-                o_acc[qs], lse_acc[qs] = _merge(o_acc[qs], lse_acc[qs], o_p, lse_p)
+                m_p = _pad_keys(m_cur[..., sl] if m_cur is not None else None, C)
+                b_p = _pad_keys(b_cur[..., sl] if b_cur is not None else None, C)
+                if cap is not None:
+                    # a pair is fully visible or the causal diagonal of two equally long chunks, so plain causal
+                    # semantics on the chunk's own key positions apply
+                    if ks not in gathered:
+                        gathered[ks] = compaction.compact_keys(kv[0][:, sl], kv[1][:, sl], m_p, b_p, cap,
+                                                               check_capacity=False)
+                    o_p, lse_p = compaction.compact_forward(q_loc[qs], gathered[ks], scale, diag)
+                else:
+                    o_p, lse_p = fwd_fn(q_loc[qs], kv[0][:, sl], kv[1][:, sl], m_p, b_p, scale, diag)
+                if not _merge_on_device(o_acc[qs], lse_acc[qs], o_p, lse_p):
+                    o_acc[qs], lse_acc[qs] = _merge(o_acc[qs], lse_acc[qs], o_p, lse_p)
             if step + 1 < world:
                 ring.finish()
         out = torch.cat(o_acc, dim=1).to(q.dtype)
         lse = torch.cat(lse_acc, dim=2)
         lse = torch.where(torch.isneginf(lse), torch.full_like(lse, float("inf")), lse)  # operator convention
         ctx.save_for_backward(q, k, v, mask, bias, out, lse)
-        ctx.scale, ctx.causal, ctx.group, ctx.bwd_fn = scale, causal, group, bwd_fn
+        ctx.scale, ctx.causal, ctx.group, ctx.bwd_fn, ctx.cap = scale, causal, group, bwd_fn, cap
         return out
 
     @staticmethod
     def backward(ctx, dout):
         q, k, v, mask, bias, out, lse = ctx.saved_tensors
-        group, scale, causal, bwd_fn = ctx.group, ctx.scale, ctx.causal, ctx.bwd_fn
+        group, scale, causal, bwd_fn, cap = ctx.group, ctx.scale, ctx.causal, ctx.bwd_fn, ctx.cap
+        if cap is not None:
+            from . import compaction
         world = dist.get_world_size(group)
         rank = dist.get_rank(group)
         B, S2, H, d = q.shape
@@ -246,13 +269,23 @@ class RingAttnFunc(torch.autograd.Function):
             m_cur = ring.cur[2 if bias is not None else 1].to(torch.bool) if mask is not None else None
             dkv_acc = ring.cur[-2] if bias is not None else ring.cur[-1]
             db_acc = ring.cur[-1] if bias is not None else None
+            gathered = {}
             for qs, ks, diag in _visible_pairs(q_chunks, zigzag_chunks(src, world), causal):
                 sl = slice(ks * C, (ks + 1) * C)
                 b_p = _pad_keys(b_cur[..., sl] if b_cur is not None else None, C)
-                dq_p, dk_p, dv_p, db_p = bwd_fn(
-                    dout[:, sl_q[qs]], q[:, sl_q[qs]], kv[0][:, sl], kv[1][:, sl],
-                    _pad_keys(m_cur[..., sl] if m_cur is not None else None, C), b_p,
-                    out[:, sl_q[qs]], lse[:, :, sl_q[qs]].contiguous(), scale, diag)
+                m_p = _pad_keys(m_cur[..., sl] if m_cur is not None else None, C)
+                lse_q = lse[:, :, sl_q[qs]].contiguous()
+                if cap is not None:
+                    if ks not in gathered:
+                        gathered[ks] = compaction.compact_keys(kv[0][:, sl], kv[1][:, sl], m_p, b_p, cap,
+                                                               check_capacity=False)
+                    dq_p, dk_p, dv_p, db_p = compaction.compact_backward(
+                        dout[:, sl_q[qs]], q[:, sl_q[qs]], gathered[ks], out[:, sl_q[qs]], lse_q, scale, diag,
+                        tuple(kv[0][:, sl].shape), tuple(b_p.shape) if b_p is not None else None)
+                else:
+                    dq_p, dk_p, dv_p, db_p = bwd_fn(
+                        dout[:, sl_q[qs]], q[:, sl_q[qs]], kv[0][:, sl], kv[1][:, sl], m_p, b_p,
+                        out[:, sl_q[qs]], lse_q, scale, diag)
                 dq_acc[qs] += dq_p.float()
                 dkv_acc[0][:, sl] += dk_p.float()
                 dkv_acc[1][:, sl] += dv_p.float()
@@ -272,7 +305,9 @@ def ring_flash_sparse_attn_func(query, key, value, attn_mask=None, attn_bias=Non
     """Context-parallel dynamic-mask attention over the ranks of `group` (default: the world group).
 
     query, key, value: this rank's zig-zag slice (see zigzag_split), shapes (B, 2C, H, d) / (B, 2C, Hk, d);
-    attn_mask (bool) and attn_bias: query-broadcast, ({B|1}, {H|Hk|1}, 1, 2C), sliced like the keys.
+    attn_mask (bool) and attn_bias: query-broadcast, ({B|1}, {H|Hk|1}, 1, 2C), sliced like the keys. Masks with
+    at most one row per kv head run over each visiting chunk's gathered kept keys; a mask with one row per query
+    head runs over the full chunks.
     Returns this rank's slice of the output; gradients flow to query, key, value and attn_bias.
     C must be a multiple of 128."""
     if not dist.is_initialized():

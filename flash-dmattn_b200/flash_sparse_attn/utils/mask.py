@@ -5,11 +5,24 @@ Differences a caller can observe: equal bias values at the selection threshold a
 order (torch.topk leaves that choice unspecified), and tensors must live on a CUDA device.
 """
 import ctypes
-from typing import Optional
+from typing import NamedTuple, Optional
 
 import torch
 
 from .. import _lib
+
+_TILE = 128
+
+
+class KeptKeys(NamedTuple):
+    """The selection of a row-broadcast dynamic mask as sorted positions instead of a bool tensor: what the
+    reference's `topk_indices` returns (utils/mask.py:20-44), padded to a whole number of 128-key tiles.
+    `flash_sparse_attn_func` accepts it in place of `attn_mask` and then never touches a bool mask."""
+
+    key_pos: torch.Tensor    # int32 (Bm, Hm, Wp): ascending positions of the kept keys, INT32_MAX in unused slots
+    count: torch.Tensor      # int32 (Bm, Hm): kept keys per row
+    slot_mask: torch.Tensor  # bool (Bm, Hm, 1, Wp): slot < count
+    seqlen_k: int            # number of keys the positions index into
 
 
 def _dtype_code(t: torch.Tensor) -> int:
@@ -19,7 +32,8 @@ def _dtype_code(t: torch.Tensor) -> int:
         raise RuntimeError(f"create_mask: unsupported bias dtype {t.dtype}") from None
 
 
-def _launch(attention_bias, attention_mask, window_size, min_dtype, block_size, kind) -> torch.Tensor:
+def _launch(attention_bias, attention_mask, window_size, min_dtype, block_size, kind, positions="none"):
+    """positions: "none" -> bool mask; "also" -> (bool mask, KeptKeys); "only" -> KeptKeys, no bool mask written."""
     bias = attention_bias.detach()
     if not bias.is_cuda:
         raise RuntimeError("create_mask: attention_bias must be a CUDA tensor (this build has no CPU path)")
@@ -46,9 +60,19 @@ def _launch(attention_bias, attention_mask, window_size, min_dtype, block_size, 
             pm = pm.expand(*pm.shape[:-1], keys).contiguous()
     if kind == _lib.MASK_TOPK and window_size > keys:
         raise RuntimeError("selected index k out of range")  # what torch.topk raises in the reference
-    out = torch.empty(out_shape, dtype=torch.bool, device=bias.device)
+    out = torch.empty(out_shape, dtype=torch.bool, device=bias.device) if positions != "only" else None
     p = _lib.MaskParams()
-    p.bias, p.premask, p.out = bias.data_ptr(), (pm.data_ptr() if pm is not None else None), out.data_ptr()
+    p.bias, p.premask = bias.data_ptr(), (pm.data_ptr() if pm is not None else None)
+    p.out = out.data_ptr() if out is not None else None
+    kept = None
+    if positions != "none":
+        cap = max(_TILE, (min(int(window_size), keys) + _TILE - 1) // _TILE * _TILE)
+        lead = tuple(out_shape[:2]) if out_shape[2] == 1 else tuple(out_shape[:3])
+        key_pos = torch.empty(lead + (cap,), dtype=torch.int32, device=bias.device)
+        count = torch.empty(lead, dtype=torch.int32, device=bias.device)
+        slot_mask = torch.empty(tuple(out_shape[:3]) + (cap,), dtype=torch.bool, device=bias.device)
+        p.key_pos, p.count, p.slot_mask, p.capacity = key_pos.data_ptr(), count.data_ptr(), slot_mask.data_ptr(), cap
+        kept = KeptKeys(key_pos, count, slot_mask, keys)
 
     def strides(t):
         return [0 if t.shape[i] == 1 else t.stride(i) for i in range(3)]
@@ -66,7 +90,9 @@ def _launch(attention_bias, attention_mask, window_size, min_dtype, block_size, 
     with torch.cuda.device(bias.device):
         stream = torch.cuda.current_stream(bias.device).cuda_stream
         _lib.check(lib.fdma_create_mask(ctypes.byref(p), stream), "fdma_create_mask")
-    return out
+    if positions == "only":
+        return kept
+    return (out, kept) if positions == "also" else out
 
 
 def topk_mask(attention_bias, attention_mask, window_size, min_dtype, block_size=None, **kwargs):
@@ -74,6 +100,11 @@ def topk_mask(attention_bias, attention_mask, window_size, min_dtype, block_size
     if block_size is not None and block_size <= 0:
         raise ValueError(f"block_size must be a positive integer, got {block_size}.")
     return _launch(attention_bias, attention_mask, window_size, min_dtype, block_size, _lib.MASK_TOPK)
+
+
+def _topk_mask_with_positions(attention_bias, attention_mask, window_size, min_dtype):
+    """Bool mask and, from the same kernel launch, the sorted positions of its kept keys."""
+    return _launch(attention_bias, attention_mask, window_size, min_dtype, None, _lib.MASK_TOPK, positions="also")
 
 
 def relu_mask(attention_bias, attention_mask, min_dtype, block_size=None, **kwargs):
@@ -87,9 +118,30 @@ def topk_indices(attention_bias: torch.Tensor, window_size: int, **kwargs) -> to
     """Sorted indices of the top-`window_size` keys of a (batch, kv_heads, key_len) bias
     (reference: utils/mask.py:20-44), derived from the selection kernel's mask."""
     b3 = attention_bias.detach()
-    mask = _launch(b3.unsqueeze(2), None, window_size, float("-inf"), None, _lib.MASK_TOPK).squeeze(2)
-    idx = torch.nonzero(mask, as_tuple=False)[:, -1]
-    return idx.view(*b3.shape[:-1], window_size)
+    if window_size > b3.shape[-1]:
+        raise RuntimeError("selected index k out of range")
+    kept = _launch(b3.unsqueeze(2), None, window_size, float("-inf"), None, _lib.MASK_TOPK, positions="only")
+    # the selection kernel writes the ascending positions itself; entries equal to -inf are never selected
+    return kept.key_pos[..., :window_size].to(torch.int64)
+
+
+def _reshape_padding_mask(attention_mask, batch_size, query_len, key_len):
+    """2-D (B, Sk) / (B, Sq) padding masks -> (B, 1, 1, Sk), the latter left-padded with True (reference:
+    utils/mask.py:198-218)."""
+    if attention_mask is not None and attention_mask.dim() == 2:
+        if attention_mask.shape[-1] == key_len:
+            attention_mask = attention_mask.view(batch_size, 1, 1, key_len)
+        elif attention_mask.shape[-1] == query_len:
+            pad_len = key_len - query_len
+            attention_mask = attention_mask.view(batch_size, 1, 1, query_len)
+            if pad_len > 0:
+                attention_mask = torch.nn.functional.pad(attention_mask, [pad_len, 0], value=True)
+        else:
+            raise ValueError(
+                f"attention_mask shape {attention_mask.shape} is not compatible with key_len {key_len} "
+                f"or query_len {query_len}."
+            )
+    return attention_mask
 
 
 def create_mask(
@@ -110,27 +162,44 @@ def create_mask(
     window_size largest entries per row (never an entry equal to min_dtype); "relu" keeps bias > 0.
     block_size > 1 then replaces each block of keys by its majority vote.
     """
-    if attention_mask is not None and attention_mask.dim() == 2:
-        if attention_mask.shape[-1] == key_len:
-            attention_mask = attention_mask.view(batch_size, 1, 1, key_len)
-        elif attention_mask.shape[-1] == query_len:
-            pad_len = key_len - query_len
-            attention_mask = attention_mask.view(batch_size, 1, 1, query_len)
-            if pad_len > 0:
-                attention_mask = torch.nn.functional.pad(attention_mask, [pad_len, 0], value=True)
-        else:
-            raise ValueError(
-                f"attention_mask shape {attention_mask.shape} is not compatible with key_len {key_len} "
-                f"or query_len {query_len}."
-            )
+    attention_mask = _reshape_padding_mask(attention_mask, batch_size, query_len, key_len)
     if type == "topk":
-        mask = topk_mask(attention_bias, attention_mask, window_size, min_dtype, block_size)
-        if block_size is None or block_size <= 1:
-            # At most window_size keys are kept per row. The attention entry point uses this bound to size its
-            # compacted key tensors without reading the counts back; the tensor's version counter ties the bound
+        if block_size is not None and block_size <= 0:
+            raise ValueError(f"block_size must be a positive integer, got {block_size}.")
+        rows = attention_bias.shape[2] if attention_bias.dim() == 4 else 0
+        if attention_mask is not None and attention_mask.dim() == 4:
+            rows = max(rows, attention_mask.shape[2])
+        if rows == 1 and (block_size is None or block_size <= 1) and 0 < window_size <= attention_bias.shape[-1]:
+            # Row-broadcast selection: the same launch also writes the sorted positions of the kept keys. They ride
+            # on the returned tensor as a cache that `flash_sparse_attn_func` uses to gather the kept keys without
+            # re-reading the bool mask and without a device read-back; the tensor's version counter ties the cache
             # to the mask's current contents (any in-place edit invalidates it).
-            mask._fdma_keep_bound = (min(int(window_size), int(mask.shape[-1])), mask._version)
-        return mask
+            mask, kept = _topk_mask_with_positions(attention_bias, attention_mask, window_size, min_dtype)
+            mask._fdma_kept = (kept, mask._version)
+            return mask
+        return topk_mask(attention_bias, attention_mask, window_size, min_dtype, block_size)
     if type == "relu":
         return relu_mask(attention_bias, attention_mask, min_dtype, block_size)
     raise ValueError(f"Unsupported mask type: {type}. Supported types are 'topk' and 'relu'.")
+
+
+def create_kept_keys(
+    attention_bias: torch.Tensor,
+    attention_mask: Optional[torch.Tensor],
+    batch_size: int,
+    query_len: int,
+    key_len: int,
+    window_size: int,
+    min_dtype: float,
+) -> KeptKeys:
+    """`create_mask(..., type="topk")` for a row-broadcast bias ({B|1}, {Hk|1}, 1, Sk), returned as the sorted
+    positions of the kept keys (a `KeptKeys`) instead of a bool tensor: no (.., Sk) mask is written or read.
+    Pass the result as `attn_mask` to `flash_sparse_attn_func`. Same selection as `create_mask`: the
+    `window_size` largest entries per row, never an entry equal to `min_dtype`; `attention_mask` pre-masks keys
+    (4-D broadcastable to the bias with one query row, or the 2-D padding forms `create_mask` takes)."""
+    if attention_bias.dim() != 4 or attention_bias.shape[2] != 1:
+        raise RuntimeError("create_kept_keys needs a row-broadcast bias of shape ({B|1}, {Hk|1}, 1, Sk)")
+    attention_mask = _reshape_padding_mask(attention_mask, batch_size, query_len, key_len)
+    if attention_mask is not None and attention_mask.shape[2] != 1:
+        raise RuntimeError("create_kept_keys needs a pre-mask with one query row")
+    return _launch(attention_bias, attention_mask, window_size, min_dtype, None, _lib.MASK_TOPK, positions="only")

@@ -126,6 +126,9 @@ typedef struct fdma_bwd_params {
                                            dBias (except dBias shared across batch / kv heads) have a fixed summation
                                            order in both modes */
   int32_t reserved;
+  float* softmax_d; /* optional out, may be NULL: D = rowsum(dOut o Out) as fp32 (B, H, round_up(Sq,128)) contiguous,
+                       zeros in the padding columns -- the `softmax_d` tensor mha_bwd returns (flash_api.cpp:952,
+                       :1049) */
 } fdma_bwd_params;
 
 size_t fdma_bwd_workspace_bytes(const fdma_bwd_params* p);
@@ -158,6 +161,18 @@ typedef struct fdma_mask_params {
   int32_t kind;       /* fdma_mask_kind */
   int32_t block_size; /* 0 or 1: no smoothing */
   float min_value;    /* the caller's min_dtype (mask.py:171) */
+  /* Optional position output (kind TOPK, no block smoothing): the selection written directly as the sorted index
+   * list that the reference builds with topk + sort in `topk_indices` (mask.py:20-44), without the bool tensor in
+   * between. key_pos (rows, capacity) int32 receives the ascending positions of the selected keys of each row
+   * (rows = out_b*out_h*out_rows, in that order), INT32_MAX in the unused slots; count (rows) their number;
+   * slot_mask (rows, capacity) bool bytes, if given, slot < count. capacity >= min(window, keys). With key_pos
+   * given, `out` may be NULL (no bool mask is written). These are exactly the tensors fdma_compact_index derives
+   * from a bool mask, so fdma_gather_rows / fdma_fwd_params::key_pos take them as they are. */
+  int32_t* key_pos;
+  int32_t* count;
+  void* slot_mask;
+  int32_t capacity;
+  int32_t reserved;
 } fdma_mask_params;
 
 int fdma_create_mask(const fdma_mask_params* p, void* stream);
@@ -177,16 +192,39 @@ int fdma_version(void);
 int fdma_last_kernel_status(void* stream, int32_t* detail);
 
 /*
+ * Non-blocking look at the same condition on the CURRENT device: a kernel whose wait gives up also stores its code
+ * into 4 bytes of page-locked host memory (allocated once per device by the first tcgen05 launch there), which this
+ * call reads without touching the GPU. Returns 0 or FDMA_ERR_TIMEOUT; clears nothing (fdma_last_kernel_status
+ * does). A host layer can call it at the entry of every operator call and learn of a timed-out earlier kernel
+ * whose results must not be trusted. No counterpart in the reference.
+ */
+int fdma_poll_kernel_status(int32_t* detail);
+
+/*
+ * Self-test of the bounded wait (no counterpart in the reference): one small CTA allocates tensor memory and
+ * waits on an mbarrier that nothing arrives on, with a limit of `limit_us` microseconds (1 .. 1 000 000). The wait
+ * gives up, records code 901 in the status word, and the CTA frees its tensor memory and returns; *result_dev
+ * (device int) becomes 1 when every thread saw the wait fail. The next fdma_last_kernel_status call returns
+ * FDMA_ERR_TIMEOUT with detail 901. It cannot hang: the only wait in it is the bounded one.
+ */
+int fdma_selftest_wait_timeout(uint32_t limit_us, int* result_dev, void* stream);
+
+/*
  * Forward pass with library-owned scratch. It has no counterpart in the reference (whose C++ side allocates
  * its own temporaries with torch::empty). Same arguments, results and status codes as fdma_fwd, except that
- * p->workspace / p->workspace_bytes are ignored: the per-tile activity bytes that a per-query mask needs live in
- * a fixed 1 MiB array inside the library (fdma_static_scratch_limit() returns that size). It exists for hosts
+ * p->workspace / p->workspace_bytes are ignored: whatever scratch fdma_fwd_workspace_bytes(p) asks for lives in a
+ * fixed 1 MiB array inside the library (fdma_static_scratch_limit() returns that size). It exists for hosts
  * that cannot supply scratch at call time -- engines that partition device memory once at start-up and give
  * their operators no allocator, or loops where a device allocation is not acceptable. It allocates and frees
- * nothing. A problem needing more than the limit (B * h_mask * ceil(Sq/128) * ceil(Sk/128) bytes) returns
- * FDMA_ERR_TOO_LARGE and launches nothing. The first call on each device resolves the array's address: issue it
- * outside any stream capture. Calls share the array; calls whose GPU work overlaps in time race and must be
- * serialised by the caller.
+ * nothing. Two kinds of call need scratch, and the limit applies to each as fdma_fwd_workspace_bytes reports it
+ * (query it first to know):
+ *   - a per-query mask: one activity byte per 128x128 tile, B * h_mask * ceil(Sq/128) * ceil(Sk/128) bytes;
+ *   - a single-query call (seqlen_q == 1, with or without a mask) on the row-gather decode kernel: per-split
+ *     partials B * H * splits * 8 * (d + 2) * 4 bytes (splits >= 1, chosen from Sk and the SM count), e.g. 1.02 MiB --
+ *     over the limit -- at B * H = 256, d = 128 with one split.
+ * A call needing more than the limit returns FDMA_ERR_TOO_LARGE and launches nothing. The first call on each
+ * device resolves the array's address: issue it outside any stream capture. Calls share the array; calls whose
+ * GPU work overlaps in time race and must be serialised by the caller.
  */
 int fdma_fwd_static_scratch(const fdma_fwd_params* p, void* stream);
 size_t fdma_static_scratch_limit(void);
@@ -233,6 +271,26 @@ typedef struct fdma_rows_params {
 } fdma_rows_params;
 int fdma_gather_rows(const fdma_rows_params* p, void* stream);
 int fdma_scatter_rows(const fdma_rows_params* p, void* stream);
+
+/*
+ * fdma_merge_partials: folds a partial attention result computed over a subset of the keys into a running result,
+ * with the rule of the reference's split-KV combine kernel (src/flash_fwd_kernel.h:1695-1727):
+ *   lse' = log(exp(lse_acc) + exp(lse_part)),  acc' = exp(lse_acc - lse') acc + exp(lse_part - lse') part.
+ * acc (B,Sq,H,d) fp32 contiguous and lse_acc (B,H,Sq) fp32 are updated in place; start them at 0 and -inf.
+ * part is a 16-bit forward output (strides in elements), lse_part its LSE, where +inf (the forward's value for a row
+ * without a visible key) counts as "no contribution". d a multiple of 8, at most 256; 16-byte aligned rows.
+ */
+typedef struct fdma_merge_params {
+  float* acc;
+  float* lse_acc;
+  const void* part;
+  const float* lse_part;
+  int64_t part_batch_stride, part_row_stride, part_head_stride;
+  int32_t b, seqlen_q, h, d;
+  int32_t dtype; /* fdma_dtype of part: BF16 or FP16 */
+  int32_t reserved;
+} fdma_merge_params;
+int fdma_merge_partials(const fdma_merge_params* p, void* stream);
 
 /*
  * Measurement hook (no counterpart in the reference, which is timed from Python with wall clocks,

@@ -63,16 +63,35 @@ def test_null_and_invalid_arguments_are_rejected_without_a_device():
     assert lib.fdma_create_mask(ctypes.byref(m), None) == -1
 
 
-def test_struct_layout_matches_the_header():
-    # sizes measured from the C header with gcc on x86-64 (LP64): a change on either side must show up here
-    assert ctypes.sizeof(_lib.FwdParams) == 296
-    assert ctypes.sizeof(_lib.BwdParams) == 480
-    assert ctypes.sizeof(_lib.CompactParams) == 64
-    assert ctypes.sizeof(_lib.RowsParams) == 120
-    assert _lib.FwdParams.key_pos.offset == 264
-    assert _lib.FwdParams.causal_shift.offset == 292
-    assert ctypes.sizeof(_lib.MaskParams) == 112
-    assert _lib.FwdParams.workspace.offset == 248
-    assert _lib.BwdParams.dout.offset == 296
-    assert _lib.BwdParams.dbias_b.offset == 456
-    assert _lib.MaskParams.min_value.offset == 104
+def test_struct_layout_matches_the_header(tmp_path):
+    """Every ctypes mirror has the size, and every field the offset, that gcc gives the C struct of include/fdma.h
+    (a small C program prints them; a change on either side shows up here)."""
+    import shutil
+    import subprocess
+
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no gcc")
+    pairs = (("fdma_fwd_params", _lib.FwdParams), ("fdma_bwd_params", _lib.BwdParams),
+             ("fdma_mask_params", _lib.MaskParams), ("fdma_compact_params", _lib.CompactParams),
+             ("fdma_rows_params", _lib.RowsParams), ("fdma_merge_params", _lib.MergeParams))
+    lines = ["#include <stdio.h>", "#include <stddef.h>", '#include "fdma.h"', "int main(void) {"]
+    for cname, cls in pairs:
+        lines.append(f'  printf("{cname} %zu\\n", sizeof({cname}));')
+        for fname, _ in cls._fields_:
+            if fname == "f":
+                continue
+            lines.append(f'  printf("{cname}.{fname} %zu\\n", offsetof({cname}, {fname}));')
+    lines += ["  return 0;", "}"]
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run([gcc, "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)], check=True)
+    want = dict(ln.split() for ln in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.splitlines())
+    for cname, cls in pairs:
+        assert ctypes.sizeof(cls) == int(want[cname]), cname
+        for fname, _ in cls._fields_:
+            if fname == "f":
+                continue
+            assert getattr(cls, fname).offset == int(want[f"{cname}.{fname}"]), f"{cname}.{fname}"
+    assert ctypes.sizeof(_lib.FwdParams) == 296  # the forward block is frozen: fdma_bwd_params embeds it first

@@ -154,8 +154,8 @@ def test_compact_matches_tile_path_full_window(dev):
 
 
 def test_default_route_selection(dev):
-    """flash_sparse_attn_func picks the gathered-keys route from the mask's shape: the bound left by create_mask
-    sizes the gather without a read-back, an in-place edit of the mask voids that bound (counts are read back
+    """flash_sparse_attn_func picks the gathered-keys route from the mask's shape: the position list left by
+    create_mask sizes and feeds the gather without a read-back, an in-place edit of the mask voids it (counts are read back
     instead), a mostly-kept mask and a per-query mask stay on the full-range route."""
     from flash_sparse_attn import flash_sparse_attn_func
     from flash_sparse_attn import flash_sparse_attn_interface as iface
@@ -166,7 +166,10 @@ def test_default_route_selection(dev):
     q, k, v, bias, dout = oracle.make_inputs(B, S, S, H, Hk, d, (B, Hk, 1, S), seed=4, dtype=dtype)
     qd, kd, vd, bd = (t.to(dev) for t in (q, k, v, bias))
     mask = create_mask(bd, None, B, S, S, W, torch.finfo(dtype).min)
-    assert mask._fdma_keep_bound == (W, mask._version)
+    kept, version = mask._fdma_kept
+    assert version == mask._version and kept.seqlen_k == S and kept.key_pos.shape == (B, Hk, 256)
+    for h in range(Hk):  # the cached positions are the mask's kept keys
+        assert torch.equal(kept.key_pos[0, h, :W].long(), torch.nonzero(mask[0, h, 0]).flatten())
     assert iface._compaction_capacity(qd, kd, mask, bd, None, None) == 256
     ref = oracle.attention_forward(q, k, v, mask.cpu(), bias, None, True)[0]
     check("out", flash_sparse_attn_func(qd, kd, vd, mask, bd, is_causal=True).cpu(), ref, dtype)

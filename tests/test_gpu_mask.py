@@ -53,7 +53,7 @@ def test_topk_bit_exact_vs_oracle(dev, dtype, shape, window):
 
 
 def test_ties_vs_torch_topk_on_device(dev):
-    # bf16 N(0,1) over 32768 keys: ~30 equal values at the threshold (BASELINE config-3 rows)
+    # bf16 N(0,1) over 32768 keys, top-2048: ~30 equal values at the threshold
     g = torch.Generator().manual_seed(0)
     bias = torch.randn((2, 8, 1, 32768), generator=g).to(torch.bfloat16).to(dev)
     got = _cm(bias, None, 2, 1, 32768, 2048, torch.finfo(torch.bfloat16).min)
@@ -103,7 +103,7 @@ def test_2d_padding_mask_and_block_smooth(dev):
 
 
 def test_full_size_rows_properties(dev):
-    # BASELINE config-2 row geometry (8192 keys, top-1024), many rows: exact count per row and every selected
+    # rows of 8192 keys, top-1024, many rows: exact count per row and every selected
     # value >= every unselected value -- properties that need no CPU-side oracle at this size
     bias = torch.randn((1, 8, 2048, 8192), device=dev, dtype=torch.bfloat16)
     got = _cm(bias, None, 1, 2048, 8192, 1024, torch.finfo(torch.bfloat16).min)
@@ -112,3 +112,55 @@ def test_full_size_rows_properties(dev):
     lo_sel = torch.where(got, bias.float(), torch.full_like(bias, big, dtype=torch.float32)).amin(-1)
     hi_unsel = torch.where(got, torch.full_like(bias, -big, dtype=torch.float32), bias.float()).amax(-1)
     assert (lo_sel >= hi_unsel).all()
+
+
+def test_topk_indices_vs_torch(dev):
+    """`topk_indices` (reference: utils/mask.py:20-44 = torch.topk(...).indices sorted) on tie-free fp32 rows, where
+    the selection is unique: int64, ascending, equal to torch's."""
+    from flash_sparse_attn.utils.mask import topk_indices
+
+    g = torch.Generator().manual_seed(12)
+    for shape, w in (((2, 3, 5000), 257), ((1, 2, 128), 128), ((1, 1, 40000), 1000)):
+        bias = torch.randn(shape, generator=g).to(dev)
+        assert bias.unique().numel() == bias.numel()  # no ties at all
+        got = topk_indices(bias, w)
+        want = torch.topk(bias, w, dim=-1, largest=True, sorted=False).indices.sort(dim=-1).values
+        assert got.dtype == torch.int64 and got.shape == shape[:2] + (w,)
+        assert torch.equal(got, want)
+    with pytest.raises(RuntimeError, match="out of range"):
+        topk_indices(bias, 40001)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("shape,window", [((2, 3, 1, 1000), 100), ((1, 8, 1, 32768), 2048), ((1, 1, 1, 70000), 1024),
+                                          ((2, 2, 1, 4096), 4096), ((1, 2, 1, 8), 3)])
+def test_positions_bit_exact_vs_oracle(dev, dtype, shape, window):
+    """The position output of the selection kernel (fdma_mask_params::key_pos / count / slot_mask) equals
+    torch.nonzero of the oracle's mask, also on the tie-heavy 16-bit rows; the bool mask written by the same launch
+    is unchanged; positions-only mode (no bool mask) gives the same list."""
+    from flash_sparse_attn.utils.mask import create_kept_keys, create_mask
+
+    B, H, _, Sk = shape
+    g = torch.Generator().manual_seed(hash((shape, window)) % 1000 + 1)
+    bias = torch.randn(shape, generator=g).to(dtype)
+    pm = torch.rand((B, 1, 1, Sk), generator=g) < 0.9   # a pre-mask that removes a tenth of the keys
+    mn = torch.finfo(dtype).min
+    for premask in (None, pm):
+        want = oracle.create_mask(bias, premask, B, 1, Sk, window, mn)
+        pmd = premask.to(dev) if premask is not None else None
+        mask = create_mask(bias.to(dev), pmd, B, 1, Sk, window, mn)
+        assert torch.equal(mask.cpu(), want)
+        only = create_kept_keys(bias.to(dev), pmd, B, 1, Sk, window, mn)
+        for kept in (mask._fdma_kept[0], only):
+            cap = kept.key_pos.shape[-1]
+            assert cap % 128 == 0 and cap >= min(window, Sk) and kept.seqlen_k == Sk
+            assert kept.key_pos.shape == (B, H, cap) and kept.count.shape == (B, H)
+            assert kept.slot_mask.shape == (B, H, 1, cap)
+            for b in range(B):
+                for h in range(H):
+                    idx = torch.nonzero(want[b, h, 0]).flatten()
+                    n = idx.numel()
+                    assert int(kept.count[b, h]) == n
+                    assert torch.equal(kept.key_pos[b, h, :n].cpu().long(), idx)
+                    assert bool((kept.key_pos[b, h, n:] == 2**31 - 1).all())
+                    assert bool(kept.slot_mask[b, h, 0, :n].all()) and not bool(kept.slot_mask[b, h, 0, n:].any())

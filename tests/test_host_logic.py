@@ -108,7 +108,7 @@ def test_create_mask_argument_errors():
 
 def test_head_dim_routing_and_compaction_eligibility():
     """Which head dim a call runs at, and which mask shapes take the gathered-keys route (metadata only: the
-    capacity comes from the bound create_mask leaves on its result, never from the device here)."""
+    capacity comes from the position list create_mask leaves on its result, never from the device here)."""
     for d, fwd, bwd in ((32, 64, 128), (64, 64, 128), (72, 128, 128), (128, 128, 128), (136, 256, 256),
                         (256, 256, 256), (320, 320, 320)):
         assert iface._kernel_head_dim(d, False) == fwd and iface._kernel_head_dim(d, True) == bwd
@@ -126,9 +126,16 @@ def test_head_dim_routing_and_compaction_eligibility():
         k = torch.empty(B, Sk, Hk, d, dtype=torch.bfloat16, device="meta")
         bias = torch.empty(B, Hk, 1, Sk, dtype=torch.bfloat16, device="meta")
 
+        from flash_sparse_attn.utils.mask import KeptKeys
+
         def tagged(shape, bound):
+            """A bool mask carrying the position list create_mask computes with it (metadata only here)."""
             m = torch.empty(shape, dtype=torch.bool, device="meta")
-            m._fdma_keep_bound = (bound, m._version)
+            cap = max(128, (bound + 127) // 128 * 128)
+            kept = KeptKeys(torch.empty(shape[:2] + (cap,), dtype=torch.int32, device="meta"),
+                            torch.empty(shape[:2], dtype=torch.int32, device="meta"),
+                            torch.empty(shape[:2] + (1, cap), dtype=torch.bool, device="meta"), shape[-1])
+            m._fdma_kept = (kept, m._version)
             return m
 
         cap = lambda m, b=bias, **kw: iface._compaction_capacity(q, k, m, b, kw.get("softcap"), kw.get("probs"))
@@ -141,6 +148,10 @@ def test_head_dim_routing_and_compaction_eligibility():
         assert cap(tagged((B, Hk, 1, Sk), 300), None) == 384
         assert cap(tagged((B, Hk, 1, Sk), 300), probs=True) is None
         assert cap(None) is None
+        # the position list itself in place of the mask
+        assert cap(tagged((B, Hk, 1, Sk), 300)._fdma_kept[0]) == 384
+        assert cap(tagged((B, Hk, 1, Sk), 3500)._fdma_kept[0]) is None
+        assert cap(tagged((B, Hk, 1, Sk // 2), 300)._fdma_kept[0]) is None   # built for another key count
         q1 = torch.empty(B, 1, H, d, dtype=torch.bfloat16, device="meta")
         assert iface._compaction_capacity(q1, k, tagged((B, Hk, 1, Sk), 300), bias, None, None) is None  # decode
         iface.set_compaction("off")
