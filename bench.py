@@ -2,14 +2,14 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--batch-per-gpu B]
 
-Workload (BASELINE.json configs[2], the shape its metric is quoted on): S = Sq = Sk = 32768, top-2048 mask per
+Workload (the long-context training shape the headline metric is quoted on): S = Sq = Sk = 32768, top-2048 mask per
 (batch, kv head) from a query-broadcast bias (B,Hkv,1,Sk) ~ N(0,1), causal, Hq = 32, Hkv = 8, d = 128, bf16,
 dOut ~ N(0,1), seeded synthetic data. One batch element per GPU (8 independent (batch, kv-head) units); with N GPUs
 the global batch is N, sharded over ranks with no collective in the data path (weak scaling).
 
 A step = one forward + one backward through the C ABI, the same sequence of calls flash_sparse_attn_func makes
-for this mask shape: fdma_compact_index, fdma_gather_rows (K, V, bias), fdma_fwd, fdma_bwd, fdma_scatter_rows
-(dK, dV, dBias). The mask is row-broadcast, so the library gathers the kept keys first and the attention kernels
+for this mask shape: fdma_gather_rows (K, V, bias) at the positions create_mask wrote, fdma_fwd, fdma_bwd,
+fdma_scatter_rows (dK, dV, dBias). The mask is row-broadcast, so the library gathers the kept keys first and the attention kernels
 run over W instead of Sk keys (--compaction off times fdma_fwd + fdma_bwd over the full key range; the default
 run reports that too, as `tile_path`). create_mask is outside the timed region, as in the reference's benchmarks
 (benchmarks/forward_performance.py:185-204). FLOPs are counted only on the tiles the kernels really process, of
@@ -51,6 +51,24 @@ def set_geometry(seq_len: int, window: int, head_dim: int = 128):
 
 FWD_TILE, BWD_TILE = (128, 128), (64, 128)
 NOMINAL_TFLOPS = 2250.0
+
+
+def workload_config(world: int, batch_per_gpu: int, compaction: str) -> dict:
+    """The `config` object of the JSON line; both arms (ours and --impl reference) print exactly this."""
+    compact = compaction == "auto"
+    return {"workload": WORKLOAD, "global_batch": batch_per_gpu * world, "seq_len": S, "window": WINDOW,
+            "parallelism": f"(batch x kv-head) units sharded over {world} GPU(s), no collective",
+            "l2": "inputs larger than L2 (Q alone is 256 MiB per batch element)",
+            "route": ("gathered kept keys (key compaction)" if compact else "full key range with tile skipping (tile-OR)"),
+            "key_compaction": compaction,
+            "flops": ("tiles of the gathered kept keys that the kernels process" if compact
+                      else "tiles of the full key range that hold a kept key"),
+            "tiles": {"fwd": list(FWD_TILE), "bwd": list(BWD_TILE)}}
+
+
+def metric_name(compaction: str) -> str:
+    return ("fwd+bwd TFLOP/s on kept blocks (gathered-keys route)" if compaction == "auto"
+            else "fwd+bwd TFLOP/s on kept blocks (tile-OR route)")
 
 
 # ------------------------------------------------------------------------------------------------------------
@@ -188,21 +206,33 @@ class ClockSampler:
 CPU_ROWS = 1024  # query rows of the bounded CPU sample (the last rows of the sequence: full causal extent)
 
 
-def cpu_sample(steps: int, warmup: int, compact: bool = True) -> dict:
+def cpu_sample(steps: int, warmup: int, compact: bool = True, budget_s: float = 1e9) -> dict:
     """Eager fp32 forward+backward of ONE kv head (its 4 query heads) x the last CPU_ROWS query rows against
-    all 32768 keys, timed on the host cores; FLOPs counted on that slice's kept 128x128 tiles."""
+    all 32768 keys, timed on all host cores; FLOPs counted on that slice's kept 128x128 tiles. Runs `warmup` untimed
+    and `steps` timed passes, stopping early (never before one timed pass) once `budget_s` seconds have gone by."""
     from oracle import oracle
 
+    # torchrun exports OMP_NUM_THREADS=1 to its workers: take every host core regardless
+    torch.set_num_threads(max(1, os.cpu_count() or 1))
     G = HQ // HKV
     q, k, v, bias, dout = oracle.make_inputs(1, CPU_ROWS, S, G, 1, D, (1, 1, 1, S), seed=0, dtype=torch.bfloat16)
     mask = oracle.create_mask(bias, None, 1, CPU_ROWS, S, WINDOW, torch.finfo(torch.bfloat16).min)
     flops = count_flops(mask, 1, CPU_ROWS, S, G, 1, D, True, compact)
-    times = []
+    times, warm_run = [], 0
+    t_begin = time.perf_counter()
     for it in range(warmup + steps):
+        timed = it >= warmup
+        over = time.perf_counter() - t_begin > budget_s
+        if over and times:
+            break
+        if over:
+            timed = True  # the budget ran out during the warm-up: the next pass is the timed one
         t0 = time.perf_counter()
         oracle.attention_forward_backward(q, k, v, mask, bias, dout, None, True)
-        if it >= warmup:
+        if timed:
             times.append(time.perf_counter() - t0)
+        else:
+            warm_run += 1
     sec = sum(times) / len(times)
     flop_ref = flops["canonical_128x128"]
     return {
@@ -210,20 +240,24 @@ def cpu_sample(steps: int, warmup: int, compact: bool = True) -> dict:
         "sample": f"1 kv head x {G} query heads x last {CPU_ROWS} query rows x {S} keys, fp32 eager, "
                   f"{sec * 1e3:.0f} ms per fwd+bwd, FLOPs on 128x128 tiles of "
                   f"{'the gathered kept keys' if compact else 'the full key range'}",
-        "ms_per_step": sec * 1e3,
+        "ms_per_step": sec * 1e3, "steps_run": len(times), "warmup_run": warm_run,
     }
 
 
 def run_reference(args, rank: int, world: int):
+    """The reference's eager algorithm on the host cores (rank 0 only; the other ranks exit without work). Each step is
+    a bounded sample of the workload (see cpu_sample); --steps / --warmup are honoured up to a two-minute budget, and
+    the line reports how many ran."""
     if rank != 0:
         return
-    steps = max(1, min(args.steps, 10))  # ~4 s of host work per step: keeps the arm within a few minutes
-    cb = cpu_sample(steps, min(args.warmup, 1), args.compaction == "auto")
+    cb = cpu_sample(max(1, args.steps), max(0, args.warmup), args.compaction == "auto", budget_s=120.0)
     line = {
-        "impl": "reference", "metric": "fwd+bwd TFLOP/s on kept blocks", "value": cb["value"], "unit": "TFLOP/s",
-        "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": cb["ms_per_step"],
+        "impl": "reference", "metric": metric_name(args.compaction), "value": cb["value"], "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "steps_run": cb["steps_run"],
+        "warmup_run": cb["warmup_run"], "ms_per_step": cb["ms_per_step"],
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "note": "reference eager algorithm (CPU oracle port), bounded sample per step"},
+        "config": workload_config(args.gpus, args.batch_per_gpu, args.compaction),
+        "note": "reference eager algorithm (CPU oracle port) on the host cores, bounded sample per step",
         "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": cb["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -234,19 +268,10 @@ def run_reference(args, rank: int, world: int):
 # ------------------------------------------------------------------------------------------------------------
 # our arm
 # ------------------------------------------------------------------------------------------------------------
-def load_peaks():
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(path):
-        with open(path) as f:
-            pk = json.load(f)
-        return float(pk.get("bf16_tflops_sustained", pk.get("bf16_tflops"))), "measured (cuBLAS bf16, sustained)"
-    return 1400.0, "fallback (sustained)"
-
-
 class AttentionStep:
     """Pre-allocated buffers and pre-filled C-ABI parameter blocks for one forward + backward of the workload, over
-    the full key range (compact=False: fdma_fwd, fdma_bwd) or over the gathered kept keys (compact=True: the nine
-    calls flash_sparse_attn_func makes for a row-broadcast mask)."""
+    the full key range (compact=False: fdma_fwd, fdma_bwd) or over the gathered kept keys (compact=True: the eight
+    calls flash_sparse_attn_func makes for a row-broadcast mask whose position list create_mask has written)."""
 
     def __init__(self, lib, dev, q, k, v, mask, bias, dout, compact: bool):
         from flash_sparse_attn import _lib, compaction
@@ -263,20 +288,15 @@ class AttentionStep:
         self.pre, self.post = [], []  # (function, parameter block) run before the forward / after the backward
         kk, vv, mm, bb, dkk, dvv, dbb = k, v, mask, bias, self.dk, self.dv, self.dbias
         if compact:
-            cap = iface.round_multiple(WINDOW, 128)
-            Bm, Hm = mask.shape[0], mask.shape[1]
-            self.key_pos = torch.empty((Bm, Hm, cap), dtype=torch.int32, device=dev)
-            self.count = torch.empty((Bm, Hm), dtype=torch.int32, device=dev)
-            mm = torch.empty((Bm, Hm, 1, cap), dtype=torch.bool, device=dev)
+            # the position list create_mask wrote with the bool mask (the mask itself is not read again)
+            kept = iface._cached_kept_keys(mask, Sk)
+            assert kept is not None, "create_mask left no position list on the mask"
+            self.key_pos = kept.key_pos
+            cap = self.key_pos.shape[-1]
+            mm = kept.slot_mask
             kk, vv = (torch.empty((B, cap, Hk, d), dtype=q.dtype, device=dev) for _ in range(2))
             bb = torch.empty((bias.shape[0], bias.shape[1], 1, cap), dtype=q.dtype, device=dev)
             dkk, dvv, dbb = torch.empty_like(kk), torch.empty_like(vv), torch.empty_like(bb)
-            m2 = mask[:, :, 0, :Sk]
-            cp = _lib.CompactParams()
-            cp.mask, cp.mask_batch_stride, cp.mask_head_stride = m2.data_ptr(), m2.stride(0), m2.stride(1)
-            cp.b_mask, cp.h_mask, cp.seqlen_k, cp.capacity = Bm, Hm, Sk, cap
-            cp.key_pos, cp.count, cp.mask_out = self.key_pos.data_ptr(), self.count.data_ptr(), mm.data_ptr()
-            self.pre.append((lib.fdma_compact_index, cp))
             bst = lambda t: (t.stride(0), 1, t.stride(1))  # a (B, H, 1, keys) bias as rows of one element
             for src, dst in ((k, kk), (v, vv)):
                 self.pre.append((lib.fdma_gather_rows, compaction._rows_params(
@@ -312,9 +332,9 @@ class AttentionStep:
         self.ws = torch.empty(max(ws_f, ws_b, 1), dtype=torch.uint8, device=dev)
         self.fp.workspace, self.fp.workspace_bytes = self.ws.data_ptr(), ws_f
         bp.f.workspace, bp.f.workspace_bytes = self.ws.data_ptr(), ws_b
-        # launches per step, from the code paths above: index 1 + gathers 3 | fwd_kernel 1 | bwd_prep, bwd_kernel,
+        # launches per step, from the code paths above: gathers 3 | fwd_kernel 1 | bwd_prep, bwd_kernel,
         # convert_dq 3 (+ 3 partial reductions when the backward grid is split) | scatters 3 (their zero fills are memsets)
-        self.launches = (4 + 1 + 6 + 3) if compact else 4
+        self.launches = (3 + 1 + 6 + 3) if compact else 4
 
     def run_pre(self):
         for fn, prm in self.pre:
@@ -333,19 +353,16 @@ class AttentionStep:
             self._lib.check(fn(ctypes.byref(prm), st), "scatter")
 
 
-def time_steps(step, steps: int, stream, barrier, sampler=None):
+def time_steps(step, steps: int, stream, barrier):
     """K steps between two events on the launching stream, barrier + synchronize on both sides; per-step events
-    around the forward and the backward attention kernels. Returns (total ms, mean fwd kernel ms, mean bwd kernel ms,
-    clocks)."""
+    around the forward and the backward attention kernels. Returns (total ms, mean fwd kernel ms, mean bwd kernel
+    ms)."""
     kernel_events = []
     for _ in range(steps):
         evs = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
         for e in evs:
             e.record(stream)  # materialises the underlying cudaEvent_t
         kernel_events.append(evs)
-    barrier()
-    if sampler is not None:
-        sampler.mark()
     t_start, t_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     t_start.record(stream)
@@ -353,10 +370,84 @@ def time_steps(step, steps: int, stream, barrier, sampler=None):
         step(kernel_events[i])
     t_stop.record(stream)
     barrier()
-    clocks = sampler.stop() if sampler is not None else None
     fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in kernel_events)
     bwd_ms = statistics.mean(e[2].elapsed_time(e[3]) for e in kernel_events)
-    return t_start.elapsed_time(t_stop), fwd_ms, bwd_ms, clocks
+    return t_start.elapsed_time(t_stop), fwd_ms, bwd_ms
+
+
+def load_peak_file() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f)
+    return {}
+
+
+def tensor_peaks(sm_mhz) -> dict:
+    """Denominators of the tensor-bound roofline: the measured cuBLAS bf16 burst rate while the SM clock sits at or
+    above 1800 MHz during the run (a kernel timed in short bursts), the sustained rate otherwise; both are reported."""
+    pk = load_peak_file()
+    burst = float(pk.get("bf16_tflops", 1590.0))
+    sustained = float(pk.get("bf16_tflops_sustained", 1400.0))
+    src = "measured" if pk else "fallback"
+    use_burst = sm_mhz is None or sm_mhz >= 1800.0
+    return {"peak": burst if use_burst else sustained, "burst": burst, "sustained": sustained,
+            "source": f"of {src} (cuBLAS bf16, {'burst' if use_burst else 'sustained'})"}
+
+
+def hbm_peak():
+    pk = load_peak_file()
+    return float(pk.get("hbm_gbs", 6650.0)), ("of measured (copy)" if pk else "of fallback (copy)")
+
+
+def chunked_oracle(q, k, v, mask, bias, dout, rows):
+    """fp32 oracle on the device, `rows` query rows at a time (causal: a chunk needs the keys up to its last row).
+    Checker only, outside every timed region."""
+    from oracle import oracle
+
+    B, Sq, H, d = q.shape
+    kf, vf, bf = (t.float().requires_grad_(True) for t in (k, v, bias))
+    o_ref = torch.empty((B, Sq, H, d), dtype=torch.float32, device=q.device)
+    dq_ref = torch.empty_like(o_ref)
+    for r0 in range(0, Sq, rows):
+        qc = q[:, r0:r0 + rows].float().requires_grad_(True)
+        oc, _ = oracle.attention_forward(qc, kf[:, : r0 + rows], vf[:, : r0 + rows], mask[..., : r0 + rows],
+                                         bf[..., : r0 + rows], None, True)
+        (oc * dout[:, r0:r0 + rows].float()).sum().backward()
+        o_ref[:, r0:r0 + rows] = oc.detach()
+        dq_ref[:, r0:r0 + rows] = qc.grad
+    return o_ref, dq_ref, kf.grad, vf.grad, bf.grad
+
+
+def parity_report(q, k, v, mask, bias, dout) -> dict:
+    """One kv-head group of the timed workload (kv head 0 of batch element 0 with its query heads) through the public
+    API, against the fp32 oracle evaluated in chunks of 2048 query rows: per tensor max-abs, mean-abs, the floor that
+    one 16-bit rounding of the exact value costs, and the largest error in ulps."""
+    from flash_sparse_attn import flash_sparse_attn_func
+    from oracle import oracle
+
+    G = HQ // HKV
+    qs, ks, vs = q[:1, :, :G].contiguous(), k[:1, :, :1].contiguous(), v[:1, :, :1].contiguous()
+    bs, ms, ds = bias[:1, :1].contiguous(), mask[:1, :1].contiguous(), dout[:1, :, :G].contiguous()
+    ql, kl, vl, bl = (t.detach().requires_grad_(True) for t in (qs, ks, vs, bs))
+    out = flash_sparse_attn_func(ql, kl, vl, attn_mask=ms, attn_bias=bl, is_causal=True)
+    out.backward(ds)
+    ref = chunked_oracle(qs, ks, vs, ms, bs, ds, 2048)
+    rep = {"against": "fp32 oracle, one kv-head group of the timed workload, chunks of 2048 query rows",
+           "bounds": {"max_abs": oracle.MAX_ABS, "mean_abs": oracle.MEAN_ABS,
+                      "reduced_tensors": f"dk, dv, dbias: + {oracle.FLOOR_FACTOR} x floor_bound (max), "
+                                         f"+ {oracle.FLOOR_FACTOR} x floor_mean (mean)"}}
+    ok_all = True
+    for name, got, want, reduced in zip(("out", "dq", "dk", "dv", "dbias"), (out.detach(), ql.grad, kl.grad, vl.grad, bl.grad),
+                                        ref, (False, False, True, True, True)):
+        r = oracle.error_report(name, got, want)
+        ok, _ = oracle.within_tolerance(r, reduced)
+        ok_all = ok_all and ok
+        rep[name] = {"max_abs": r["max_abs"], "mean_abs": r["mean_abs"], "floor_max": r["floor_max_abs"],
+                     "floor_bound": r["floor_bound"], "floor_mean": r["floor_mean_abs"], "ulp_norm": r["ulp_norm"],
+                     "within_bounds": ok}
+    rep["green"] = ok_all
+    return rep
 
 
 def run_ours(args, rank: int, world: int, local_rank: int):
@@ -389,6 +480,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 
     # ---- device-resident timing ----
     step = AttentionStep(lib, dev, q, k, v, mask, bias, dout, compact)
+    step_launches = step.launches
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler is not None:
         sampler.start()
@@ -400,9 +492,17 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         n_w += 1
         if n_w % 8 == 0:
             torch.cuda.synchronize(dev)
-    ms_total, fwd_ms, bwd_ms, clocks = time_steps(step, args.steps, stream, barrier, sampler)
+    # the timed region of K steps is taken `repeats` times back to back; the line reports the median region
+    barrier()
+    if sampler is not None:
+        sampler.mark()
+    regions = [time_steps(step, args.steps, stream, barrier) for _ in range(max(1, args.repeats))]
+    clocks = sampler.stop() if sampler is not None else None
     _lib.check(lib.fdma_last_kernel_status(stream.cuda_stream, None), "kernel status")
     out, dq, dk, dv, dbias = step.out, step.dq, step.dk, step.dv, step.dbias
+    med = lambda xs: statistics.median(xs)
+    step_ms_all = [r[0] / args.steps for r in regions]
+    ms_per_step_local, fwd_ms, bwd_ms = med(step_ms_all), med([r[1] for r in regions]), med([r[2] for r in regions])
 
     # ---- the same workload over the full key range (tile skipping only), for comparison ----
     tile = None
@@ -411,18 +511,47 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         for _ in range(3):
             tstep()
         t_steps = max(1, min(args.steps, 5))
-        t_ms, t_fwd, t_bwd, _ = time_steps(tstep, t_steps, stream, barrier)
+        t_ms, t_fwd, t_bwd = time_steps(tstep, t_steps, stream, barrier)
         t_fl = count_flops(mask_host, B, S, S, HQ, HKV, D, True, False)
         tile = {"ms_per_step": t_ms / t_steps, "fwd_kernel_ms": t_fwd, "bwd_kernel_ms": t_bwd,
                 "tflops_on_its_kept_tiles": t_fl["total"] / (t_ms / t_steps * 1e-3) / 1e12,
-                "note": "per GPU, rank 0; fdma_fwd + fdma_bwd over all Sk keys, skipping tiles without a kept key"}
+                "bwd_kernel_tflops": t_fl["bwd"] / (t_bwd * 1e-3) / 1e12,
+                "fwd_kernel_tflops": t_fl["fwd"] / (t_fwd * 1e-3) / 1e12,
+                "note": "per GPU, rank 0; fdma_fwd + fdma_bwd over all Sk keys, skipping tiles without a kept key; "
+                        "never mixed into `value`"}
         _lib.check(lib.fdma_last_kernel_status(stream.cuda_stream, None), "kernel status")
         del tstep
 
+    # ---- the public API on device-resident tensors (allocations, workspaces and the Python layer included) ----
+    api_ms = None
+    if not args.no_api:
+        qa, ka, va, ba = (t.detach().requires_grad_(True) for t in (q, k, v, bias))
+
+        def api_step():
+            o = flash_sparse_attn_func(qa, ka, va, attn_mask=mask, attn_bias=ba, is_causal=True)
+            o.backward(dout)
+            qa.grad = ka.grad = va.grad = ba.grad = None
+
+        for _ in range(3):
+            api_step()
+        n_api = max(2, min(args.steps, 10))
+        barrier()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record(stream)
+        for _ in range(n_api):
+            api_step()
+        a1.record(stream)
+        barrier()
+        api_ms = a0.elapsed_time(a1) / n_api
+        del qa, ka, va, ba
+
+    # ---- parity of the timed workload against the oracle (checker, outside every timed region) ----
+    parity = parity_report(q, k, v, mask, bias, dout) if rank == 0 and not args.no_parity else None
+
     # ---- end to end through the public API with pinned host buffers ----
     # The mask is not an input: as in a model, it is made on the device from the uploaded bias (create_mask, inside
-    # the timed region), which also leaves flash_sparse_attn_func the bound it needs to gather keys without a
-    # read-back.
+    # the timed region), which also leaves flash_sparse_attn_func the position list it needs to gather keys without
+    # a read-back.
     host_in = {n: t.detach().cpu().pin_memory() for n, t in (("q", q), ("k", k), ("v", v), ("bias", bias),
                                                               ("dout", dout))}
     host_out = {n: torch.empty(t.shape, dtype=t.dtype).pin_memory()
@@ -467,7 +596,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                 host_out2[sl][n].copy_(t, non_blocking=True)
             ev_out[sl].record(s_out)
 
-    e2e_ms = float("nan")
+    e2e_ms = copy_ms = float("nan")
     if not args.no_e2e:
         e2e_steps = max(2, min(args.steps, 6))
         e2e_step(0)
@@ -485,12 +614,60 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         barrier()
         e2e_ms = e0.elapsed_time(e1) / e2e_steps
         live[0] = live[1] = None
+        # The ceiling the host sets: the same bytes, up and down at once on two streams, with no compute at all
+        # (every rank at the same time, as in the run above).
+        res0 = {"out": out, "dq": dq, "dk": dk, "dv": dv, "dbias": dbias}
+        barrier()
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0.record(stream)
+        s_in.wait_event(c0)
+        s_out.wait_event(c0)
+        for i in range(e2e_steps):
+            with torch.cuda.stream(s_in):
+                for n in in_names:
+                    dev_in[i & 1][n].copy_(host_in[n], non_blocking=True)
+            with torch.cuda.stream(s_out):
+                for n, t in res0.items():
+                    host_out2[i & 1][n].copy_(t, non_blocking=True)
+        fin_in, fin_out = torch.cuda.Event(), torch.cuda.Event()
+        fin_in.record(s_in)
+        fin_out.record(s_out)
+        stream.wait_event(fin_in)
+        stream.wait_event(fin_out)
+        c1.record(stream)
+        barrier()
+        copy_ms = c0.elapsed_time(c1) / e2e_steps
+
+    # ---- secondary workloads (rank 0 of a single-GPU run): short runs of the other benchmark shapes ----
+    secondary = None
+    if world == 1 and not args.no_secondary:
+        del step, host_in, host_out, host_out2, dev_in
+        torch.cuda.empty_cache()
+        sec_args = argparse.Namespace(**vars(args))
+        sec_args.steps, sec_args.warmup = max(3, min(args.steps, 5)), 3
+        secondary = {}
+        for name, fn in (("per_query_S8192", measure_perquery), ("decode_B32_Sk65536", measure_decode),
+                         ("create_mask_65536x8192", measure_mask)):
+            ln = fn(sec_args, 0, 1, local_rank)
+            secondary[name] = {"metric": ln["metric"], "ms_per_step": ln["ms_per_step"], "value": ln["value"],
+                               "unit": ln["unit"], "roofline": ln["roofline"], "workload": ln["config"]["workload"]}
+            for extra in ("fwd_ms", "bwd_ms", "decode_kernel_ms"):
+                if extra in ln:
+                    secondary[name][extra] = ln[extra]
+            torch.cuda.empty_cache()
+
+    # ---- context parallelism over all ranks for one long sequence (multi-GPU runs only) ----
+    cp = None
+    if world > 1 and not args.no_cp:
+        torch.cuda.empty_cache()
+        cp = measure_cp(args, rank, world, local_rank)
 
     # ---- max over ranks ----
-    vals = torch.tensor([ms_total, e2e_ms, fwd_ms, bwd_ms], dtype=torch.float64, device=dev)
+    vals = torch.tensor([ms_per_step_local, e2e_ms, fwd_ms, bwd_ms, copy_ms, min(step_ms_all), max(step_ms_all),
+                         api_ms if api_ms is not None else float("nan")], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(vals, op=dist.ReduceOp.MAX)
-    ms_total, e2e_ms, fwd_ms, bwd_ms = vals.tolist()
+    ms_per_step, e2e_ms, fwd_ms, bwd_ms, copy_ms, ms_min, ms_max, api_ms_max = vals.tolist()
     flop_sum = torch.tensor([float(flops["total"]), float(flops["canonical_128x128"]), float(flops["causal_dense"]),
                              float(flops["bwd"]), float(flops["fwd"]), float(flops["element_level"])],
                             dtype=torch.float64, device=dev)
@@ -499,49 +676,140 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     if rank != 0:
         return
     tot, canon, dense, bwd_fl, fwd_fl, elem_fl = flop_sum.tolist()
-    ms_per_step = ms_total / args.steps
     value = tot / (ms_per_step * 1e-3) / 1e12
-    peak, peak_src = load_peaks()
+    peaks = tensor_peaks(clocks["sm_mhz"] if clocks else None)
     bwd_tflops = (bwd_fl / world) / (bwd_ms * 1e-3) / 1e12  # per launch, per GPU
+    fwd_tflops = (fwd_fl / world) / (fwd_ms * 1e-3) / 1e12
     cpu = cpu_sample(1, 1, compact) if world == 1 and not args.no_cpu else None
     line = {
-        "metric": "fwd+bwd TFLOP/s on kept blocks", "value": value, "unit": "TFLOP/s", "n_gpus": world,
-        "steps": args.steps, "warmup": args.warmup, "warmup_steps_run": n_w, "ms_per_step": ms_per_step,
+        "metric": metric_name(args.compaction), "value": value, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "warmup_steps_run": n_w, "repeats": len(regions),
+        "ms_per_step": ms_per_step, "ms_per_step_min": ms_min, "ms_per_step_max": ms_max,
         "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "global_batch": B * world, "seq_len": S, "window": WINDOW,
-                   "parallelism": f"(batch x kv-head) units sharded over {world} GPU(s), no collective",
-                   "l2": "inputs larger than L2 (Q alone is 256 MiB per batch element)",
-                   "key_compaction": args.compaction,
-                   "flops": ("tiles of the gathered kept keys that the kernels process" if compact
-                             else "tiles of the full key range that hold a kept key"),
-                   "tiles": {"fwd": list(FWD_TILE), "bwd": list(BWD_TILE)}},
+        "config": workload_config(world, B, args.compaction),
         "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
+        "api_ms_per_step": api_ms_max if api_ms is not None else None,
         "tflops_canonical_128x128_tiles": canon / (ms_per_step * 1e-3) / 1e12,
         "tflops_element_level": elem_fl / (ms_per_step * 1e-3) / 1e12,
         "tflops_causal_dense_equivalent": dense / (ms_per_step * 1e-3) / 1e12,
         "utilisation_of_nominal_2250": value / world / NOMINAL_TFLOPS,
-        "roofline": {"bound": "tensor", "kernel": "bwd_kernel", "achieved": bwd_tflops, "peak": peak,
-                     "unit": "TFLOP/s", "frac": bwd_tflops / peak, "peak_source": "of " + peak_src,
-                     "traffic": None, "fwd_kernel_achieved": (fwd_fl / world) / (fwd_ms * 1e-3) / 1e12},
+        "roofline": {"bound": "tensor", "kernel": "bwd_kernel", "achieved": bwd_tflops, "peak": peaks["peak"],
+                     "unit": "TFLOP/s", "frac": bwd_tflops / peaks["peak"], "peak_source": peaks["source"],
+                     "frac_sustained": bwd_tflops / peaks["sustained"], "peak_sustained": peaks["sustained"],
+                     "frac_of_nominal_2250": bwd_tflops / NOMINAL_TFLOPS,
+                     "traffic": None, "fwd_kernel_achieved": fwd_tflops, "fwd_kernel_frac": fwd_tflops / peaks["peak"]},
         "e2e": {"value": tot / (e2e_ms * 1e-3) / 1e12 if e2e_ms == e2e_ms else None, "unit": "TFLOP/s",
                 "ms_per_step": e2e_ms if e2e_ms == e2e_ms else None,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "copy_only_ms_per_step": copy_ms if copy_ms == copy_ms else None,
+                "frac_of_copy_ceiling": (copy_ms / e2e_ms) if e2e_ms == e2e_ms and copy_ms == copy_ms else None,
                 "note": "create_mask + flash_sparse_attn_func + backward on pinned host buffers; uploads, compute and "
-                        "downloads of consecutive steps overlap on three streams"},
-        "gpu_launches": args.steps * step.launches,
+                        "downloads of consecutive steps overlap on three streams. copy_only = the same bytes up and "
+                        "down with no compute, all ranks at once: the host's ceiling for this figure"},
+        "gpu_launches": args.steps * len(regions) * step_launches,
         "clocks": clocks,
     }
     if tile is not None:
-        line["tile_path"] = tile
+        line["tile_or"] = {"ms_per_step": tile["ms_per_step"], "tflops_on_its_kept_tiles": tile["tflops_on_its_kept_tiles"],
+                           "bwd_kernel_ms": tile["bwd_kernel_ms"], "fwd_kernel_ms": tile["fwd_kernel_ms"],
+                           "bwd_kernel_tflops": tile["bwd_kernel_tflops"],
+                           "bwd_kernel_frac": tile["bwd_kernel_tflops"] / peaks["peak"],
+                           "fwd_kernel_tflops": tile["fwd_kernel_tflops"],
+                           "fwd_kernel_frac": tile["fwd_kernel_tflops"] / peaks["peak"],
+                           "frac_of_nominal_2250": tile["tflops_on_its_kept_tiles"] / NOMINAL_TFLOPS,
+                           "note": tile["note"]}
+    if parity is not None:
+        line["parity"] = parity
+    if secondary is not None:
+        line["secondary"] = secondary
+    if cp is not None:
+        line["cp"] = cp
     if cpu is not None:
         line["cpu_baseline"] = {k_: cpu[k_] for k_ in ("value", "unit", "cores", "kind", "sample")}
     print(json.dumps(line), flush=True)
 
 
+def measure_cp(args, rank: int, world: int, local_rank: int) -> dict:
+    """Gathered-keys context parallelism over all ranks on the wide-head long-sequence shape (B=1, S=131072, Hq=16,
+    Hkv=1, d=256, W=1024, causal, fwd+bwd with dBias), next to the time ONE GPU needs for the same sequence (rank 0
+    runs it alone while the others wait). Returned on every rank; only rank 0's copy is printed."""
+    import torch.distributed as dist
+
+    from flash_sparse_attn import flash_sparse_attn_func, gathered_cp, ring
+    from flash_sparse_attn.utils.mask import create_mask
+
+    dev = torch.device(f"cuda:{local_rank}")
+    B, Sr, H, Hk, d, w = 1, 131072, 16, 1, 256, 1024
+    g = torch.Generator(device="cpu").manual_seed(7)
+    bias_full = torch.randn((B, Hk, 1, Sr), generator=g).to(torch.bfloat16)
+    mask_full = create_mask(bias_full.to(dev), None, B, Sr, Sr, w, torch.finfo(torch.bfloat16).min)
+    rnd = lambda gen, *shape: torch.randn(shape, generator=gen, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    steps, warm = max(2, min(args.steps, 5)), 2
+
+    def timed(fn):
+        for _ in range(warm):
+            fn()
+        dist.barrier(); torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        dist.barrier(); torch.cuda.synchronize(dev)
+        t = torch.tensor([e0.elapsed_time(e1) / steps], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    # one GPU alone (rank 0), full sequence
+    one_ms = torch.zeros(1, dtype=torch.float64, device=dev)
+    if rank == 0:
+        g1 = torch.Generator(device=dev).manual_seed(99)
+        qf, kf, vf, df = rnd(g1, B, Sr, H, d), rnd(g1, B, Sr, Hk, d), rnd(g1, B, Sr, Hk, d), rnd(g1, B, Sr, H, d)
+        qf.requires_grad_(True); kf.requires_grad_(True); vf.requires_grad_(True)
+        bf = bias_full.to(dev).requires_grad_(True)
+
+        def one():
+            o = flash_sparse_attn_func(qf, kf, vf, attn_mask=mask_full, attn_bias=bf, is_causal=True)
+            o.backward(df)
+            qf.grad = kf.grad = vf.grad = bf.grad = None
+
+        for _ in range(warm):
+            one()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            one()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        one_ms[0] = e0.elapsed_time(e1) / steps
+        del qf, kf, vf, df, bf
+        torch.cuda.empty_cache()
+    dist.broadcast(one_ms, 0)
+
+    gl = torch.Generator(device=dev).manual_seed(100 + rank)
+    S2 = Sr // world
+    q, k, v, dout = rnd(gl, B, S2, H, d), rnd(gl, B, S2, Hk, d), rnd(gl, B, S2, Hk, d), rnd(gl, B, S2, H, d)
+    q.requires_grad_(True); k.requires_grad_(True); v.requires_grad_(True)
+    bias = ring.zigzag_split(bias_full, 3, rank, world).contiguous().to(dev).requires_grad_(True)
+    mask = ring.zigzag_split(mask_full.cpu(), 3, rank, world).contiguous().to(dev)
+
+    def cp_step():
+        out = gathered_cp.gathered_cp_flash_sparse_attn_func(q, k, v, mask, bias, None, True)
+        out.backward(dout)
+        q.grad = k.grad = v.grad = bias.grad = None
+
+    cp_ms = timed(cp_step)
+    return {"scheme": "gathered-keys context parallel (kept K/V rows all-reduced, zig-zag query chunks)",
+            "workload": f"B=1 S={Sr} Hq={H} Hkv={Hk} d={d} W={w} causal, fwd+bwd with dBias", "n_gpus": world,
+            "ms_per_step": cp_ms, "one_gpu_ms_per_step": one_ms.item(), "speedup_vs_one_gpu": one_ms.item() / cp_ms,
+            "scaling": "strong", "steps": steps}
+
+
 def run_ring(args, rank: int, world: int, local_rank: int):
     """Secondary workload (not the headline line): one long sequence, KV-ring context parallel over all ranks.
-    BASELINE config 5: B=1, S=131072, Hq=16, Hkv=1, d=256, top-1024 query-broadcast mask, causal, fwd+bwd with
+    The wide-head MQA long-sequence shape: B=1, S=131072, Hq=16, Hkv=1, d=256, top-1024 query-broadcast mask, causal, fwd+bwd with
     dBias."""
     import torch.distributed as dist
 
@@ -627,8 +895,8 @@ def run_ring(args, rank: int, world: int, local_rank: int):
     print(json.dumps(line), flush=True)
 
 
-def run_decode(args, rank: int, world: int, local_rank: int):
-    """Secondary workload (not the headline line): BASELINE config 4, single-query forward over a KV cache,
+def measure_decode(args, rank: int, world: int, local_rank: int):
+    """Secondary workload (not the headline line): the decode shape, single-query forward over a KV cache,
     B = 32 per GPU (--decode-batch), Sk = 65536, Hq = 32, Hkv = 8, d = 128, top-4096 mask, non-causal. HBM-bound:
     reported as GB/s of the bytes the kernel's skip granule (one key row) makes it read."""
     import torch.distributed as dist
@@ -681,12 +949,7 @@ def run_decode(args, rank: int, world: int, local_rank: int):
         return
     ms, total_bytes, kernel_ms = vals.tolist()
     kernel_ms /= world
-    peak = 6538.9
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    src = "fallback"
-    if os.path.exists(path):
-        with open(path) as f:
-            peak, src = float(json.load(f).get("hbm_gbs", peak)), "measured (copy)"
+    peak, src = hbm_peak()
     gbs = total_bytes / (ms * 1e-3) / 1e9
     line = {
         "metric": "decode forward GB/s of bytes read at key-row granularity", "value": gbs, "unit": "GB/s",
@@ -697,15 +960,19 @@ def run_decode(args, rank: int, world: int, local_rank: int):
         "decode_kernel_ms": kernel_ms,
         "roofline": {"bound": "hbm", "kernel": "decode_mma_kernel",
                      "achieved": total_bytes / world / (kernel_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
-                     "frac": total_bytes / world / (kernel_ms * 1e-3) / 1e9 / peak, "peak_source": "of " + src,
-                     "traffic": None},
+                     "frac": total_bytes / world / (kernel_ms * 1e-3) / 1e9 / peak, "peak_source": src,
+                     # one ncu capture of this kernel at B = 8 (profiles/decode_mma_kernel_B8_Sk65536_ncu_full.md):
+                     # 146.9 MB of DRAM traffic for 139 MB of algorithmic bytes; traffic grows with the kept rows,
+                     # so the ratio is applied to this launch's bytes
+                     "traffic": total_bytes / world * (146.9 / 139.0),
+                     "traffic_source": "ncu capture at B=8 scaled by algorithmic bytes (x1.057)"},
         "gpu_launches": args.steps * 2,  # decode_kernel + decode_merge_kernel
     }
-    print(json.dumps(line), flush=True)
+    return line
 
 
-def run_perquery(args, rank: int, world: int, local_rank: int):
-    """Secondary workload (not the headline line): BASELINE config 2, per-query bias and mask. B=1, S=8192, Hq=32,
+def measure_perquery(args, rank: int, world: int, local_rank: int):
+    """Secondary workload (not the headline line): the per-query training shape, per-query bias and mask. B=1, S=8192, Hq=32,
     Hkv=8, d=128, bias (B,Hkv,Sq,Sk) ~ N(0,1), mask = top-1024 per query row AND causal, fwd+bwd with a per-query
     dBias, through the C ABI on device-resident tensors. FLOPs on 128x128 (forward) / 64x128 (backward) tiles that
     hold a kept, causally visible element."""
@@ -733,10 +1000,11 @@ def run_perquery(args, rank: int, world: int, local_rank: int):
     step = AttentionStep(lib, dev, q, k, v, mask, bias, dout, False)
     for _ in range(max(args.warmup, 3)):
         step()
-    ms_total, fwd_ms, bwd_ms, _ = time_steps(step, args.steps, stream, lambda: torch.cuda.synchronize(dev))
+    ms_total, fwd_ms, bwd_ms = time_steps(step, args.steps, stream, lambda: torch.cuda.synchronize(dev))
     _lib.check(lib.fdma_last_kernel_status(stream.cuda_stream, None), "kernel status")
     ms = ms_total / args.steps
-    peak, peak_src = load_peaks()
+    pk = tensor_peaks(None)
+    peak, peak_src = pk["peak"], pk["source"]
     bwd_tf = 10 * D * 64 * 128 * tiles_b / (bwd_ms * 1e-3) / 1e12
     line = {
         "metric": "fwd+bwd TFLOP/s on kept blocks (per-query bias and mask)", "value": flops / (ms * 1e-3) / 1e12,
@@ -747,14 +1015,15 @@ def run_perquery(args, rank: int, world: int, local_rank: int):
                    "tiles": {"fwd": list(FWD_TILE), "bwd": list(BWD_TILE)}},
         "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
         "roofline": {"bound": "tensor", "kernel": "bwd_kernel", "achieved": bwd_tf, "peak": peak, "unit": "TFLOP/s",
-                     "frac": bwd_tf / peak, "peak_source": "of " + peak_src, "traffic": None},
+                     "frac": bwd_tf / peak, "peak_source": peak_src, "frac_sustained": bwd_tf / pk["sustained"],
+                     "traffic": None},
         "gpu_launches": args.steps * 5,  # tile_activity x2, fwd_kernel, bwd_prep, bwd_kernel (+ convert_dq)
     }
-    print(json.dumps(line), flush=True)
+    return line
 
 
-def run_mask(args, rank: int, world: int, local_rank: int):
-    """Secondary workload (not the headline line): create_mask alone at BASELINE config 2's size, 65536 rows (B=1,
+def measure_mask(args, rank: int, world: int, local_rank: int):
+    """Secondary workload (not the headline line): create_mask alone at the per-query training shape's size, 65536 rows (B=1,
     Hkv=8, Sq=8192) x 8192 keys of bf16 bias, top-1024 per row. HBM-bound: GB/s of bias bytes read + mask bytes
     written. --mask-rows shrinks it for profiler captures."""
     from flash_sparse_attn import _lib
@@ -781,11 +1050,7 @@ def run_mask(args, rank: int, world: int, local_rank: int):
     ms = e0.elapsed_time(e1) / args.steps
     assert int(mask[0, 0, 0].sum()) == w
     nbytes = bias.numel() * 2 + mask.numel()
-    peak, src = 6538.9, "fallback"
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(path):
-        with open(path) as f:
-            peak, src = float(json.load(f).get("hbm_gbs", peak)), "measured (copy)"
+    peak, src = hbm_peak()
     gbs = nbytes / (ms * 1e-3) / 1e9
     line = {
         "metric": "create_mask GB/s (bias read + mask written)", "value": gbs, "unit": "GB/s", "n_gpus": 1,
@@ -794,10 +1059,27 @@ def run_mask(args, rank: int, world: int, local_rank: int):
         "config": {"workload": f"create_mask: {rows} rows x {keys} keys bf16, top-{w} per row", "bytes_per_step": nbytes,
                    "l2": "bias larger than L2"},
         "roofline": {"bound": "hbm", "kernel": "topk16_reg_kernel", "achieved": gbs, "peak": peak, "unit": "GB/s",
-                     "frac": gbs / peak, "peak_source": "of " + src, "traffic": None},
+                     "frac": gbs / peak, "peak_source": src, "traffic": None},
         "gpu_launches": args.steps,
     }
-    print(json.dumps(line), flush=True)
+    return line
+
+
+def _print_if_line(line):
+    if line is not None:
+        print(json.dumps(line), flush=True)
+
+
+def run_decode(args, rank, world, local_rank):
+    _print_if_line(measure_decode(args, rank, world, local_rank))
+
+
+def run_perquery(args, rank, world, local_rank):
+    _print_if_line(measure_perquery(args, rank, world, local_rank))
+
+
+def run_mask(args, rank, world, local_rank):
+    _print_if_line(measure_mask(args, rank, world, local_rank))
 
 
 def main():
@@ -818,17 +1100,27 @@ def main():
     ap.add_argument("--decode-batch", type=int, default=32)
     ap.add_argument("--mask-rows", type=int, default=65536)
     ap.add_argument("--ring-seq-len", type=int, default=131072)
-    ap.add_argument("--ring-head-dim", type=int, default=256, help="256 = BASELINE config 5; 128 for comparison")
+    ap.add_argument("--ring-head-dim", type=int, default=256, help="256 = the wide-head long-sequence shape; 128 for comparison")
     ap.add_argument("--cp-scheme", default="ring", choices=["ring", "gathered"],
                     help="--workload ring: rotate K/V chunks (ring) or all-reduce the kept K/V rows (gathered)")
     ap.add_argument("--compaction", default="auto", choices=["auto", "off"],
                     help="auto = the library's default route for this mask (kept keys gathered first); off = full key range")
     ap.add_argument("--no-tile-path", action="store_true", help="skip the full-key-range comparison leg")
+    ap.add_argument("--repeats", type=int, default=5, help="how many times the timed region of K steps is taken "
+                                                           "(the line reports the median region, with min and max)")
+    ap.add_argument("--no-api", action="store_true", help="skip the public-API leg on device-resident tensors")
+    ap.add_argument("--no-parity", action="store_true", help="skip the oracle comparison of the timed workload")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the short runs of the other benchmark shapes")
+    ap.add_argument("--no-cp", action="store_true", help="multi-GPU runs: skip the context-parallel long-sequence leg")
+    ap.add_argument("--lean", action="store_true", help="profiling runs: only the device-resident timed region")
     ap.add_argument("--min-warmup-seconds", type=float, default=0.5,
                     help="warm-up runs at least this long (0 for profiler captures, where launch counts must be fixed)")
     args = ap.parse_args()
     if args.impl == "ours":
         args.warmup = max(args.warmup, 3)
+    if args.lean:
+        args.no_cpu = args.no_e2e = args.no_tile_path = args.no_api = args.no_parity = args.no_secondary = True
+        args.no_cp, args.repeats = True, 1
     if args.seq_len != S or args.window != WINDOW or args.head_dim != D:
         set_geometry(args.seq_len, args.window, args.head_dim)
     rank = int(os.environ.get("RANK", "0"))

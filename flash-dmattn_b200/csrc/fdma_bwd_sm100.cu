@@ -40,6 +40,7 @@ constexpr float kLog2e = 1.4426950408889634f;
 
 enum DbiasMode { kDbNone = 0, kDbColsum = 1, kDbDirect = 2, kDbAtomic = 3 };
 
+
 enum WaitCode {
   kWaitKv = 201, kWaitQdoEmpty = 202, kWaitQdoFull = 203, kWaitSFull = 204, kWaitDpFull = 205, kWaitPds = 206,
   kWaitDqFull = 207, kWaitDqEmpty = 208, kWaitDpFree = 209, kWaitFinal = 210
@@ -1127,13 +1128,14 @@ int launch(const fdma_bwd_params& bp, const BwdPlan& pl, cudaStream_t stream) {
 
   auto kern = bp.deterministic ? (pl.bcast ? bwd_kernel<kBf16, true, true> : bwd_kernel<kBf16, false, true>)
                                : (pl.bcast ? bwd_kernel<kBf16, true, false> : bwd_kernel<kBf16, false, false>);
-  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemB::kAlloc);
+  const int smem_bytes = SmemB::kAlloc;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   if (e != cudaSuccess) return static_cast<int>(e);
   dim3 grid(((p.seqlen_k + kBN - 1) / kBN) * pl.nsplit, p.h_k, p.b);
   cudaEvent_t ev0, ev1;
   take_timing_events(&ev0, &ev1);
   if (ev0) cudaEventRecord(ev0, stream);
-  kern<<<grid, kThreads, SmemB::kAlloc, stream>>>(kp);
+  kern<<<grid, kThreads, smem_bytes, stream>>>(kp);
   if (ev1) cudaEventRecord(ev1, stream);
   e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);

@@ -142,8 +142,8 @@ def test_one_kv_head_group_against_chunked_oracle_at_32k(dev):
 def test_per_query_bias_and_mask_group_against_oracle_at_8192(dev, compaction_mode):
     """One kv head with its four query heads at S = 8192, W = 1024, d = 128, per-query bias and mask (B, Hkv, Sq, Sk)
     and a per-query dBias: O, dQ, dK, dV and dBias against the un-chunked fp32 oracle (its 4 x 8192 x 8192 scores
-    fit). Per-query dBias is one 16-bit rounding of dS summed over the four heads, not a sum over queries, so it is
-    held to the plain bounds."""
+    fit). Per-query dBias is dS summed over the four heads of the group and reaches magnitudes (12 here) whose 16-bit
+    rounding alone exceeds 2e-2, so it takes the bounds of the reduced gradients."""
     if compaction_mode == "auto":
         pytest.skip("a per-query mask always runs over the full key range: one run is enough")
     B, S, H, Hk, d, W = 1, 8192, 4, 1, 128, 1024
@@ -151,10 +151,7 @@ def test_per_query_bias_and_mask_group_against_oracle_at_8192(dev, compaction_mo
     got = _run(q, k, v, mask, bias, dout)
     ref = oracle.attention_forward_backward(q, k, v, mask, bias, dout, None, True)
     ref = (ref[0], ref[2], ref[3], ref[4], ref[5])
-    for name, g, r, reduced in zip(("out", "dq", "dk", "dv", "dbias"), got, ref, (False, False, True, True, False)):
-        assert torch.isfinite(g.float()).all(), name
-        ok, msg = oracle.within_tolerance(oracle.error_report(name, g, r), reduced)
-        assert ok, msg
+    _compare(got, ref)
 
 
 def test_decode_at_full_size_against_oracle(dev, compaction_mode):

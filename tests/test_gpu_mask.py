@@ -121,8 +121,9 @@ def test_topk_indices_vs_torch(dev):
 
     g = torch.Generator().manual_seed(12)
     for shape, w in (((2, 3, 5000), 257), ((1, 2, 128), 128), ((1, 1, 40000), 1000)):
-        bias = torch.randn(shape, generator=g).to(dev)
-        assert bias.unique().numel() == bias.numel()  # no ties at all
+        n = shape[0] * shape[1] * shape[2]
+        bias = ((torch.randperm(n, generator=g).float() - n / 2) * 1e-3).view(shape).to(dev)  # all values distinct
+        assert bias.unique().numel() == bias.numel()
         got = topk_indices(bias, w)
         want = torch.topk(bias, w, dim=-1, largest=True, sorted=False).indices.sort(dim=-1).values
         assert got.dtype == torch.int64 and got.shape == shape[:2] + (w,)

@@ -49,14 +49,15 @@ def _worker(rank, world, port, causal, route, d, scheme="ring"):
         for name, got, ref, dim in (("out", out, want[0], 1), ("dq", ql.grad, want[2], 1), ("dk", kl.grad, want[3], 1),
                                     ("dv", vl.grad, want[4], 1), ("dbias", bl.grad, want[5], 3)):
             r = oracle.error_report(name, gather(got, dim), ref)
-            assert r["max_abs"] <= 2e-2 + 3 * r["floor_max_abs"] and r["mean_abs"] <= 2e-3 + 2 * r["floor_mean_abs"], r
+            ok, msg = oracle.within_tolerance(r, name in ("dk", "dv", "dbias"))
+            assert ok, msg
     finally:
         dist.destroy_process_group()
 
 
 @pytest.mark.parametrize("causal,route,d", [
     (True, "off", 128), (False, "off", 128), (True, "auto", 128), (False, "auto", 128),
-    (True, "auto", 256),   # BASELINE config 5's head dim: tcgen05 forward and two-pass backward under the ring
+    (True, "auto", 256),   # head dim 256: tcgen05 forward and two-pass backward under the ring
 ], ids=["causal-tiles", "full-tiles", "causal-compaction", "full-compaction", "causal-compaction-d256"])
 def test_ring_two_gpus(causal, route, d):
     if torch.cuda.device_count() < 2:
