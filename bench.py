@@ -419,6 +419,20 @@ def chunked_oracle(q, k, v, mask, bias, dout, rows):
     return o_ref, dq_ref, kf.grad, vf.grad, bf.grad
 
 
+def reference_cuda_kernels() -> dict:
+    """The reference's mma.sync kernels, recompiled unchanged for sm_100 (baseline/build_ref_cuda.py), timed on one
+    batch element of this workload through the reference's own flash_sparse_attn_func, in a child process that sees
+    only baseline/_ref (baseline/time_ref_cuda.py). Context for `value` and `tile_or`; not the reference arm."""
+    script = os.path.join(ROOT, "baseline", "time_ref_cuda.py")
+    try:
+        res = subprocess.run([sys.executable, script, "--seq-len", str(S), "--window", str(WINDOW), "--steps", "3"],
+                             capture_output=True, text=True, timeout=300)
+        lines = [ln for ln in res.stdout.splitlines() if ln.startswith("{")]
+        return json.loads(lines[-1]) if lines else {"unavailable": (res.stderr or "no output")[-300:]}
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": repr(e)[:300]}
+
+
 def parity_report(q, k, v, mask, bias, dout) -> dict:
     """One kv-head group of the timed workload (kv head 0 of batch element 0 with its query heads) through the public
     API, against the fp32 oracle evaluated in chunks of 2048 query rows: per tensor max-abs, mean-abs, the floor that
@@ -656,6 +670,12 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                     secondary[name][extra] = ln[extra]
             torch.cuda.empty_cache()
 
+    # ---- the reference's own CUDA kernels on this GPU (a labelled extra, its own process; single-GPU runs) ----
+    ref_cuda = None
+    if world == 1 and not args.no_ref_cuda:
+        torch.cuda.empty_cache()
+        ref_cuda = reference_cuda_kernels()
+
     # ---- context parallelism over all ranks for one long sequence (multi-GPU runs only) ----
     cp = None
     if world > 1 and not args.no_cp:
@@ -725,6 +745,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         line["secondary"] = secondary
     if cp is not None:
         line["cp"] = cp
+    if ref_cuda is not None:
+        line["reference_cuda_kernels"] = ref_cuda
     if cpu is not None:
         line["cpu_baseline"] = {k_: cpu[k_] for k_ in ("value", "unit", "cores", "kind", "sample")}
     print(json.dumps(line), flush=True)
@@ -1112,6 +1134,7 @@ def main():
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle comparison of the timed workload")
     ap.add_argument("--no-secondary", action="store_true", help="skip the short runs of the other benchmark shapes")
     ap.add_argument("--no-cp", action="store_true", help="multi-GPU runs: skip the context-parallel long-sequence leg")
+    ap.add_argument("--no-ref-cuda", action="store_true", help="skip timing the reference's own CUDA kernels")
     ap.add_argument("--lean", action="store_true", help="profiling runs: only the device-resident timed region")
     ap.add_argument("--min-warmup-seconds", type=float, default=0.5,
                     help="warm-up runs at least this long (0 for profiler captures, where launch counts must be fixed)")
@@ -1120,7 +1143,7 @@ def main():
         args.warmup = max(args.warmup, 3)
     if args.lean:
         args.no_cpu = args.no_e2e = args.no_tile_path = args.no_api = args.no_parity = args.no_secondary = True
-        args.no_cp, args.repeats = True, 1
+        args.no_cp, args.no_ref_cuda, args.repeats = True, True, 1
     if args.seq_len != S or args.window != WINDOW or args.head_dim != D:
         set_geometry(args.seq_len, args.window, args.head_dim)
     rank = int(os.environ.get("RANK", "0"))

@@ -49,7 +49,8 @@ def _worker(rank, world, port, causal, route, d, scheme="ring"):
         for name, got, ref, dim in (("out", out, want[0], 1), ("dq", ql.grad, want[2], 1), ("dk", kl.grad, want[3], 1),
                                     ("dv", vl.grad, want[4], 1), ("dbias", bl.grad, want[5], 3)):
             r = oracle.error_report(name, gather(got, dim), ref)
-            ok, msg = oracle.within_tolerance(r, name in ("dk", "dv", "dbias"))
+            # under the ring dQ too is a sum: one 16-bit partial per visited chunk pair, added in fp32
+            ok, msg = oracle.within_tolerance(r, name in ("dq", "dk", "dv", "dbias"))
             assert ok, msg
     finally:
         dist.destroy_process_group()
