@@ -13,7 +13,8 @@ import torch
 
 from . import _lib
 
-__all__ = ["flash_sparse_attn_func", "FlashDMAttnFunc", "set_kernel_path", "set_compaction"]
+__all__ = ["flash_sparse_attn_func", "flash_sparse_attn_varlen_func", "FlashDMAttnFunc", "set_kernel_path",
+           "set_compaction"]
 
 _KEY_PAD = 128  # mask / bias key dimension is padded to a multiple of this (interface.py:420-430 of the reference)
 _kernel_path = _lib.PATH_AUTO
@@ -458,3 +459,73 @@ def flash_sparse_attn_func(
         query, key, value, attn_mask, attn_bias, softmax_scale, is_causal, softcap, deterministic,
         return_attn_probs, torch.is_grad_enabled(),
     )
+
+
+def flash_sparse_attn_varlen_func(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    cu_seqlens_q: torch.Tensor,
+    cu_seqlens_k: torch.Tensor,
+    max_seqlen_q: int,
+    max_seqlen_k: int,
+    softmax_scale: Optional[float] = None,
+    is_causal: Optional[bool] = None,
+    softcap: Optional[float] = None,
+    deterministic: Optional[bool] = None,
+    return_attn_probs: Optional[bool] = None,
+    block_table: Optional[torch.Tensor] = None,
+):
+    """Attention over packed variable-length sequences; same signature and result as the reference function of the
+    same name (flash_sparse_attn/flash_sparse_attn_interface.py:687-790), which, like this one, takes no dynamic
+    mask or bias.
+
+    query (total_q, H, d); key, value (total_k, Hk, d); cu_seqlens_q / cu_seqlens_k (n + 1,) int32 cumulative lengths.
+    Sequence i is rows cu_seqlens_q[i] : cu_seqlens_q[i+1] of query against rows cu_seqlens_k[i] : cu_seqlens_k[i+1]
+    of key / value; is_causal aligns each sequence's causal mask to ITS bottom-right corner. Returns out
+    (total_q, H, d), or with return_attn_probs=True (out, softmax_lse (H, total_q) fp32, empty tensor).
+
+    Each sequence is a contiguous slice of the packed tensors, so it is handed to the dense kernels as a zero-copy
+    (1, L, H, d) view: one forward (and backward) launch sequence per packed sequence, no padding, no mask. The
+    boundaries are read on the host (one device synchronisation per call). A paged KV cache (`block_table`) is not
+    built and raises NotImplementedError."""
+    if block_table is not None:
+        raise NotImplementedError("paged KV (block_table) is not built into the B200 kernels")
+    if query.dim() != 3 or key.dim() != 3 or value.dim() != 3:
+        raise RuntimeError("query, key and value must be (total_tokens, nheads, headdim)")
+    if cu_seqlens_q.numel() != cu_seqlens_k.numel() or cu_seqlens_q.numel() < 2:
+        raise RuntimeError("cu_seqlens_q and cu_seqlens_k must both have batch_size + 1 entries")
+    cq, ck = cu_seqlens_q.tolist(), cu_seqlens_k.tolist()
+    if cq[-1] > query.shape[0] or ck[-1] > key.shape[0]:
+        raise RuntimeError("cu_seqlens exceed the number of packed tokens")
+    H, d = query.shape[1], query.shape[2]
+    outs, lses = [], []
+    if cq[0] > 0:  # tokens before the first boundary belong to no sequence
+        outs.append(query.new_zeros((cq[0], H, d)))
+        lses.append(torch.full((H, cq[0]), float("inf"), dtype=torch.float32, device=query.device))
+    for i in range(len(cq) - 1):
+        lq, lk = cq[i + 1] - cq[i], ck[i + 1] - ck[i]
+        if lq <= 0:
+            continue
+        if lq > max_seqlen_q or lk > max_seqlen_k:
+            raise RuntimeError("a sequence is longer than max_seqlen_q / max_seqlen_k")
+        q_i = query[cq[i]:cq[i + 1]].unsqueeze(0)
+        if lk <= 0:  # no key at all: zero output, LSE = +inf (flash_api.cpp:532-539)
+            outs.append((q_i * 0)[0])
+            lses.append(torch.full((H, lq), float("inf"), dtype=torch.float32, device=query.device))
+            continue
+        res = flash_sparse_attn_func(q_i, key[ck[i]:ck[i + 1]].unsqueeze(0), value[ck[i]:ck[i + 1]].unsqueeze(0),
+                                     None, None, softmax_scale, is_causal, softcap, deterministic, return_attn_probs)
+        if return_attn_probs:
+            outs.append(res[0][0])
+            lses.append(res[1][0])
+        else:
+            outs.append(res[0])
+    tail = query.shape[0] - cq[-1]
+    if tail > 0:
+        outs.append(query.new_zeros((tail, H, d)))
+        lses.append(torch.full((H, tail), float("inf"), dtype=torch.float32, device=query.device))
+    out = torch.cat(outs, dim=0) if outs else query.new_zeros(query.shape)
+    if not return_attn_probs:
+        return out
+    return out, torch.cat(lses, dim=1), torch.empty((0,), dtype=query.dtype, device=query.device)

@@ -11,17 +11,17 @@ on gathered positions (for query_length < key_length under the left padding the 
 the padded query rows are zeroed afterwards. Few valid keys -> `flash_sparse_attn_func` takes its gathered-keys route.
 
 Packed sequences given by position ids or cu_seqlens (:538-565, `_prepare_from_posids` :270-302) go through the
-reference's varlen kernel as well; here the flattened tokens run as ONE sequence under a per-query visibility mask
-(same example, and causal inside the example with the bottom-right alignment of its own lengths), which the
-full-range kernels skip tile by tile. The mask takes Tq x Tk bytes, so totals above `_PACKED_MASK_LIMIT` elements
-raise NotImplementedError rather than allocate it.
+reference's varlen kernel as well. Here small packs (Tq x Tk up to `_PACKED_MASK_LIMIT` elements) run as ONE
+sequence under a per-query visibility mask (same example, and causal inside the example with the bottom-right
+alignment of its own lengths), which the full-range kernels skip tile by tile -- one launch however many examples
+there are; larger packs go through `flash_sparse_attn_varlen_func`, which runs every example as a zero-copy slice.
 """
 import os
 from typing import Optional
 
 import torch
 
-from ..flash_sparse_attn_interface import flash_sparse_attn_func
+from ..flash_sparse_attn_interface import flash_sparse_attn_func, flash_sparse_attn_varlen_func
 from ..utils.mask import create_mask
 
 
@@ -42,7 +42,7 @@ def _is_packed_sequence(position_ids: Optional[torch.Tensor], batch_size: int) -
     return not bool((position_ids[0] == expected).all())
 
 
-_PACKED_MASK_LIMIT = 1 << 28  # elements of the (Tq, Tk) visibility mask built for packed sequences
+_PACKED_MASK_LIMIT = 1 << 24  # largest (Tq, Tk) visibility mask built for packed sequences; beyond: per-example calls
 
 
 def _packed_visibility(cu_q: torch.Tensor, cu_k: torch.Tensor, total_q: int, total_k: int, causal: bool,
@@ -50,9 +50,6 @@ def _packed_visibility(cu_q: torch.Tensor, cu_k: torch.Tensor, total_q: int, tot
     """(total_q, total_k) bool: query token i sees key token j iff both lie in the same example and, when causal,
     j_local <= i_local + len_k - len_q (the varlen kernels' bottom-right alignment per example). Tokens past the
     last boundary see nothing."""
-    if total_q * total_k > _PACKED_MASK_LIMIT:
-        raise NotImplementedError(
-            f"packed sequences of {total_q} x {total_k} tokens need the variable-length kernels, which are not built")
     cu_q = cu_q.to(device=device, dtype=torch.int64)
     cu_k = cu_k.to(device=device, dtype=torch.int64)
     n = cu_q.numel() - 1
@@ -114,6 +111,14 @@ def _flash_sparse_attention_forward(
         q1 = query_states.reshape(1, -1, query_states.size(-2), query_states.size(-1))
         k1 = key_states.reshape(1, -1, key_states.size(-2), key_states.size(-1))
         v1 = value_states.reshape(1, -1, value_states.size(-2), value_states.size(-1))
+        if q1.size(1) * k1.size(1) > _PACKED_MASK_LIMIT:
+            if max_length_q is None or max_length_k is None:
+                max_length_q = int((cu_seq_lens_q[1:] - cu_seq_lens_q[:-1]).max())
+                max_length_k = int((cu_seq_lens_k[1:] - cu_seq_lens_k[:-1]).max())
+            out = flash_sparse_attn_varlen_func(q1[0], k1[0], v1[0], cu_seq_lens_q, cu_seq_lens_k, max_length_q,
+                                                max_length_k, softmax_scale=softmax_scale, is_causal=is_causal,
+                                                softcap=softcap, deterministic=deterministic)
+            return out.view(B, -1, out.size(-2), out.size(-1))
         visible = _packed_visibility(cu_seq_lens_q, cu_seq_lens_k, q1.size(1), k1.size(1), is_causal, q1.device)
         out = flash_sparse_attn_func(q1, k1, v1, visible[None, None], None, softmax_scale=softmax_scale,
                                      is_causal=False, softcap=softcap, deterministic=deterministic)

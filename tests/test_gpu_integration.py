@@ -102,11 +102,14 @@ def test_padding_mask_single_query(dev):
         check(f"out[{b}]", out[b:b + 1].cpu(), ref, dtype)
 
 
+@pytest.mark.parametrize("route", ["visibility-mask", "per-example"])
 @pytest.mark.parametrize("how", ["position_ids", "cu_seqlens"])
-def test_packed_sequences_match_per_example_attention(dev, how):
+def test_packed_sequences_match_per_example_attention(dev, how, route):
     """Packed examples in one row (reference: flash_sparse_attn/integrations/modeling_flash_sparse_attention_utils.py
-    :538-565): each example must equal causal attention over its own tokens, values and gradients."""
+    :538-565): each example must equal causal attention over its own tokens, values and gradients -- both through
+    the one-launch visibility-mask route (small packs) and through flash_sparse_attn_varlen_func (large packs)."""
     from flash_sparse_attn.integrations import flash_sparse_attention_forward
+    from flash_sparse_attn.integrations import modeling_flash_sparse_attention_utils as glue
 
     lens = (200, 180, 132)
     S, H, Hk, d = sum(lens), 4, 2, 64
@@ -120,8 +123,14 @@ def test_packed_sequences_match_per_example_attention(dev, how):
     else:
         cu = torch.tensor([0, 200, 380, 512], dtype=torch.int32, device=dev)
         kw.update(cu_seq_lens_q=cu, cu_seq_lens_k=cu, max_length_q=200, max_length_k=200)
-    out, _ = flash_sparse_attention_forward(module, qd.transpose(1, 2), kd.transpose(1, 2), vd.transpose(1, 2),
-                                            None, None, scaling=d ** -0.5, **kw)
+    limit = glue._PACKED_MASK_LIMIT
+    if route == "per-example":
+        glue._PACKED_MASK_LIMIT = 100
+    try:
+        out, _ = flash_sparse_attention_forward(module, qd.transpose(1, 2), kd.transpose(1, 2), vd.transpose(1, 2),
+                                                None, None, scaling=d ** -0.5, **kw)
+    finally:
+        glue._PACKED_MASK_LIMIT = limit
     assert out.shape == (1, S, H, d)
     out.backward(dout.to(dev))
     lo = 0
@@ -145,10 +154,49 @@ def test_unsupported_branches_raise(dev):
     pad = torch.ones(1, 16, dtype=torch.bool, device=dev)
     with pytest.raises(ValueError):
         flash_sparse_attention_forward(module, q, q, q, pad, torch.zeros(1, 2, 1, 16, device=dev, dtype=torch.bfloat16))
-    packed = torch.cat([torch.arange(8), torch.arange(8)])[None].to(dev)
-    limit, glue._PACKED_MASK_LIMIT = glue._PACKED_MASK_LIMIT, 100
-    try:
-        with pytest.raises(NotImplementedError):
-            flash_sparse_attention_forward(module, q, q, q, None, None, position_ids=packed)
-    finally:
-        glue._PACKED_MASK_LIMIT = limit
+    from flash_sparse_attn import flash_sparse_attn_varlen_func
+
+    cu = torch.tensor([0, 8, 16], dtype=torch.int32, device=dev)
+    with pytest.raises(NotImplementedError):  # paged KV is not built
+        flash_sparse_attn_varlen_func(q[0].transpose(0, 1), q[0].transpose(0, 1), q[0].transpose(0, 1), cu, cu, 8, 8,
+                                      block_table=torch.zeros(2, 1, dtype=torch.int32, device=dev))
+
+
+def test_varlen_func_ragged_lengths_vs_oracle(dev):
+    """flash_sparse_attn_varlen_func (reference: flash_sparse_attn_interface.py:687-790): ragged query / key lengths
+    per sequence (bottom-right causal alignment of each sequence's own lengths, a sequence without keys, one
+    without queries), output, LSE and gradients against the oracle run per sequence."""
+    from flash_sparse_attn import flash_sparse_attn_varlen_func
+
+    lq = (130, 0, 64, 200)
+    lk = (300, 50, 0, 200)
+    H, Hk, d = 4, 2, 128
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(41)
+    q = torch.randn(sum(lq), H, d, generator=g).to(dtype)
+    k = torch.randn(sum(lk), Hk, d, generator=g).to(dtype)
+    v = torch.randn(sum(lk), Hk, d, generator=g).to(dtype)
+    dout = torch.randn(sum(lq), H, d, generator=g).to(dtype)
+    cu_q = torch.tensor([0] + list(torch.tensor(lq).cumsum(0)), dtype=torch.int32, device=dev)
+    cu_k = torch.tensor([0] + list(torch.tensor(lk).cumsum(0)), dtype=torch.int32, device=dev)
+    qd, kd, vd = (t.to(dev).requires_grad_(True) for t in (q, k, v))
+    out, lse, _ = flash_sparse_attn_varlen_func(qd, kd, vd, cu_q, cu_k, max(lq), max(lk), is_causal=True,
+                                                return_attn_probs=True)
+    assert out.shape == q.shape and lse.shape == (H, sum(lq))
+    out.backward(dout.to(dev))
+    oq = ok_ = 0
+    for a, b in zip(lq, lk):
+        sq, sk = slice(oq, oq + a), slice(ok_, ok_ + b)
+        if a > 0 and b > 0:
+            r = oracle.attention_forward_backward(q[None, sq], k[None, sk], v[None, sk], None, None, dout[None, sq],
+                                                  None, True)
+            check("out", out[sq].detach().cpu()[None], r[0], dtype)
+            fin = torch.isfinite(r[1][0])
+            assert (lse[:, sq].cpu()[fin] - r[1][0][fin]).abs().max() < 2e-3
+            check("dq", qd.grad[sq].cpu()[None], r[2], dtype)
+            check("dk", kd.grad[sk].cpu()[None], r[3], dtype, reduced=True)
+            check("dv", vd.grad[sk].cpu()[None], r[4], dtype, reduced=True)
+        elif a > 0:
+            assert bool((out[sq] == 0).all()) and bool(torch.isposinf(lse[:, sq]).all())
+            assert bool((qd.grad[sq] == 0).all())
+        oq, ok_ = oq + a, ok_ + b
