@@ -718,7 +718,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                      "unit": "TFLOP/s", "frac": bwd_tflops / peaks["peak"], "peak_source": peaks["source"],
                      "frac_sustained": bwd_tflops / peaks["sustained"], "peak_sustained": peaks["sustained"],
                      "frac_of_nominal_2250": bwd_tflops / NOMINAL_TFLOPS,
-                     "traffic": None, "fwd_kernel_achieved": fwd_tflops, "fwd_kernel_frac": fwd_tflops / peaks["peak"]},
+                     # dram__bytes_read + dram__bytes_write of one bwd_kernel launch of exactly this workload, one ncu
+                     # capture (profiles/fwd_bwd_kernel_S32768_compaction_dram_traffic.md); other geometries: null
+                     "traffic": (2364e6 if (compact and (S, WINDOW, D, B) == (32768, 2048, 128, 1)) else None),
+                     "fwd_kernel_achieved": fwd_tflops, "fwd_kernel_frac": fwd_tflops / peaks["peak"]},
         "e2e": {"value": tot / (e2e_ms * 1e-3) / 1e12 if e2e_ms == e2e_ms else None, "unit": "TFLOP/s",
                 "ms_per_step": e2e_ms if e2e_ms == e2e_ms else None,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
