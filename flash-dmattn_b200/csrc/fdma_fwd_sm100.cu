@@ -24,6 +24,9 @@
 #include <cuda_fp16.h>
 #include <math_constants.h>
 
+#include <algorithm>
+#include <mutex>
+
 #include "fdma_internal.h"
 #include "fdma_ptx.cuh"
 
@@ -45,7 +48,8 @@ constexpr unsigned kPolyPairs = FDMA_POLY_PAIRS;  // bit i: pair i of every 16 p
 // Codes stored in the status word when a wait gives up.
 enum WaitCode {
   kWaitQ = 101, kWaitKvEmpty = 102, kWaitKvFullK = 103, kWaitKvFullV = 104, kWaitP = 105, kWaitS = 106,
-  kWaitO = 107, kWaitBmEmpty = 108, kWaitBmFull = 109
+  kWaitO = 107, kWaitBmEmpty = 108, kWaitBmFull = 109, kWaitQEmpty = 110, kWaitOFree = 111, kWaitFlagsFull = 112,
+  kWaitFlagsEmpty = 113
 };
 
 struct FwdKernelParams {
@@ -64,6 +68,9 @@ struct FwdKernelParams {
   int64_t bias_batch_stride, bias_head_stride, bias_row_stride;
   int b, seqlen_q, seqlen_k, h, h_k, h_mask, h_bias;
   int is_causal;
+  int n_mblk;        // query blocks (of kNQ tiles) per (batch, head)
+  int n_items;       // work items = n_mblk * h * b
+  unsigned* sched;   // zeroed by the launcher: index of the next item nobody has taken yet
   float scale_log2;  // softmax_scale * log2(e)
 };
 
@@ -81,9 +88,9 @@ struct Smem {
   static constexpr int kKvOff = kQOff + kNQ * kQBytes;
   static constexpr int kBmOff = kKvOff + kStages * kKvBytes;
   static constexpr int kPosOff = kBmOff + kBmSlots * kBN * 4;
-  static constexpr int kFlagsOff = kPosOff + kBmSlots * kBN * 4;
-  static constexpr int kBarOff = kFlagsOff + kMaxTiles;
-  static constexpr int kNumBars = 1 + 2 * kStages + 2 + 2 + 1 + 2 * kBmSlots + 1;
+  static constexpr int kFlagsOff = kPosOff + kBmSlots * kBN * 4;   // two tables: this work item's and the next one's
+  static constexpr int kBarOff = kFlagsOff + 2 * kMaxTiles;
+  static constexpr int kNumBars = 2 + 2 * kStages + 2 + 2 + 1 + 2 + 2 * kBmSlots + 1 + 4;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kTotal = kMiscOff + 16;
   static constexpr int kAlloc = kTotal + 1024;  // slack to align the base to 1024 B
@@ -127,10 +134,34 @@ __global__ void tile_activity_kernel(const uint8_t* __restrict__ mask, int64_t s
   if (lane == 0) act[w] = any ? 1 : 0;
 }
 
+// Work item = one query block (kNQ query tiles of 128 rows) of one (batch, head). CTAs are persistent: the list is
+// ordered by decreasing causal extent (last query blocks first) and a CTA takes the next item nobody has taken yet
+// (one atomicAdd per item on a counter the launcher zeroes), which balances the SMs to within one short item. Barrier phases, ring positions and tensor memory carry over
+// from one item to the next; nothing is re-initialised, and the pieces of an item that no role of the PREVIOUS
+// item needs any more start early: the tile flags of the next item are built by warp 3 during the current item,
+// its Q and first K / V tiles are loaded as soon as the tensor core has finished with the current Q, its first
+// S = Q K^T products are issued while the softmax warps still write out the current O.
+struct FwdItem {
+  int mblk, h, b, hk, hm, hb;
+};
+
+__device__ __forceinline__ FwdItem fwd_item(const FwdKernelParams& p, int item) {
+  FwdItem w;
+  const int per_block = p.h * p.b;
+  const int rem = item % per_block;
+  w.mblk = p.n_mblk - 1 - item / per_block;
+  w.h = rem % p.h;  // heads of one kv group are neighbours in the list: they meet their shared tiles in L2
+  w.b = rem / p.h;
+  w.hk = w.h / (p.h / p.h_k);
+  w.hm = w.h / (p.h / p.h_mask);
+  w.hb = w.h / (p.h / p.h_bias);
+  return w;
+}
+
 template <int D, bool kBf16, bool kBcast>
 __global__ void __launch_bounds__(Smem<D>::kThreads, 1) fwd_kernel(const __grid_constant__ FwdKernelParams p) {
   using L = Smem<D>;
-  constexpr int kNQ = L::kNQ, kStages = L::kStages, kThreads = L::kThreads;
+  constexpr int kNQ = L::kNQ, kStages = L::kStages;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) &
                                                          ~static_cast<uintptr_t>(1023));
@@ -138,62 +169,56 @@ __global__ void __launch_bounds__(Smem<D>::kThreads, 1) fwd_kernel(const __grid_
   unsigned char* s_kv = smem + L::kKvOff;
   float* s_bm = reinterpret_cast<float*>(smem + L::kBmOff);
   int* s_pos = reinterpret_cast<int*>(smem + L::kPosOff);
-  uint8_t* s_flags = smem + L::kFlagsOff;
+  uint8_t* s_flags_all = smem + L::kFlagsOff;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
-  uint64_t* bar_q = bars;
-  uint64_t* bar_kv_full = bars + 1;
+  uint64_t* bar_q = bars;                           // Q of the item has landed
+  uint64_t* bar_q_empty = bars + 1;                 // the tensor core is done with the item's Q
+  uint64_t* bar_kv_full = bars + 2;
   uint64_t* bar_kv_empty = bar_kv_full + kStages;
-  uint64_t* bar_s_full = bar_kv_empty + kStages;  // [2]
-  uint64_t* bar_p_full = bar_s_full + 2;          // [2]
-  uint64_t* bar_o_done = bar_p_full + 2;
-  uint64_t* bar_bm_full = bar_o_done + 1;
+  uint64_t* bar_s_full = bar_kv_empty + kStages;    // [2]
+  uint64_t* bar_p_full = bar_s_full + 2;            // [2]
+  uint64_t* bar_o_done = bar_p_full + 2;            // every product of the item has completed
+  uint64_t* bar_o_free = bar_o_done + 1;            // [2] the softmax warps have read O_t out of tensor memory
+  uint64_t* bar_bm_full = bar_o_free + 2;
   uint64_t* bar_bm_empty = bar_bm_full + kBmSlots;
   uint64_t* bar_stagger = bar_bm_empty + kBmSlots;  // warpgroup 0 -> warpgroup 1, once
+  uint64_t* bar_flags_full = bar_stagger + 1;       // [2]
+  uint64_t* bar_flags_empty = bar_flags_full + 2;   // [2]
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + L::kMiscOff);
   volatile int* s_abort = reinterpret_cast<volatile int*>(smem + L::kMiscOff + 4);
+  volatile int* s_item = reinterpret_cast<volatile int*>(smem + L::kMiscOff + 8);  // [2]: item of the flag table
+  constexpr int kFlagReaders = 3 + 4 * kNQ;  // producer, MMA issuer, addend warp, one arrival per softmax warp
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  // Query block and head of this CTA. Heaviest (latest) query blocks first under causal masking. Per-query masks
-  // and biases are read from global memory by every head that shares them, so in that mode the heads of one kv
-  // group take consecutive CTA indices for the same query block and meet their shared tiles in L2.
-  int mblk = gridDim.x - 1 - blockIdx.x;
-  int h = blockIdx.y;
-  if (!kBcast) {
-    const int G = p.h / p.h_k;
-    const int lin = blockIdx.x + gridDim.x * blockIdx.y;
-    h = (lin / (G * static_cast<int>(gridDim.x))) * G + lin % G;
-    mblk = gridDim.x - 1 - (lin / G) % gridDim.x;
-  }
-  const int b = blockIdx.z;
-  const int hk = h / (p.h / p.h_k);
-  const int hm = h / (p.h / p.h_mask);
-  const int hb = h / (p.h / p.h_bias);
   const int Sq = p.seqlen_q, Sk = p.seqlen_k;
   const int off = Sk - Sq;
   const int nt_all = (Sk + kBN - 1) / kBN;
   const bool causal = p.is_causal != 0;
-  // Compacted keys: the causal limit is tested on the keys' original positions (ascending along the tile index).
-  const int32_t* pos_row = nullptr;
-  if (kBcast && causal && p.key_pos)
-    pos_row = p.key_pos + b * p.pos_batch_stride +
-              (p.h_pos == p.h ? h : (p.h_pos == p.h_k ? hk : 0)) * p.pos_head_stride;
-
-  int n_end[kNQ];
-#pragma unroll
-  for (int t = 0; t < kNQ; ++t) {
-    const int m0 = (mblk * kNQ + t) * kBM;
-    int ne = nt_all;
-    if (causal && !pos_row) ne = min(ne, max(0, (m0 + kBM + off + kBN - 1) / kBN));
-    if (m0 >= Sq) ne = 0;
-    n_end[t] = ne;
-  }
-  const int nT = max(n_end[0], n_end[kNQ - 1]);
   const WaitCtl ctl{s_abort, p.status};
+  // Per item: number of key tiles each query tile can see at most (causal / length limit), and their maximum.
+  auto tile_limits = [&](const FwdItem& w, int (&n_end)[kNQ], const int32_t*& pos_row) {
+    pos_row = nullptr;
+    if (kBcast && causal && p.key_pos)  // compacted keys: the causal limit is tested on the keys' positions
+      pos_row = p.key_pos + w.b * p.pos_batch_stride +
+                (p.h_pos == p.h ? w.h : (p.h_pos == p.h_k ? w.hk : 0)) * p.pos_head_stride;
+    int nT = 0;
+#pragma unroll
+    for (int t = 0; t < kNQ; ++t) {
+      const int m0 = (w.mblk * kNQ + t) * kBM;
+      int ne = nt_all;
+      if (causal && !pos_row) ne = min(ne, max(0, (m0 + kBM + off + kBN - 1) / kBN));
+      if (m0 >= Sq) ne = 0;
+      n_end[t] = ne;
+      nT = max(nT, ne);
+    }
+    return nT;
+  };
 
-  // ---------------- set-up: barriers, TMEM, tile flags ----------------
+  // ---------------- set-up: barriers, TMEM ----------------
   if (tid == 0) {
     *s_abort = 0;
     mbar_init(bar_q, 1);
+    mbar_init(bar_q_empty, 1);
     for (int i = 0; i < kStages; ++i) {
       mbar_init(bar_kv_full + i, 1);
       mbar_init(bar_kv_empty + i, 1);
@@ -201,6 +226,9 @@ __global__ void __launch_bounds__(Smem<D>::kThreads, 1) fwd_kernel(const __grid_
     for (int t = 0; t < 2; ++t) {
       mbar_init(bar_s_full + t, 1);
       mbar_init(bar_p_full + t, kBM);
+      mbar_init(bar_o_free + t, 4);  // one arrival per softmax warp of the query tile
+      mbar_init(bar_flags_full + t, 1);
+      mbar_init(bar_flags_empty + t, kFlagReaders);
     }
     mbar_init(bar_o_done, 1);
     mbar_init(bar_stagger, kBM);
@@ -219,55 +247,6 @@ __global__ void __launch_bounds__(Smem<D>::kThreads, 1) fwd_kernel(const __grid_
     prefetch_tmap(&p.tm_k);
     prefetch_tmap(&p.tm_v);
   }
-  // Tile flags: bit t of s_flags[j] = key tile j is processed for query tile t.
-  for (int j = tid; j < nT; j += kThreads) {
-    uint8_t f = 0;
-    if (kBcast) {
-      bool any = true;
-      if (p.mask) {
-        const uint8_t* mrow = p.mask + b * p.mask_batch_stride + hm * p.mask_head_stride + j * kBN;
-        uint32_t acc = 0;
-#pragma unroll
-        for (int i = 0; i < kBN / 16; ++i) {
-          const uint4 v = *reinterpret_cast<const uint4*>(mrow + i * 16);
-          uint32_t w[4] = {v.x, v.y, v.z, v.w};
-          if (j * kBN + i * 16 + 16 > Sk) {  // ragged last tile: drop keys >= Sk
-#pragma unroll
-            for (int e = 0; e < 16; ++e)
-              if (j * kBN + i * 16 + e >= Sk) w[e >> 2] &= ~(0xFFu << ((e & 3) * 8));
-          }
-          acc |= w[0] | w[1] | w[2] | w[3];
-        }
-        any = acc != 0;
-      }
-      if (any) {
-#pragma unroll
-        for (int t = 0; t < kNQ; ++t)
-          if (j < n_end[t]) f |= (1 << t);
-        if (pos_row) {  // the tile's smallest position against the last row of each query tile
-          const int64_t pmin = pos_row[j * kBN];
-#pragma unroll
-          for (int t = 0; t < kNQ; ++t) {
-            const int qlast = min((mblk * kNQ + t) * kBM + kBM - 1, Sq - 1);
-            if (pmin > static_cast<int64_t>(qlast) + p.causal_shift) f &= ~(1 << t);
-          }
-        }
-      }
-    } else {
-#pragma unroll
-      for (int t = 0; t < kNQ; ++t) {
-        if (j < n_end[t]) {
-          bool a = true;
-          if (p.act) {
-            const int MT = (Sq + kBM - 1) / kBM;
-            a = p.act[((static_cast<int64_t>(b) * p.h_mask + hm) * MT + (mblk * kNQ + t)) * nt_all + j] != 0;
-          }
-          if (a) f |= (1 << t);
-        }
-      }
-    }
-    s_flags[j] = f;
-  }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -278,49 +257,81 @@ __global__ void __launch_bounds__(Smem<D>::kThreads, 1) fwd_kernel(const __grid_
   // (one query tile per CTA: 256 threads have 256 registers each available, nothing to re-partition)
   if (kNQ == 2) asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
   if (warp == 0) {
-    if (lane == 0 && nT > 0) {
+    if (lane == 0) {
       FDMA_PROF_BEGIN();
-      // Q tiles (rows beyond Sq are zero-filled by TMA)
-      mbar_arrive_expect_tx(bar_q, kNQ * L::kQBytes);
-#pragma unroll
-      for (int t = 0; t < kNQ; ++t)
-#pragma unroll
-        for (int kb = 0; kb < D / 64; ++kb)
-          tma_load_4d(s_q + t * L::kQBytes + kb * (kBM * 128), &p.tm_q, bar_q, kb * 64, h, (mblk * kNQ + t) * kBM, b);
       int it = 0;
       bool ok = true;
-      for (int j = 0; j < nT && ok; ++j) {
-        if (s_flags[j] == 0) continue;
+      for (int ic = 0; ok; ++ic) {
+        ok = mbar_wait(bar_flags_full + (ic & 1), (ic >> 1) & 1, ctl, kWaitFlagsFull);
+        if (!ok) break;
+        const int item = s_item[ic & 1];
+        if (item >= p.n_items) break;
+        const FwdItem w = fwd_item(p, item);
+        int n_end[kNQ];
+        const int32_t* pos_row;
+        const int nT = tile_limits(w, n_end, pos_row);
+        const uint8_t* s_flags = s_flags_all + (ic & 1) * kMaxTiles;
+        ok = mbar_wait(bar_q_empty, (ic & 1) ^ 1, ctl, kWaitQEmpty);
+        if (!ok) break;
+        // Q tiles (rows beyond Sq are zero-filled by TMA)
+        mbar_arrive_expect_tx(bar_q, kNQ * L::kQBytes);
 #pragma unroll
-        for (int kv = 0; kv < 2; ++kv) {
-          const int slot = it % kStages;
-          ok = FDMA_PROF_WAIT(0, mbar_wait(bar_kv_empty + slot, ((it / kStages) & 1) ^ 1, ctl, kWaitKvEmpty));
-          if (!ok) break;
-          mbar_arrive_expect_tx(bar_kv_full + slot, L::kKvBytes);
-          const CUtensorMap* tm = kv == 0 ? &p.tm_k : &p.tm_v;
+        for (int t = 0; t < kNQ; ++t)
 #pragma unroll
           for (int kb = 0; kb < D / 64; ++kb)
-            tma_load_4d(s_kv + slot * L::kKvBytes + kb * (kBN * 128), tm, bar_kv_full + slot, kb * 64, hk, j * kBN, b);
-          ++it;
+            tma_load_4d(s_q + t * L::kQBytes + kb * (kBM * 128), &p.tm_q, bar_q, kb * 64, w.h,
+                        (w.mblk * kNQ + t) * kBM, w.b);
+        for (int j = 0; j < nT && ok; ++j) {
+          if (s_flags[j] == 0) continue;
+#pragma unroll
+          for (int kv = 0; kv < 2; ++kv) {
+            const int slot = it % kStages;
+            ok = FDMA_PROF_WAIT(0, mbar_wait(bar_kv_empty + slot, ((it / kStages) & 1) ^ 1, ctl, kWaitKvEmpty));
+            if (!ok) break;
+            mbar_arrive_expect_tx(bar_kv_full + slot, L::kKvBytes);
+            const CUtensorMap* tm = kv == 0 ? &p.tm_k : &p.tm_v;
+#pragma unroll
+            for (int kb = 0; kb < D / 64; ++kb)
+              tma_load_4d(s_kv + slot * L::kKvBytes + kb * (kBN * 128), tm, bar_kv_full + slot, kb * 64, w.hk, j * kBN,
+                          w.b);
+            ++it;
+          }
         }
+        mbar_arrive(bar_flags_empty + (ic & 1));
       }
       FDMA_PROF_END(0, true);
     }
   } else if (warp == 1) {
-    if (nT > 0) {  // whole warp, uniform control flow; the issue wrappers elect one lane
-      constexpr uint32_t idesc_qk = umma_idesc(kBM, kBN, kBf16, false, false);
-      constexpr uint32_t idesc_pv = umma_idesc(kBM, D, kBf16, false, true);
-      const uint32_t q_addr = smem_u32(s_q), kv_addr = smem_u32(s_kv);
-      FDMA_PROF_BEGIN();
-      bool ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(0, mbar_wait(bar_q, 0, ctl, kWaitQ)));
+    // whole warp, uniform control flow; the issue wrappers elect one lane
+    constexpr uint32_t idesc_qk = umma_idesc(kBM, kBN, kBf16, false, false);
+    constexpr uint32_t idesc_pv = umma_idesc(kBM, D, kBf16, false, true);
+    const uint32_t q_addr = smem_u32(s_q), kv_addr = smem_u32(s_kv);
+    FDMA_PROF_BEGIN();
+    int a = 0;                    // ring position: K of the a-th kept tile (over all items) is ring item 2a, V 2a+1
+    uint32_t pcnt[2] = {0, 0};    // P hand-overs received per query tile, over all items (barrier parity)
+    bool ok = true;
+    for (int ic = 0; ok; ++ic) {
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_flags_full + (ic & 1), (ic >> 1) & 1, ctl, kWaitFlagsFull));
+      if (!ok) break;
+      const int item = s_item[ic & 1];
+      if (item >= p.n_items) break;
+      const FwdItem w = fwd_item(p, item);
+      int n_end[kNQ];
+      const int32_t* pos_row;
+      const int nT = tile_limits(w, n_end, pos_row);
+      const uint8_t* s_flags = s_flags_all + (ic & 1) * kMaxTiles;
+      ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(0, mbar_wait(bar_q, ic & 1, ctl, kWaitQ)));
+      if (!ok) break;
       tc_fence_after_sync();
-      int a = 0;            // index of the current kept tile; its K is ring item 2a, its V item 2a+1
-      int prev_j = -1;      // previous kept tile (its PV is still to be issued)
-      uint32_t pcnt[2] = {0, 0};
+      int prev_j = -1;            // previous kept tile of this item (its PV is still to be issued)
+      uint32_t pv_done[2] = {0, 0};  // PV products issued for this item per query tile (0: the first one overwrites O)
       for (int j = 0; j <= nT && ok; ++j) {
         const bool last = (j == nT);
         const uint8_t fl = last ? 0 : s_flags[j];
         if (!last && fl == 0) continue;
+        if (last && prev_j < 0) break;  // the item has no kept tile at all
+        if (last) umma_commit(bar_q_empty);  // every S = Q K^T of the item has been issued: Q may be replaced as soon
+                                             // as they complete, while the last P V products are still to come
         const uint8_t pfl = prev_j >= 0 ? s_flags[prev_j] : 0;
         const int k_it = 2 * a, v_it = 2 * (a - 1) + 1;
         if (!last) {
@@ -340,15 +351,20 @@ __global__ void __launch_bounds__(Smem<D>::kThreads, 1) fwd_kernel(const __grid_
           if (pfl & (1 << t)) {
             ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(3 + t, mbar_wait(bar_p_full + t, pcnt[t] & 1, ctl, kWaitP)));
             if (!ok) break;
+            if (pv_done[t] == 0 && ic > 0) {  // the previous item's O_t must have left tensor memory
+              ok = __all_sync(0xffffffffu, mbar_wait(bar_o_free + t, (ic - 1) & 1, ctl, kWaitOFree));
+              if (!ok) break;
+            }
             tc_fence_after_sync();
             const uint32_t o_col = tmem_base + kNQ * kBN + t * 128;
             const uint32_t v_base = kv_addr + (v_it % kStages) * L::kKvBytes;
 #pragma unroll
             for (int kk = 0; kk < kBN / 16; ++kk) {
               const uint64_t bd = umma_desc_sw128(v_base + kk * 2048, kBN * 128, 1024);
-              umma_ts(o_col, s_col + kk * 8, bd, idesc_pv, (pcnt[t] > 0 || kk > 0) ? 1u : 0u);
+              umma_ts(o_col, s_col + kk * 8, bd, idesc_pv, (pv_done[t] > 0 || kk > 0) ? 1u : 0u);
             }
             ++pcnt[t];
+            ++pv_done[t];
           }
           if (fl & (1 << t)) {
             const uint32_t qa = q_addr + t * L::kQBytes;
@@ -370,54 +386,144 @@ __global__ void __launch_bounds__(Smem<D>::kThreads, 1) fwd_kernel(const __grid_
           ++a;
         }
       }
+      if (!ok) break;
+      if (prev_j < 0) umma_commit(bar_q_empty);  // (an item without kept tiles never read its Q)
       umma_commit(bar_o_done);
-      FDMA_PROF_END(8, lane == 0);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_flags_empty + (ic & 1));
     }
+    FDMA_PROF_END(8, lane == 0);
   } else if (warp == 2) {
-    if (kBcast) {
-      const uint8_t* mrow = p.mask ? p.mask + b * p.mask_batch_stride + hm * p.mask_head_stride : nullptr;
-      const uint16_t* brow = p.bias ? reinterpret_cast<const uint16_t*>(p.bias) + b * p.bias_batch_stride +
-                                          hb * p.bias_head_stride
-                                    : nullptr;
-      int bi = 0;
-      bool ok = true;
-      for (int j = 0; j < nT && ok; ++j) {
-        if (s_flags[j] == 0) continue;
-        const int slot = bi % kBmSlots;
-        ok = mbar_wait(bar_bm_empty + slot, ((bi / kBmSlots) & 1) ^ 1, ctl, kWaitBmEmpty);
-        if (!ok) break;
-        const int k0 = j * kBN + lane * 4;
-        float v[4];
-        uint32_t mbits = 0x01010101u;
-        if (mrow) mbits = *reinterpret_cast<const uint32_t*>(mrow + k0);
-        uint2 braw = make_uint2(0u, 0u);
-        if (brow) braw = *reinterpret_cast<const uint2*>(brow + k0);
-        const uint16_t bh[4] = {static_cast<uint16_t>(braw.x & 0xFFFFu), static_cast<uint16_t>(braw.x >> 16),
-                                static_cast<uint16_t>(braw.y & 0xFFFFu), static_cast<uint16_t>(braw.y >> 16)};
+    // bias + mask of a key tile -> one fp32 addend per key (row-broadcast mode); other modes only release the flags
+    int bi = 0;
+    bool ok = true;
+    for (int ic = 0; ok; ++ic) {
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_flags_full + (ic & 1), (ic >> 1) & 1, ctl, kWaitFlagsFull));
+      if (!ok) break;
+      const int item = s_item[ic & 1];
+      if (item >= p.n_items) break;
+      const FwdItem w = fwd_item(p, item);
+      int n_end[kNQ];
+      const int32_t* pos_row;
+      const int nT = tile_limits(w, n_end, pos_row);
+      const uint8_t* s_flags = s_flags_all + (ic & 1) * kMaxTiles;
+      if (kBcast) {
+        const uint8_t* mrow = p.mask ? p.mask + w.b * p.mask_batch_stride + w.hm * p.mask_head_stride : nullptr;
+        const uint16_t* brow = p.bias ? reinterpret_cast<const uint16_t*>(p.bias) + w.b * p.bias_batch_stride +
+                                            w.hb * p.bias_head_stride
+                                      : nullptr;
+        for (int j = 0; j < nT && ok; ++j) {
+          if (s_flags[j] == 0) continue;
+          const int slot = bi % kBmSlots;
+          ok = __all_sync(0xffffffffu, mbar_wait(bar_bm_empty + slot, ((bi / kBmSlots) & 1) ^ 1, ctl, kWaitBmEmpty));
+          if (!ok) break;
+          const int k0 = j * kBN + lane * 4;
+          float v[4];
+          uint32_t mbits = 0x01010101u;
+          if (mrow) mbits = *reinterpret_cast<const uint32_t*>(mrow + k0);
+          uint2 braw = make_uint2(0u, 0u);
+          if (brow) braw = *reinterpret_cast<const uint2*>(brow + k0);
+          const uint16_t bh[4] = {static_cast<uint16_t>(braw.x & 0xFFFFu), static_cast<uint16_t>(braw.x >> 16),
+                                  static_cast<uint16_t>(braw.y & 0xFFFFu), static_cast<uint16_t>(braw.y >> 16)};
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          float bf;
-          if (kBf16) bf = __uint_as_float(static_cast<uint32_t>(bh[i]) << 16);
-          else bf = __half2float(__ushort_as_half(bh[i]));
-          const bool keep = ((mbits >> (8 * i)) & 0xFFu) != 0 && (k0 + i) < Sk;
-          v[i] = keep ? bf * kLog2e : -CUDART_INF_F;
-        }
-        *reinterpret_cast<float4*>(s_bm + slot * kBN + lane * 4) = make_float4(v[0], v[1], v[2], v[3]);
-        if (pos_row) {
-          int4 pv = make_int4(0x7FFFFFFF, 0x7FFFFFFF, 0x7FFFFFFF, 0x7FFFFFFF);
-          if (k0 + 3 < Sk) {
-            pv = *reinterpret_cast<const int4*>(pos_row + k0);
-          } else {
-            if (k0 < Sk) pv.x = pos_row[k0];
-            if (k0 + 1 < Sk) pv.y = pos_row[k0 + 1];
-            if (k0 + 2 < Sk) pv.z = pos_row[k0 + 2];
+          for (int i = 0; i < 4; ++i) {
+            float bf;
+            if (kBf16) bf = __uint_as_float(static_cast<uint32_t>(bh[i]) << 16);
+            else bf = __half2float(__ushort_as_half(bh[i]));
+            const bool keep = ((mbits >> (8 * i)) & 0xFFu) != 0 && (k0 + i) < Sk;
+            v[i] = keep ? bf * kLog2e : -CUDART_INF_F;
           }
-          *reinterpret_cast<int4*>(s_pos + slot * kBN + lane * 4) = pv;
+          *reinterpret_cast<float4*>(s_bm + slot * kBN + lane * 4) = make_float4(v[0], v[1], v[2], v[3]);
+          if (pos_row) {
+            int4 pv = make_int4(0x7FFFFFFF, 0x7FFFFFFF, 0x7FFFFFFF, 0x7FFFFFFF);
+            if (k0 + 3 < Sk) {
+              pv = *reinterpret_cast<const int4*>(pos_row + k0);
+            } else {
+              if (k0 < Sk) pv.x = pos_row[k0];
+              if (k0 + 1 < Sk) pv.y = pos_row[k0 + 1];
+              if (k0 + 2 < Sk) pv.z = pos_row[k0 + 2];
+            }
+            *reinterpret_cast<int4*>(s_pos + slot * kBN + lane * 4) = pv;
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_bm_full + slot);
+          ++bi;
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_bm_full + slot);
-        ++bi;
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_flags_empty + (ic & 1));
+    }
+  } else {
+    // warp 3: tile flags of every item, one item ahead of the other roles. Bit t of flags[j] = key tile j is
+    // processed for query tile t.
+    bool ok = true;
+    for (int ic = 0; ok; ++ic) {
+      ok = __all_sync(0xffffffffu, mbar_wait(bar_flags_empty + (ic & 1), ((ic >> 1) & 1) ^ 1, ctl, kWaitFlagsEmpty));
+      if (!ok) break;
+      int item = 0;
+      if (lane == 0) item = static_cast<int>(min(atomicAdd(p.sched, 1u), static_cast<unsigned>(p.n_items)));
+      item = __shfl_sync(0xffffffffu, item, 0);
+      if (lane == 0) s_item[ic & 1] = item;  // n_items = no item left: the other roles leave their loops on it
+      if (item >= p.n_items) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_flags_full + (ic & 1));
+        break;
+      }
+      const FwdItem w = fwd_item(p, item);
+      int n_end[kNQ];
+      const int32_t* pos_row;
+      const int nT = tile_limits(w, n_end, pos_row);
+      uint8_t* s_flags = s_flags_all + (ic & 1) * kMaxTiles;
+      for (int j = lane; j < nT; j += 32) {
+        uint8_t f = 0;
+        if (kBcast) {
+          bool any = true;
+          if (p.mask) {
+            const uint8_t* mrow = p.mask + w.b * p.mask_batch_stride + w.hm * p.mask_head_stride + j * kBN;
+            uint32_t acc = 0;
+#pragma unroll
+            for (int i = 0; i < kBN / 16; ++i) {
+              const uint4 v = *reinterpret_cast<const uint4*>(mrow + i * 16);
+              uint32_t wd[4] = {v.x, v.y, v.z, v.w};
+              if (j * kBN + i * 16 + 16 > Sk) {  // ragged last tile: drop keys >= Sk
+#pragma unroll
+                for (int e = 0; e < 16; ++e)
+                  if (j * kBN + i * 16 + e >= Sk) wd[e >> 2] &= ~(0xFFu << ((e & 3) * 8));
+              }
+              acc |= wd[0] | wd[1] | wd[2] | wd[3];
+            }
+            any = acc != 0;
+          }
+          if (any) {
+#pragma unroll
+            for (int t = 0; t < kNQ; ++t)
+              if (j < n_end[t]) f |= (1 << t);
+            if (pos_row) {  // the tile's smallest position against the last row of each query tile
+              const int64_t pmin = pos_row[j * kBN];
+#pragma unroll
+              for (int t = 0; t < kNQ; ++t) {
+                const int qlast = min((w.mblk * kNQ + t) * kBM + kBM - 1, Sq - 1);
+                if (pmin > static_cast<int64_t>(qlast) + p.causal_shift) f &= ~(1 << t);
+              }
+            }
+          }
+        } else {
+#pragma unroll
+          for (int t = 0; t < kNQ; ++t) {
+            if (j < n_end[t]) {
+              bool act = true;
+              if (p.act) {
+                const int MT = (Sq + kBM - 1) / kBM;
+                act = p.act[((static_cast<int64_t>(w.b) * p.h_mask + w.hm) * MT + (w.mblk * kNQ + t)) * nt_all + j] != 0;
+              }
+              if (act) f |= (1 << t);
+            }
+          }
+        }
+        s_flags[j] = f;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_flags_full + (ic & 1));
     }
   }
   } else {
@@ -425,30 +531,42 @@ __global__ void __launch_bounds__(Smem<D>::kThreads, 1) fwd_kernel(const __grid_
     // ---------------- softmax warpgroup for query tile t ----------------
     const int t = (warp - 4) >> 2;
     const int row = (warp & 3) * 32 + lane;          // row inside the tile == TMEM lane
-    const int m0 = (mblk * kNQ + t) * kBM;
-    const int qrow = m0 + row;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t s_taddr = tmem_base + lane_addr + t * kBN;
     const uint32_t o_taddr = tmem_base + lane_addr + kNQ * kBN + t * 128;
+    FDMA_PROF_BEGIN();
+    uint32_t scnt = 0;   // S tiles received over all items (barrier parity)
+    int bi = 0;          // addend-ring position over all items
+    bool ok = true;
+    bool stagger_sent = false;
+    for (int ic = 0; ok; ++ic) {
+    ok = __all_sync(0xffffffffu, mbar_wait(bar_flags_full + (ic & 1), (ic >> 1) & 1, ctl, kWaitFlagsFull));
+    if (!ok) break;
+    const int item = s_item[ic & 1];
+    if (item >= p.n_items) break;
+    const FwdItem w = fwd_item(p, item);
+    const int h = w.h, b = w.b;
+    int n_end[kNQ];
+    const int32_t* pos_row;
+    const int nT = tile_limits(w, n_end, pos_row);
+    const uint8_t* s_flags = s_flags_all + (ic & 1) * kMaxTiles;
+    const int m0 = (w.mblk * kNQ + t) * kBM;
+    const int qrow = m0 + row;
     const int qclamp = min(qrow, Sq - 1);
     const uint8_t* mrow = nullptr;
     const uint16_t* brow = nullptr;
     if (!kBcast) {
-      if (p.mask) mrow = p.mask + b * p.mask_batch_stride + hm * p.mask_head_stride + qclamp * p.mask_row_stride;
+      if (p.mask) mrow = p.mask + b * p.mask_batch_stride + w.hm * p.mask_head_stride + qclamp * p.mask_row_stride;
       if (p.bias)
-        brow = reinterpret_cast<const uint16_t*>(p.bias) + b * p.bias_batch_stride + hb * p.bias_head_stride +
+        brow = reinterpret_cast<const uint16_t*>(p.bias) + b * p.bias_batch_stride + w.hb * p.bias_head_stride +
                qclamp * p.bias_row_stride;
     }
     float m_ref = -CUDART_INF_F, l = 0.f;
-    FDMA_PROF_BEGIN();
-    uint32_t scnt = 0;
-    int bi = 0;
-    bool ok = true;
+    uint32_t sitem = 0;  // S tiles of this item processed by this warpgroup
     // The two warpgroups share the transcendental unit; running their exp2 phases at the same time doubles the
     // length of both. Warpgroup 1 therefore starts only when warpgroup 0 reaches the exp2 phase of its first
     // tile, which keeps the two loops roughly half a period apart.
-    bool stagger_sent = false;
-    if (kNQ == 2 && t == 1) ok = __all_sync(0xffffffffu, mbar_wait(bar_stagger, 0, ctl, kWaitS));
+    if (kNQ == 2 && t == 1 && ic == 0) ok = __all_sync(0xffffffffu, mbar_wait(bar_stagger, 0, ctl, kWaitS));
     for (int j = 0; j < nT && ok; ++j) {
       const uint8_t fl = s_flags[j];
       if (fl == 0) continue;
@@ -571,7 +689,7 @@ __global__ void __launch_bounds__(Smem<D>::kThreads, 1) fwd_kernel(const __grid_
         if (__any_sync(0xffffffffu, need)) {
           const float m_new = need ? fmaxf(m_ref, m_tile) : m_ref;
           const float alpha = (m_new == -CUDART_INF_F) ? 1.f : fast_exp2(m_ref - m_new);
-          if (scnt > 0) {  // O_t holds earlier tiles: rescale it (their MMAs finished before this S arrived)
+          if (sitem > 0) {  // O_t holds earlier tiles: rescale it (their MMAs finished before this S arrived)
             uint32_t r[32];
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
@@ -615,6 +733,7 @@ __global__ void __launch_bounds__(Smem<D>::kThreads, 1) fwd_kernel(const __grid_
         tc_fence_before_sync();
         mbar_arrive(bar_p_full + t);
         ++scnt;
+        ++sitem;
       }
       if (kBcast) {
         __syncwarp();
@@ -622,28 +741,38 @@ __global__ void __launch_bounds__(Smem<D>::kThreads, 1) fwd_kernel(const __grid_
       }
       ++bi;
     }
-    if (t == 0 && !stagger_sent) mbar_arrive(bar_stagger);  // no tile processed: release warpgroup 1 anyway
-    // ---------------- epilogue ----------------
-    if (ok && nT > 0) ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(2, mbar_wait(bar_o_done, 0, ctl, kWaitO)));
-    FDMA_PROF_END(16, tid == 128);
-    FDMA_PROF_END(24, tid == 256);
+    if (!ok) break;
+    if (t == 0 && !stagger_sent) {  // no tile processed: release warpgroup 1 anyway
+      mbar_arrive(bar_stagger);
+      stagger_sent = true;
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar_flags_empty + (ic & 1));
+    // ---------------- epilogue of the item ----------------
+    ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(2, mbar_wait(bar_o_done, ic & 1, ctl, kWaitO)));
+    if (!ok) break;
     tc_fence_after_sync();
-    if (ok) {
+    {
       const bool in_range = qrow < Sq;  // TMEM loads below are warp-collective: every lane runs them
       // m_ref stays -inf iff every score of the row was masked (l can then hold 2^-125 terms of exp2_poly2)
-      const bool alive = scnt > 0 && l > 0.f && m_ref != -CUDART_INF_F;
+      const bool alive = sitem > 0 && l > 0.f && m_ref != -CUDART_INF_F;
       const float inv = alive ? 1.f / l : 0.f;
       unsigned char* orow = reinterpret_cast<unsigned char*>(p.out) +
                             (b * p.o_batch_stride + static_cast<int64_t>(qclamp) * p.o_row_stride +
                              h * p.o_head_stride) * 2;
       if (in_range)
         p.lse[(static_cast<int64_t>(b) * p.h + h) * Sq + qrow] = alive ? (m_ref + fast_log2(l)) * kLn2 : CUDART_INF_F;
-      if (scnt > 0) {
+      if (sitem > 0) {
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
           uint32_t r[32];
           tmem_ld_x32(o_taddr + c * 32, r);
           tmem_wait_ld();
+          if (c == D / 32 - 1) {  // O_t is in registers: the next item's first P V product may overwrite it
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_o_free + t);
+          }
           if (in_range) {
 #pragma unroll
             for (int v4 = 0; v4 < 4; ++v4) {
@@ -656,11 +785,18 @@ __global__ void __launch_bounds__(Smem<D>::kThreads, 1) fwd_kernel(const __grid_
             }
           }
         }
-      } else if (in_range) {
+      } else {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_o_free + t);
+        if (in_range) {
 #pragma unroll
-        for (int c = 0; c < D / 8; ++c) *reinterpret_cast<uint4*>(orow + c * 16) = make_uint4(0, 0, 0, 0);
+          for (int c = 0; c < D / 8; ++c) *reinterpret_cast<uint4*>(orow + c * 16) = make_uint4(0, 0, 0, 0);
+        }
       }
     }
+    }  // item loop
+    FDMA_PROF_END(16, tid == 128);
+    FDMA_PROF_END(24, tid == 256);
   }
 
   // ---------------- tear-down ----------------
@@ -670,6 +806,27 @@ __global__ void __launch_bounds__(Smem<D>::kThreads, 1) fwd_kernel(const __grid_
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
   }
+}
+
+// Item counters of the persistent forward: a ring of words in device memory that is part of the library image, one
+// word per launch (zeroed on the launch's stream just before it). Launches only share a word when more than
+// kSchedSlots of them are in flight on one device at the same time.
+constexpr int kSchedSlots = 256;
+__device__ unsigned g_fwd_sched[kSchedSlots];
+
+unsigned* next_sched_slot() {
+  static std::mutex mu;
+  static unsigned* base[64] = {nullptr};
+  static unsigned next[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!base[dev]) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_fwd_sched) != cudaSuccess) return nullptr;
+    base[dev] = static_cast<unsigned*>(ptr);
+  }
+  return base[dev] + (next[dev]++ % kSchedSlots);
 }
 
 struct FwdPlan {
@@ -747,7 +904,15 @@ int launch(const fdma_fwd_params& p, const FwdPlan& pl, cudaStream_t stream) {
   // The attribute belongs to the (function, device) pair: set it on every call, whichever device is current.
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc);
   if (e != cudaSuccess) return static_cast<int>(e);
-  dim3 grid((p.seqlen_q + kNQ * kBM - 1) / (kNQ * kBM), p.h, p.b);
+  kp.n_mblk = (p.seqlen_q + kNQ * kBM - 1) / (kNQ * kBM);
+  const int64_t n_items = static_cast<int64_t>(kp.n_mblk) * p.h * p.b;
+  if (n_items > 0x7FFFFFFF) return FDMA_ERR_TOO_LARGE;
+  kp.n_items = static_cast<int>(n_items);
+  dim3 grid(static_cast<unsigned>(std::min<int64_t>(n_items, sm_count())));  // persistent CTAs, one per SM
+  kp.sched = next_sched_slot();
+  if (!kp.sched) return FDMA_ERR_DRIVER;
+  e = cudaMemsetAsync(kp.sched, 0, sizeof(unsigned), stream);
+  if (e != cudaSuccess) return static_cast<int>(e);
   cudaEvent_t ev0, ev1;
   take_timing_events(&ev0, &ev1);
   if (ev0) cudaEventRecord(ev0, stream);
