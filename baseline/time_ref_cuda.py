@@ -22,6 +22,9 @@ def main():
     ap.add_argument("--seq-len", type=int, default=32768)
     ap.add_argument("--window", type=int, default=2048)
     ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--per-query", action="store_true",
+                    help="per-query bias and mask (B,Hkv,Sq,Sk) instead of row-broadcast ones (use --seq-len 8192 "
+                         "--window 1024 for the per-query training shape)")
     args = ap.parse_args()
     if not os.path.exists(os.path.join(REF, "flash_sparse_attn_cuda.so")):
         print(json.dumps({"impl": "reference-cuda", "unavailable": "baseline/_ref/flash_sparse_attn_cuda.so not built"}))
@@ -40,7 +43,7 @@ def main():
     g = torch.Generator(device=dev).manual_seed(1234)
     rnd = lambda *shape: torch.randn(shape, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
     q, k, v = rnd(1, S, H, d), rnd(1, S, Hk, d), rnd(1, S, Hk, d)
-    bias, dout = rnd(1, Hk, 1, S), rnd(1, S, H, d)
+    bias, dout = rnd(1, Hk, S if args.per_query else 1, S), rnd(1, S, H, d)
     mask = create_mask(bias, None, 1, S, S, W, torch.finfo(torch.bfloat16).min)
     q.requires_grad_(True); k.requires_grad_(True); v.requires_grad_(True); bias.requires_grad_(True)
 
@@ -70,7 +73,8 @@ def main():
     except Exception as e:  # noqa: BLE001
         print(json.dumps({"impl": "reference-cuda", "unavailable": f"run failed: {e!r}"[:400]}))
         return
-    print(json.dumps({"impl": "reference-cuda", "workload": f"B=1 S={S} W={W} d={d} Hq={H} Hkv={Hk} causal, bias (B,Hkv,1,Sk)",
+    shape = "(B,Hkv,Sq,Sk)" if args.per_query else "(B,Hkv,1,Sk)"
+    print(json.dumps({"impl": "reference-cuda", "workload": f"B=1 S={S} W={W} d={d} Hq={H} Hkv={Hk} causal, bias and mask {shape}",
                       "fwd_bwd_ms": e0.elapsed_time(e1) / args.steps, "fwd_ms": f0.elapsed_time(f1) / args.steps,
                       "steps": args.steps, "build": "sm_100, mma.sync kernels unchanged, CUTLASS headers from flashinfer"}))
 

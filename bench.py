@@ -419,14 +419,15 @@ def chunked_oracle(q, k, v, mask, bias, dout, rows):
     return o_ref, dq_ref, kf.grad, vf.grad, bf.grad
 
 
-def reference_cuda_kernels() -> dict:
+def reference_cuda_kernels(extra=()) -> dict:
     """The reference's mma.sync kernels, recompiled unchanged for sm_100 (baseline/build_ref_cuda.py), timed on one
     batch element of this workload through the reference's own flash_sparse_attn_func, in a child process that sees
     only baseline/_ref (baseline/time_ref_cuda.py). Context for `value` and `tile_or`; not the reference arm."""
     script = os.path.join(ROOT, "baseline", "time_ref_cuda.py")
     try:
-        res = subprocess.run([sys.executable, script, "--seq-len", str(S), "--window", str(WINDOW), "--steps", "3"],
-                             capture_output=True, text=True, timeout=300)
+        cmd = [sys.executable, script, "--steps", "3"] + (list(extra) if extra else
+                                                          ["--seq-len", str(S), "--window", str(WINDOW)])
+        res = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
         lines = [ln for ln in res.stdout.splitlines() if ln.startswith("{")]
         return json.loads(lines[-1]) if lines else {"unavailable": (res.stderr or "no output")[-300:]}
     except Exception as e:  # noqa: BLE001
@@ -675,6 +676,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     if world == 1 and not args.no_ref_cuda:
         torch.cuda.empty_cache()
         ref_cuda = reference_cuda_kernels()
+        if secondary is not None and "unavailable" not in ref_cuda:
+            secondary["per_query_S8192"]["reference_cuda_kernels"] = reference_cuda_kernels(
+                ("--per-query", "--seq-len", "8192", "--window", "1024"))
 
     # ---- context parallelism over all ranks for one long sequence (multi-GPU runs only) ----
     cp = None
