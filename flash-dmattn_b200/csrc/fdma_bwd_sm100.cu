@@ -89,7 +89,9 @@ struct SmemB {
   static constexpr int kLdOff = kActOff + kMaxAct;                 // per stage: 64 x LSE*log2e, 64 x D (fp32)
   static constexpr int kLdBytes = 2 * kBM * 4;
   static constexpr int kDqOff = kLdOff + kQStages * kLdBytes;      // [32 q][128 d] fp32 staging tile of the dQ writer
-  static constexpr int kRedOff = kDqOff + 32 * kD * 4;
+  static constexpr int kTrOff = kDqOff + 32 * kD * 4;              // per softmax warp: 1 KB transposition scratch
+  static constexpr int kTrBytes = 8 * 1024;
+  static constexpr int kRedOff = kTrOff + kTrBytes;
   static constexpr int kBarOff = kRedOff + kBN * 4;
   static constexpr int kNumBars = 1 + 2 * kQStages + 2 + 2 + 1 + 1 + 1 + 1;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
@@ -523,6 +525,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
     const int half = (warp - 4) >> 2;
     const int krow = (warp & 3) * 32 + lane;  // key inside the tile == TMEM lane
     const int key = n * kBN + krow;
+    unsigned char* s_tr = smem + L::kTrOff + (warp - 4) * 1024;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const bool key_ok = key < Sk;
     // value compared with q + coff in the causal test: the key's position
@@ -536,6 +539,38 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
     for (int j = 0; j < 32; ++j) dacc[j] = 0.f;
     const bool direct_group = mode == kDbDirect && p.dbias_h != p.h;  // one dbias head per kv head
     uint16_t* dbias16 = reinterpret_cast<uint16_t*>(p.dbias);
+    // Direct mode: a warp's 32 queries x 32 keys of dBias leave through its transposition scratch as 16-byte row
+    // pieces (64 bytes per row) when the tensor allows it; `vals` null stores zeros.
+    const bool db_vec = mode == kDbDirect && (reinterpret_cast<uintptr_t>(p.dbias) & 15u) == 0 &&
+                        ((p.dbias_batch_stride | p.dbias_head_stride | p.dbias_row_stride) & 7) == 0 &&
+                        n * kBN + (warp & 3) * 32 + 32 <= p.dbias_keys;
+    auto store_dbias = [&](uint16_t* dst_key, int q_first, const float* vals) {  // dst_key: (query 0, this key)
+      if (db_vec) {
+        uint16_t* tr16 = reinterpret_cast<uint16_t*>(s_tr);
+        const uint4* tr4 = reinterpret_cast<const uint4*>(s_tr);
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          if (vals) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) tr16[j * 32 + lane] = float_to_raw16<kBf16>(vals[r * 16 + j]);
+            __syncwarp();
+          }
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            const int row = q_first + r * 16 + t * 8 + (lane >> 2);
+            if (row < Sq)
+              *reinterpret_cast<uint4*>(dst_key - lane + static_cast<int64_t>(row) * p.dbias_row_stride + (lane & 3) * 8) =
+                  vals ? tr4[lane + 32 * t] : make_uint4(0, 0, 0, 0);
+          }
+          if (vals) __syncwarp();
+        }
+      } else if (key < p.dbias_keys) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (q_first + j < Sq)
+            dst_key[static_cast<int64_t>(q_first + j) * p.dbias_row_stride] = vals ? float_to_raw16<kBf16>(vals[j]) : 0;
+      }
+    };
     // Row-broadcast bias / mask that do not depend on the query head: one value per thread for the whole CTA.
     const bool group_inv = G == 1 || ((!p.bias || p.h_bias != p.h) && (!p.mask || p.h_mask != p.h));
     const bool hoist = kBcast && group_inv;
@@ -567,11 +602,8 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         const int h = hk * G + g;
         const bool active = m >= m_start && s_act[(act_g > 1 ? g : 0) * MT + (m >> 1)] != 0;
         if (!active) {
-          if (mode == kDbDirect && !direct_group && key < p.dbias_keys) {
-            uint16_t* dst = dbias16 + b * p.dbias_batch_stride + h * p.dbias_head_stride + key;
-            for (int j = 0; j < 32; ++j)
-              if (q0 + j < Sq) dst[static_cast<int64_t>(q0 + j) * p.dbias_row_stride] = 0;
-          }
+          if (mode == kDbDirect && !direct_group)
+            store_dbias(dbias16 + b * p.dbias_batch_stride + h * p.dbias_head_stride + key, q0, nullptr);
           continue;
         }
         if (kTeams && (i & 1) != half) {  // the other team's step
@@ -597,29 +629,61 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         } else {
           if (!(group_inv && bias2_loaded)) {
           bias2_loaded = true;
-          const int hm = hm_of(h), hb = hb_of(h);
-          const uint16_t* bcol = p.bias ? reinterpret_cast<const uint16_t*>(p.bias) + b * p.bias_batch_stride +
-                                              hb * p.bias_head_stride + key
-                                        : nullptr;
-          const uint8_t* mcol = p.mask ? p.mask + b * p.mask_batch_stride + hm * p.mask_head_stride + key : nullptr;
-          if (g == 0 && m + 1 < M64) {
-            // next query tile's bias / mask bytes of this warp's 32 keys: lane j asks L2 for row j
-            const int64_t qn = min((m + 1) * kBM + half * 32 + lane, Sq - 1);
-            const int wkey = min(n * kBN + (warp & 3) * 32, Sk - 1) - key;  // warp's first key, relative to this lane's
-            if (bcol) prefetch_l2(bcol + wkey + qn * p.bias_row_stride);
-            if (mcol) prefetch_l2(mcol + wkey + qn * p.mask_row_stride);
-          }
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            float two[2];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const int qq = min(q0 + 2 * j + e, Sq - 1);
-              const float bj = bcol ? raw16_to_float<kBf16>(bcol[static_cast<int64_t>(qq) * p.bias_row_stride]) * kLog2e : 0.f;
-              const bool kp = key_ok && (!mcol || mcol[static_cast<int64_t>(qq) * p.mask_row_stride] != 0);
-              two[e] = kp ? bj : -CUDART_INF_F;
+          {
+            const int hm = hm_of(h), hb = hb_of(h);
+            const uint16_t* bcol = p.bias ? reinterpret_cast<const uint16_t*>(p.bias) + b * p.bias_batch_stride +
+                                                hb * p.bias_head_stride + key
+                                          : nullptr;
+            const uint8_t* mcol = p.mask ? p.mask + b * p.mask_batch_stride + hm * p.mask_head_stride + key : nullptr;
+            const int wkey = -lane;  // the warp's first key, relative to this lane's
+            if (g == 0 && m + 1 < M64) {
+              // next query tile's bias / mask sectors of this warp's 32 keys: lane j asks L2 for row j
+              const int64_t qn = min((m + 1) * kBM + half * 32 + lane, Sq - 1);
+              if (bcol) {
+                prefetch_l2(bcol + wkey + qn * p.bias_row_stride);
+                prefetch_l2(bcol + wkey + qn * p.bias_row_stride + 16);
+              }
+              if (mcol) prefetch_l2(mcol + wkey + qn * p.mask_row_stride);
             }
-            bias2[j] = make_float2(two[0], two[1]);
+            // The thread wants one column (its key) of 32 query rows, the tensors are contiguous along keys: the
+            // warp fetches its 32 x 32 block with 16-byte loads along keys (6 per lane) and turns it through its
+            // 1 KB of shared memory -- 16 bias rows, 16 bias rows, 32 mask rows -- instead of 64 scalar loads per
+            // thread.
+            uint4 vb[4], vm[2];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              const int qq = min(q0 + (t >> 1) * 16 + (t & 1) * 8 + (lane >> 2), Sq - 1);
+              vb[t] = bcol ? ld_nc_v4(bcol + wkey + static_cast<int64_t>(qq) * p.bias_row_stride + (lane & 3) * 8)
+                           : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+              const int qq = min(q0 + t * 16 + (lane >> 1), Sq - 1);
+              vm[t] = mcol ? ld_nc_v4(mcol + wkey + static_cast<int64_t>(qq) * p.mask_row_stride + (lane & 1) * 16)
+                           : make_uint4(0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u);
+            }
+            uint4* tr4 = reinterpret_cast<uint4*>(s_tr);
+            const uint16_t* tr16 = reinterpret_cast<const uint16_t*>(s_tr);
+            float braw[32];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+              tr4[lane] = vb[2 * r];
+              tr4[lane + 32] = vb[2 * r + 1];
+              __syncwarp();
+#pragma unroll
+              for (int j = 0; j < 16; ++j) braw[r * 16 + j] = raw16_to_float<kBf16>(tr16[j * 32 + lane]) * kLog2e;
+              __syncwarp();
+            }
+            tr4[lane] = vm[0];
+            tr4[lane + 32] = vm[1];
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const bool k0 = key_ok && s_tr[(2 * j) * 32 + lane] != 0;
+              const bool k1 = key_ok && s_tr[(2 * j + 1) * 32 + lane] != 0;
+              bias2[j] = make_float2(k0 ? braw[2 * j] : -CUDART_INF_F, k1 ? braw[2 * j + 1] : -CUDART_INF_F);
+            }
+            __syncwarp();
           }
           if (causal && static_cast<int64_t>(ckey_wmax) > static_cast<int64_t>(q0) + coff) {
 #pragma unroll
@@ -719,11 +783,8 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
             if (direct_group) {
 #pragma unroll
               for (int j = 0; j < 32; ++j) dacc[j] += pv[j];
-            } else if (key < p.dbias_keys) {
-              uint16_t* dst = dbias16 + b * p.dbias_batch_stride + h * p.dbias_head_stride + key;
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (q0s + j < Sq) dst[static_cast<int64_t>(q0s + j) * p.dbias_row_stride] = float_to_raw16<kBf16>(pv[j]);
+            } else {
+              store_dbias(dbias16 + b * p.dbias_batch_stride + h * p.dbias_head_stride + key, q0s, pv);
             }
           } else if (mode == kDbAtomic && key_ok && p.dbias_rows != 1) {
             const int b2 = p.dbias_b == 1 ? 0 : b;
@@ -759,14 +820,11 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
         if (lane == 0) mbar_arrive(bar_pds + (i & 1));
         ++i;
       }
-      if (direct_group && ok && key < p.dbias_keys) {  // one store per (query, key) after the whole head group
-        uint16_t* dst = dbias16 + b * p.dbias_batch_stride + hk * p.dbias_head_stride + key;
+      if (direct_group && ok) {  // one store per (query, key) after the whole head group
+        store_dbias(dbias16 + b * p.dbias_batch_stride + hk * p.dbias_head_stride + key, q0,
+                    group_touched ? dacc : nullptr);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          if (q0 + j < Sq)
-            dst[static_cast<int64_t>(q0 + j) * p.dbias_row_stride] = float_to_raw16<kBf16>(group_touched ? dacc[j] : 0.f);
-          dacc[j] = 0.f;
-        }
+        for (int j = 0; j < 32; ++j) dacc[j] = 0.f;
       }
     }
     FDMA_PROF_END(16, tid == 128);

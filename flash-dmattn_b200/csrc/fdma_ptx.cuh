@@ -329,6 +329,9 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// 16-byte read-only load (data that no thread of the grid writes)
+__device__ __forceinline__ uint4 ld_nc_v4(const void* ptr) { return __ldg(reinterpret_cast<const uint4*>(ptr)); }
+
 __device__ __forceinline__ void prefetch_l2(const void* ptr) {
   asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr));
 }
