@@ -561,6 +561,11 @@ __global__ void __launch_bounds__(Smem<D>::kThreads, 1) fwd_kernel(const __grid_
         brow = reinterpret_cast<const uint16_t*>(p.bias) + b * p.bias_batch_stride + w.hb * p.bias_head_stride +
                qclamp * p.bias_row_stride;
     }
+    // 32-byte loads of the row pieces where the tensors' alignment allows them
+    const bool wide_m = ((reinterpret_cast<uintptr_t>(p.mask) | static_cast<uintptr_t>(p.mask_batch_stride) |
+                          static_cast<uintptr_t>(p.mask_head_stride) | static_cast<uintptr_t>(p.mask_row_stride)) & 31) == 0;
+    const bool wide_b = (reinterpret_cast<uintptr_t>(p.bias) & 31) == 0 &&
+                        ((p.bias_batch_stride | p.bias_head_stride | p.bias_row_stride) & 15) == 0;
     float m_ref = -CUDART_INF_F, l = 0.f;
     uint32_t sitem = 0;  // S tiles of this item processed by this warpgroup
     // The two warpgroups share the transcendental unit; running their exp2 phases at the same time doubles the
@@ -616,30 +621,48 @@ __global__ void __launch_bounds__(Smem<D>::kThreads, 1) fwd_kernel(const __grid_
         } else {
           const float2 l2e2 = make_float2(kLog2e, kLog2e);
 #pragma unroll
-          for (int c = 0; c < kBN / 16; ++c) {
-            uint4 mb = make_uint4(0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u);
-            if (mrow) mb = *reinterpret_cast<const uint4*>(mrow + kbase + c * 16);
-            uint4 b0 = make_uint4(0, 0, 0, 0), b1 = make_uint4(0, 0, 0, 0);
-            if (brow) {
-              b0 = *reinterpret_cast<const uint4*>(brow + kbase + c * 16);
-              b1 = *reinterpret_cast<const uint4*>(brow + kbase + c * 16 + 8);
-            }
-            const uint32_t mw[4] = {mb.x, mb.y, mb.z, mb.w};
-            const uint32_t bw[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {  // pair i of this 16-key chunk
-              float2 bf;
-              if (kBf16) {
-                bf = make_float2(__uint_as_float(bw[i] << 16), __uint_as_float(bw[i] & 0xFFFF0000u));
+          for (int c2 = 0; c2 < kBN / 32; ++c2) {   // 32 keys: one 32-byte piece of the mask row, two of the bias row
+            uint32_t mw[8] = {0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u,
+                              0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u};
+            if (mrow) {
+              if (wide_m) {
+                ld_nc_v8(mrow + kbase + c2 * 32, mw);
               } else {
-                const __half2 hh = *reinterpret_cast<const __half2*>(&bw[i]);
-                bf = make_float2(__low2float(hh), __high2float(hh));
+                const uint4 m0 = *reinterpret_cast<const uint4*>(mrow + kbase + c2 * 32);
+                const uint4 m1 = *reinterpret_cast<const uint4*>(mrow + kbase + c2 * 32 + 16);
+                mw[0] = m0.x; mw[1] = m0.y; mw[2] = m0.z; mw[3] = m0.w;
+                mw[4] = m1.x; mw[5] = m1.y; mw[6] = m1.z; mw[7] = m1.w;
               }
-              float2 add = __fmul2_rn(bf, l2e2);
-              const uint32_t mpair = mw[i >> 1] >> ((i & 1) * 16);
-              if ((mpair & 0xFFu) == 0) add.x = -CUDART_INF_F;
-              if ((mpair & 0xFF00u) == 0) add.y = -CUDART_INF_F;
-              s2[c * 8 + i] = __ffma2_rn(s2[c * 8 + i], sc2, add);
+            }
+#pragma unroll
+            for (int cc = 0; cc < 2; ++cc) {
+              const int c = c2 * 2 + cc;  // 16-key chunk
+              uint32_t bw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+              if (brow) {
+                if (wide_b) {
+                  ld_nc_v8(brow + kbase + c * 16, bw);
+                } else {
+                  const uint4 b0 = *reinterpret_cast<const uint4*>(brow + kbase + c * 16);
+                  const uint4 b1 = *reinterpret_cast<const uint4*>(brow + kbase + c * 16 + 8);
+                  bw[0] = b0.x; bw[1] = b0.y; bw[2] = b0.z; bw[3] = b0.w;
+                  bw[4] = b1.x; bw[5] = b1.y; bw[6] = b1.z; bw[7] = b1.w;
+                }
+              }
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {  // pair i of this 16-key chunk
+                float2 bf;
+                if (kBf16) {
+                  bf = make_float2(__uint_as_float(bw[i] << 16), __uint_as_float(bw[i] & 0xFFFF0000u));
+                } else {
+                  const __half2 hh = *reinterpret_cast<const __half2*>(&bw[i]);
+                  bf = make_float2(__low2float(hh), __high2float(hh));
+                }
+                float2 add = __fmul2_rn(bf, l2e2);
+                const uint32_t mpair = mw[cc * 4 + (i >> 1)] >> ((i & 1) * 16);
+                if ((mpair & 0xFFu) == 0) add.x = -CUDART_INF_F;
+                if ((mpair & 0xFF00u) == 0) add.y = -CUDART_INF_F;
+                s2[c * 8 + i] = __ffma2_rn(s2[c * 8 + i], sc2, add);
+              }
             }
           }
         }

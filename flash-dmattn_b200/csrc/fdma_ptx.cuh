@@ -332,6 +332,14 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // 16-byte read-only load (data that no thread of the grid writes)
 __device__ __forceinline__ uint4 ld_nc_v4(const void* ptr) { return __ldg(reinterpret_cast<const uint4*>(ptr)); }
 
+// 32-byte read-only load (sm_100: 256-bit global accesses); `ptr` must be 32-byte aligned. One request per sector
+// where two 16-byte loads would make two.
+__device__ __forceinline__ void ld_nc_v8(const void* ptr, uint32_t (&r)[8]) {
+  asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "l"(ptr));
+}
+
 __device__ __forceinline__ void prefetch_l2(const void* ptr) {
   asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr));
 }
