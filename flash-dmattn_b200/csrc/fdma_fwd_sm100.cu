@@ -581,24 +581,14 @@ __global__ void __launch_bounds__(Smem<D>::kThreads, 1) fwd_kernel(const __grid_
         if (!ok) break;
       }
       if (fl & (1 << t)) {
-        ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(1, mbar_wait(bar_s_full + t, scnt & 1, ctl, kWaitS)));
-        if (!ok) break;
-        tc_fence_after_sync();
-        // Scores are kept as 64 register pairs so that the scale/bias FMA, the max-subtraction and the row sum run
-        // as packed fp32x2 instructions (half the issue slots of scalar code).
-        float2 s2[kBN / 2];
-        {
-          uint32_t su[kBN];
-#pragma unroll
-          for (int c = 0; c < 4; ++c) tmem_ld_x32(s_taddr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&su[c * 32]));
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < kBN / 2; ++i) s2[i] = make_float2(__uint_as_float(su[2 * i]), __uint_as_float(su[2 * i + 1]));
-        }
         const int kbase = j * kBN;
         const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
+        // Per-query bias / mask: this row's 128 + 256 bytes of the tile are requested BEFORE the wait for the score
+        // tile, so the load latency overlaps the wait; the scores then leave TMEM 32 columns at a time and take the
+        // place of the addend registers they consume.
+        uint32_t bw[kBcast ? 1 : 8][8], mw[kBcast ? 1 : 4][8];
         if (!kBcast) {
-          // this row's mask and bias bytes of the next tile it will process: into L2 while this tile is worked on
+          // ... and of the next tile this row will process: into L2 while this tile is worked on
           int jn = j + 1;
           while (jn < nT && !(s_flags[jn] & (1 << t))) ++jn;
           if (jn < nT) {
@@ -608,60 +598,81 @@ __global__ void __launch_bounds__(Smem<D>::kThreads, 1) fwd_kernel(const __grid_
               prefetch_l2(brow + jn * kBN + 64);
             }
           }
+#pragma unroll
+          for (int c2 = 0; c2 < 4; ++c2) {
+            if (!mrow) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) mw[c2][i] = 0x01010101u;
+            } else if (wide_m) {
+              ld_nc_v8(mrow + kbase + c2 * 32, mw[c2]);
+            } else {
+              const uint4 m0 = *reinterpret_cast<const uint4*>(mrow + kbase + c2 * 32);
+              const uint4 m1 = *reinterpret_cast<const uint4*>(mrow + kbase + c2 * 32 + 16);
+              mw[c2][0] = m0.x; mw[c2][1] = m0.y; mw[c2][2] = m0.z; mw[c2][3] = m0.w;
+              mw[c2][4] = m1.x; mw[c2][5] = m1.y; mw[c2][6] = m1.z; mw[c2][7] = m1.w;
+            }
+          }
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            if (!brow) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) bw[c][i] = 0u;
+            } else if (wide_b) {
+              ld_nc_v8(brow + kbase + c * 16, bw[c]);
+            } else {
+              const uint4 b0 = *reinterpret_cast<const uint4*>(brow + kbase + c * 16);
+              const uint4 b1 = *reinterpret_cast<const uint4*>(brow + kbase + c * 16 + 8);
+              bw[c][0] = b0.x; bw[c][1] = b0.y; bw[c][2] = b0.z; bw[c][3] = b0.w;
+              bw[c][4] = b1.x; bw[c][5] = b1.y; bw[c][6] = b1.z; bw[c][7] = b1.w;
+            }
+          }
         }
-        // scores in log2 units with bias and mask folded in
+        ok = __all_sync(0xffffffffu, FDMA_PROF_WAIT(1, mbar_wait(bar_s_full + t, scnt & 1, ctl, kWaitS)));
+        if (!ok) break;
+        tc_fence_after_sync();
+        // Scores are kept as 64 register pairs so that the scale/bias FMA, the max-subtraction and the row sum run
+        // as packed fp32x2 instructions (half the issue slots of scalar code). Scores in log2 units with bias and
+        // mask folded in.
+        float2 s2[kBN / 2];
         if (kBcast) {
+          uint32_t su[kBN];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) tmem_ld_x32(s_taddr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&su[c * 32]));
+          tmem_wait_ld();
           const float4* bm4 = reinterpret_cast<const float4*>(s_bm + slot * kBN);
 #pragma unroll
           for (int i = 0; i < kBN / 4; ++i) {
             const float4 a4 = bm4[i];
-            s2[2 * i] = __ffma2_rn(s2[2 * i], sc2, make_float2(a4.x, a4.y));
-            s2[2 * i + 1] = __ffma2_rn(s2[2 * i + 1], sc2, make_float2(a4.z, a4.w));
+            s2[2 * i] = __ffma2_rn(make_float2(__uint_as_float(su[4 * i]), __uint_as_float(su[4 * i + 1])), sc2,
+                                   make_float2(a4.x, a4.y));
+            s2[2 * i + 1] = __ffma2_rn(make_float2(__uint_as_float(su[4 * i + 2]), __uint_as_float(su[4 * i + 3])), sc2,
+                                       make_float2(a4.z, a4.w));
           }
         } else {
           const float2 l2e2 = make_float2(kLog2e, kLog2e);
 #pragma unroll
-          for (int c2 = 0; c2 < kBN / 32; ++c2) {   // 32 keys: one 32-byte piece of the mask row, two of the bias row
-            uint32_t mw[8] = {0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u,
-                              0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u};
-            if (mrow) {
-              if (wide_m) {
-                ld_nc_v8(mrow + kbase + c2 * 32, mw);
-              } else {
-                const uint4 m0 = *reinterpret_cast<const uint4*>(mrow + kbase + c2 * 32);
-                const uint4 m1 = *reinterpret_cast<const uint4*>(mrow + kbase + c2 * 32 + 16);
-                mw[0] = m0.x; mw[1] = m0.y; mw[2] = m0.z; mw[3] = m0.w;
-                mw[4] = m1.x; mw[5] = m1.y; mw[6] = m1.z; mw[7] = m1.w;
-              }
-            }
+          for (int c2 = 0; c2 < kBN / 32; ++c2) {
+            uint32_t su[32];
+            tmem_ld_x32(s_taddr + c2 * 32, su);
+            tmem_wait_ld();
 #pragma unroll
             for (int cc = 0; cc < 2; ++cc) {
               const int c = c2 * 2 + cc;  // 16-key chunk
-              uint32_t bw[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-              if (brow) {
-                if (wide_b) {
-                  ld_nc_v8(brow + kbase + c * 16, bw);
-                } else {
-                  const uint4 b0 = *reinterpret_cast<const uint4*>(brow + kbase + c * 16);
-                  const uint4 b1 = *reinterpret_cast<const uint4*>(brow + kbase + c * 16 + 8);
-                  bw[0] = b0.x; bw[1] = b0.y; bw[2] = b0.z; bw[3] = b0.w;
-                  bw[4] = b1.x; bw[5] = b1.y; bw[6] = b1.z; bw[7] = b1.w;
-                }
-              }
 #pragma unroll
               for (int i = 0; i < 8; ++i) {  // pair i of this 16-key chunk
                 float2 bf;
                 if (kBf16) {
-                  bf = make_float2(__uint_as_float(bw[i] << 16), __uint_as_float(bw[i] & 0xFFFF0000u));
+                  bf = make_float2(__uint_as_float(bw[c][i] << 16), __uint_as_float(bw[c][i] & 0xFFFF0000u));
                 } else {
-                  const __half2 hh = *reinterpret_cast<const __half2*>(&bw[i]);
+                  const __half2 hh = *reinterpret_cast<const __half2*>(&bw[c][i]);
                   bf = make_float2(__low2float(hh), __high2float(hh));
                 }
                 float2 add = __fmul2_rn(bf, l2e2);
-                const uint32_t mpair = mw[cc * 4 + (i >> 1)] >> ((i & 1) * 16);
+                const uint32_t mpair = mw[c2][cc * 4 + (i >> 1)] >> ((i & 1) * 16);
                 if ((mpair & 0xFFu) == 0) add.x = -CUDART_INF_F;
                 if ((mpair & 0xFF00u) == 0) add.y = -CUDART_INF_F;
-                s2[c * 8 + i] = __ffma2_rn(s2[c * 8 + i], sc2, add);
+                s2[c * 8 + i] = __ffma2_rn(make_float2(__uint_as_float(su[cc * 16 + 2 * i]),
+                                                       __uint_as_float(su[cc * 16 + 2 * i + 1])), sc2, add);
               }
             }
           }
