@@ -788,6 +788,8 @@ __global__ void __launch_bounds__(Smem<D>::kThreads, 1) fwd_kernel(const __grid_
     tc_fence_after_sync();
     {
       const bool in_range = qrow < Sq;  // TMEM loads below are warp-collective: every lane runs them
+      const bool wide_o = (reinterpret_cast<uintptr_t>(p.out) & 31) == 0 &&
+                          ((p.o_batch_stride | p.o_row_stride | p.o_head_stride) & 15) == 0;
       // m_ref stays -inf iff every score of the row was masked (l can then hold 2^-125 terms of exp2_poly2)
       const bool alive = sitem > 0 && l > 0.f && m_ref != -CUDART_INF_F;
       const float inv = alive ? 1.f / l : 0.f;
@@ -809,13 +811,18 @@ __global__ void __launch_bounds__(Smem<D>::kThreads, 1) fwd_kernel(const __grid_
           }
           if (in_range) {
 #pragma unroll
-            for (int v4 = 0; v4 < 4; ++v4) {
-              uint4 o;
-              o.x = pack_16x2<kBf16>(__uint_as_float(r[v4 * 8 + 0]) * inv, __uint_as_float(r[v4 * 8 + 1]) * inv);
-              o.y = pack_16x2<kBf16>(__uint_as_float(r[v4 * 8 + 2]) * inv, __uint_as_float(r[v4 * 8 + 3]) * inv);
-              o.z = pack_16x2<kBf16>(__uint_as_float(r[v4 * 8 + 4]) * inv, __uint_as_float(r[v4 * 8 + 5]) * inv);
-              o.w = pack_16x2<kBf16>(__uint_as_float(r[v4 * 8 + 6]) * inv, __uint_as_float(r[v4 * 8 + 7]) * inv);
-              *reinterpret_cast<uint4*>(orow + c * 64 + v4 * 16) = o;
+            for (int v8 = 0; v8 < 2; ++v8) {   // 16 outputs = 32 bytes per store where the alignment allows
+              uint32_t o[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                o[e] = pack_16x2<kBf16>(__uint_as_float(r[v8 * 16 + 2 * e]) * inv,
+                                        __uint_as_float(r[v8 * 16 + 2 * e + 1]) * inv);
+              if (wide_o) {
+                st_v8(orow + c * 64 + v8 * 32, o);
+              } else {
+                *reinterpret_cast<uint4*>(orow + c * 64 + v8 * 32) = make_uint4(o[0], o[1], o[2], o[3]);
+                *reinterpret_cast<uint4*>(orow + c * 64 + v8 * 32 + 16) = make_uint4(o[4], o[5], o[6], o[7]);
+              }
             }
           }
         }

@@ -340,6 +340,14 @@ __device__ __forceinline__ void ld_nc_v8(const void* ptr, uint32_t (&r)[8]) {
                : "l"(ptr));
 }
 
+// 32-byte store; `ptr` must be 32-byte aligned.
+__device__ __forceinline__ void st_v8(void* ptr, const uint32_t (&r)[8]) {
+  asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+               :
+               : "l"(ptr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+
 __device__ __forceinline__ void prefetch_l2(const void* ptr) {
   asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr));
 }
