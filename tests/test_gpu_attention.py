@@ -4,7 +4,7 @@ oracle on identical seeded inputs.
 Tolerances (bf16/fp16 inputs, fp32 oracle): max-abs <= 2e-2 and mean-abs <= 2e-3. dK, dV and dBias are sums over
 many queries and reach magnitudes where ONE bf16 rounding of the exact result already exceeds the bound
 (`floor` = |ref - bf16(ref)|, the error of a perfect kernel that returns bf16); for those three the bounds are
-max-abs <= 2e-2 + 1.5 * (half an ulp at the tensor's largest magnitude) and mean-abs <= 2e-3 + 1.5 * floor_mean
+max-abs <= 2e-2 + one ulp at the tensor's largest magnitude and mean-abs <= 2e-3 + 2 * floor_mean
 (oracle.within_tolerance, with the measured ratios that back the factor). A failure
 message carries every figure: max-abs, mean-abs, both floors and the largest error in ulps of the reference."""
 import itertools

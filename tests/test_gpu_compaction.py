@@ -3,7 +3,7 @@ key-position causal test of fdma_fwd / fdma_bwd) against the fp32 oracle run on 
 and bit-exact checks of the index / gather / scatter kernels against torch indexing.
 
 Tolerances as in test_gpu_attention.py (oracle.within_tolerance): max-abs <= 2e-2, mean-abs <= 2e-3; for dK / dV /
-dBias the max bound grows by 1.5 x half an ulp at the tensor's largest magnitude, the mean bound by 1.5 x the mean bf16
+dBias the max bound grows by one ulp at the tensor's largest magnitude, the mean bound by 2 x the mean bf16
 rounding floor."""
 import pytest
 import torch

@@ -10,7 +10,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, causal, route, d, scheme="ring"):
+def _worker(rank, world, port, causal, route, d, scheme="ring", per_query_head=False):
     import torch.distributed as dist
 
     from flash_sparse_attn import flash_sparse_attn_interface as iface
@@ -27,7 +27,8 @@ def _worker(rank, world, port, causal, route, d, scheme="ring"):
     try:
         B, H, Hk = 1, 4, 1
         S = 2 * world * 256
-        q, k, v, bias, dout = oracle.make_inputs(B, S, S, H, Hk, d, (B, Hk, 1, S), seed=5, dtype=torch.bfloat16)
+        q, k, v, bias, dout = oracle.make_inputs(B, S, S, H, Hk, d, (B, H if per_query_head else Hk, 1, S), seed=5,
+                                                 dtype=torch.bfloat16)
         mask = oracle.create_mask(bias, None, B, S, S, S // 4, torch.finfo(torch.bfloat16).min)
         want = oracle.attention_forward_backward(q, k, v, mask, bias, dout, None, causal)
         loc = lambda t, dim: ring.zigzag_split(t, dim, rank, world).contiguous().to(dev)
@@ -69,6 +70,19 @@ def test_ring_two_gpus(causal, route, d):
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     mp.spawn(_worker, args=(2, port, causal, route, d), nprocs=2, join=True)
+
+
+def test_ring_two_gpus_mask_per_query_head():
+    """A mask / bias with one row per QUERY head cannot share gathered K/V inside a kv group: the ring must take the
+    full-range kernels for it even with gathering enabled, and still match the oracle."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_worker, args=(2, port, True, "auto", 128, "ring", True), nprocs=2, join=True)
 
 
 @pytest.mark.parametrize("causal,d", [(True, 128), (False, 128), (True, 256)])
