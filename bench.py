@@ -575,24 +575,27 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     d2h = sum(t.numel() * t.element_size() for t in host_out.values())
 
     # Three streams: uploads, compute, downloads. Step i's upload overlaps step i-1's compute and download (PCIe is
-    # full duplex); device input buffers and host output buffers are double-buffered, and every tensor a side stream
-    # still reads is kept referenced until that stream's event has completed.
+    # full duplex); device input buffers and host output buffers come in THREE sets, so that the host only has to wait
+    # for the download of step i-3 before it queues the upload of step i (with two sets the upload stream idles for a
+    # compute time per step, waiting for the host); every tensor a side stream still reads is kept referenced until
+    # that stream's event has completed.
+    NB = 3
     s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
     in_names = ("q", "k", "v", "bias", "dout")
-    dev_in = [{n: torch.empty_like(host_in[n], device=dev) for n in in_names} for _ in range(2)]
-    host_out2 = [host_out, {n: torch.empty_like(t).pin_memory() for n, t in host_out.items()}]
-    ev_in = [torch.cuda.Event() for _ in range(2)]
-    ev_comp = [torch.cuda.Event() for _ in range(2)]
-    ev_out = [torch.cuda.Event() for _ in range(2)]
-    live = [None, None]
+    dev_in = [{n: torch.empty_like(host_in[n], device=dev) for n in in_names} for _ in range(NB)]
+    host_out2 = [host_out] + [{n: torch.empty_like(t).pin_memory() for n, t in host_out.items()} for _ in range(NB - 1)]
+    ev_in = [torch.cuda.Event() for _ in range(NB)]
+    ev_comp = [torch.cuda.Event() for _ in range(NB)]
+    ev_out = [torch.cuda.Event() for _ in range(NB)]
+    live = [None] * NB
 
     def e2e_step(i: int):
-        sl = i & 1
-        if i >= 2:
-            ev_out[sl].synchronize()      # step i-2 has left the device: its buffers may be reused
+        sl = i % NB
+        if i >= NB:
+            ev_out[sl].synchronize()      # step i-NB has left the device: its buffers may be reused
             live[sl] = None
         with torch.cuda.stream(s_in):
-            if i >= 2:
+            if i >= NB:
                 s_in.wait_event(ev_comp[sl])
             for n in in_names:
                 dev_in[sl][n].copy_(host_in[n], non_blocking=True)
@@ -613,22 +616,24 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 
     e2e_ms = copy_ms = float("nan")
     if not args.no_e2e:
-        e2e_steps = max(2, min(args.steps, 6))
-        e2e_step(0)
-        e2e_step(1)
+        # enough steps that filling and draining the three-stage pipeline (one upload, one compute and one download
+        # that nothing overlaps) weighs little against the steady state
+        e2e_steps = max(NB + 1, min(2 * args.steps, 30))
+        for i in range(NB):
+            e2e_step(i)
         torch.cuda.synchronize(dev)
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         s_in.wait_event(e0)
         for i in range(e2e_steps):
-            e2e_step(2 + i)
-        stream.wait_event(ev_out[0])
-        stream.wait_event(ev_out[1])
+            e2e_step(NB + i)
+        for ev in ev_out:
+            stream.wait_event(ev)
         e1.record(stream)
         barrier()
         e2e_ms = e0.elapsed_time(e1) / e2e_steps
-        live[0] = live[1] = None
+        live = [None] * NB
         # The ceiling the host sets: the same bytes, up and down at once on two streams, with no compute at all
         # (every rank at the same time, as in the run above).
         res0 = {"out": out, "dq": dq, "dk": dk, "dv": dv, "dbias": dbias}
@@ -640,10 +645,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         for i in range(e2e_steps):
             with torch.cuda.stream(s_in):
                 for n in in_names:
-                    dev_in[i & 1][n].copy_(host_in[n], non_blocking=True)
+                    dev_in[i % NB][n].copy_(host_in[n], non_blocking=True)
             with torch.cuda.stream(s_out):
                 for n, t in res0.items():
-                    host_out2[i & 1][n].copy_(t, non_blocking=True)
+                    host_out2[i % NB][n].copy_(t, non_blocking=True)
         fin_in, fin_out = torch.cuda.Event(), torch.cuda.Event()
         fin_in.record(s_in)
         fin_out.record(s_out)
