@@ -96,11 +96,20 @@ int encode_tmap_4d(void* out_map, const void* base, int elem_bytes, const uint64
   cuuint64_t gstr[3] = {strides_bytes[0], strides_bytes[1], strides_bytes[2]};
   cuuint32_t bx[4] = {box[0], box[1], box[2], box[3]};
   cuuint32_t es[4] = {1, 1, 1, 1};
-  CUresult r = g_encode(static_cast<CUtensorMap*>(out_map),
-                        elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4,
-                        const_cast<void*>(base), gdims, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  auto encode = [&]() {
+    return g_encode(static_cast<CUtensorMap*>(out_map),
+                    elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4,
+                    const_cast<void*>(base), gdims, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  };
+  CUresult r = encode();
+  if (r == CUDA_ERROR_INVALID_CONTEXT) {
+    // The encode call is the driver API and wants a context current on THIS thread. A thread that has only been
+    // handed cached device memory so far (an autograd worker running its first backward) has none: a runtime call
+    // binds the device's primary context, then the encode goes through.
+    (void)cudaFree(nullptr);
+    r = encode();
+  }
   return r == CUDA_SUCCESS ? 0 : FDMA_ERR_DRIVER;
 }
 

@@ -72,6 +72,35 @@ def test_forward_on_two_devices_in_one_process():
         check("dk", kl.grad.cpu(), ref[3], torch.bfloat16, reduced=True)
 
 
+def test_first_backward_of_a_fresh_process(dev):
+    """The backward runs on an autograd worker thread. When everything that thread needs comes out of the allocator's
+    cache, its first CUDA call of any kind is the library's tensor-map encode, a driver-API call that wants a context
+    current on the calling thread: the library has to bind one itself. Needs a process of its own -- in this one
+    earlier tests have long since made the worker thread allocate."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = (
+        "import torch\n"
+        "from flash_sparse_attn import flash_sparse_attn_func\n"
+        "g = torch.Generator(device='cuda').manual_seed(0)\n"
+        "r = lambda *s: torch.randn(s, generator=g, device='cuda', dtype=torch.float32).to(torch.bfloat16)\n"
+        "for d in (128, 256):\n"
+        "    q, k, v, bias, dout = r(1, 256, 2, d), r(1, 256, 1, d), r(1, 256, 1, d), r(1, 1, 1, 256), r(1, 256, 2, d)\n"
+        "    q.requires_grad_(True)\n"
+        "    out = flash_sparse_attn_func(q, k, v, attn_bias=bias, is_causal=True)\n"
+        "    out.backward(dout)\n"
+        "    torch.cuda.synchronize()\n"
+        "    assert torch.isfinite(q.grad.float()).all()\n"
+        "print('backward ok')\n")
+    env = dict(os.environ, PYTHONPATH=os.pathsep.join([root, os.path.join(root, "flash-dmattn_b200"),
+                                                        os.environ.get("PYTHONPATH", "")]))
+    res = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0 and "backward ok" in res.stdout, res.stderr[-2000:]
+
+
 @pytest.mark.parametrize("d", [128, 256])
 def test_deterministic_backward_propagates_non_finite(dev, d):
     """deterministic=True sums dQ in 64-bit fixed point, which cannot hold Inf or NaN; a row whose dOut carries an
