@@ -125,6 +125,34 @@ def test_deterministic_backward_propagates_non_finite(dev, d):
     _kernel_status_ok()
 
 
+@pytest.mark.parametrize("heads", ["kv", "query"])
+def test_per_query_dbias_with_an_unpadded_key_extent(dev, heads):
+    """The backward operator with a per-(query, key) dBias whose key extent is Sk itself (420, not a multiple of 32),
+    a view into a wider buffer: the warps that lie wholly inside write 16-byte row pieces, the one that straddles Sk
+    writes element by element, and nothing lands beyond key Sk - 1 or query Sq - 1."""
+    B, Sq, Sk, H, Hk, d = 1, 300, 420, 4, 2, 128
+    hb = Hk if heads == "kv" else H
+    q, k, v, bias, dout = oracle.make_inputs(B, Sq, Sk, H, Hk, d, (B, hb, Sq, Sk), seed=11, dtype=torch.bfloat16, device=dev)
+    g = torch.Generator(device="cpu").manual_seed(12)
+    mask = (torch.rand(B, hb, Sq, Sk, generator=g) < 0.3).to(dev)
+    Sk_r = (Sk + 127) // 128 * 128
+    pad = lambda t: torch.nn.functional.pad(t, (0, Sk_r - Sk))
+    bias_p, mask_p = pad(bias), pad(mask)
+    out, lse, _ = torch.ops.flash_sparse_attn._flash_sparse_attn_forward(q, k, v, mask_p, bias_p, d ** -0.5, True, 0.0, False)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    sentinel = 12345.0
+    buf = torch.full((B, hb, Sq + 4, Sk_r), sentinel, dtype=torch.bfloat16, device=dev)
+    db = buf[:, :, :Sq, :Sk]
+    torch.ops.flash_sparse_attn._flash_sparse_attn_backward(dout, q, k, v, mask_p, bias_p, out, lse, dq, dk, dv, db,
+                                                            d ** -0.5, True, 0.0, False)
+    torch.cuda.synchronize()
+    assert (buf[:, :, :, Sk:] == sentinel).all() and (buf[:, :, Sq:, :] == sentinel).all(), "write outside dBias"
+    ref = oracle.attention_forward_backward(q.cpu(), k.cpu(), v.cpu(), mask.cpu(), bias.cpu(), dout.cpu(), None, True)
+    check("dbias", db.cpu(), ref[5], torch.bfloat16, reduced=True)
+    check("dq", dq.cpu(), ref[2], torch.bfloat16)
+    _kernel_status_ok()
+
+
 @pytest.mark.parametrize("geom,path", [((2, 200, 264, 4, 2, 128), "auto"), ((1, 130, 130, 2, 2, 64), "simt"),
                                        ((1, 256, 256, 2, 1, 256), "auto")])
 def test_backward_operator_returns_softmax_d(dev, geom, path):
