@@ -203,6 +203,18 @@ def test_tcgen05_forward_backward(dev, kernel_path, geom, bias_kind, mask_kind, 
     compare_all(case, causal, torch.bfloat16)
 
 
+@pytest.mark.parametrize("geom,bias_kind,mask_kind,causal", [
+    ((1, 256, 384, 4, 2, 128), "perq", "randq", True),      # per-query bias / mask / dBias shared by a head group
+    ((1, 300, 420, 4, 4, 128), "perhead", "randq", True),   # one row per query head, ragged
+    ((1, 256, 1280, 2, 1, 256), "perq", "randq", False),    # head dim 256 forward; CUDA-core backward
+])
+def test_per_query_tensors_in_fp16(dev, kernel_path, geom, bias_kind, mask_kind, causal):
+    """The per-query kernels' 16- and 32-byte bias / mask / dBias accesses in the other 16-bit type."""
+    kernel_path("auto")
+    case = build_case(dev, *geom, bias_kind, mask_kind, 0, torch.float16)
+    compare_all(case, causal, torch.float16)
+
+
 def test_tcgen05_backward_fp16_and_run_to_run_spread(dev, kernel_path):
     kernel_path("tcgen05")
     case = build_case(dev, 1, 384, 384, 4, 2, 128, "bcast", "topk", 100, torch.float16)
