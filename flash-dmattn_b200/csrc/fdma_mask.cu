@@ -307,6 +307,8 @@ __device__ __forceinline__ uint32_t key_pair16(uint32_t u) {
   return key | nan;
 }
 
+constexpr int kTieSlots = 32;  // up to this many keys tied at the threshold are ranked by one warp
+
 // kPos: also (or, with a null `out`, only) writes the ascending positions of the selected keys.
 template <int DT, int CHUNKS, bool kPos>
 __global__ void __launch_bounds__(kThreads, CHUNKS <= 4 ? 4 : 1) topk16_reg_kernel(const fdma_mask_params p) {
@@ -316,6 +318,8 @@ __global__ void __launch_bounds__(kThreads, CHUNKS <= 4 ? 4 : 1) topk16_reg_kern
   __shared__ uint32_t s_prefix;
   __shared__ int s_need;
   __shared__ int s_eq_total;
+  __shared__ int s_tie[kTieSlots];  // indices of the keys tied at the threshold, when they are few
+  __shared__ int s_tie_n;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n = p.keys;
   const int64_t total_rows = static_cast<int64_t>(p.out_b) * p.out_h * p.out_rows;
@@ -370,6 +374,7 @@ __global__ void __launch_bounds__(kThreads, CHUNKS <= 4 ? 4 : 1) topk16_reg_kern
   if (tid == 0) {
     s_prefix = 0;
     s_need = min(p.window, n);
+    s_tie_n = 0;
   }
   __syncwarp();
   // ---- pass 1: histogram of the high byte ----
@@ -479,6 +484,40 @@ __global__ void __launch_bounds__(kThreads, CHUNKS <= 4 ? 4 : 1) topk16_reg_kern
         ob[w] = (lo >= thr ? 1u : 0u) | (hi2 >= thr ? 0x100u : 0u);
       }
       emit(c, ob);
+    }
+  } else if (!kPos && s_eq_total <= kTieSlots) {
+    // A handful of keys tied at the threshold (the usual case): the lowest key indices win. Every thread writes the
+    // keys above the threshold and drops the index of each tied key of its own into a short list; after a barrier
+    // warp 0 ranks the list (one entry per lane, 32 shuffles) and sets the bytes of the winners itself. The
+    // block-wide scans of the general path below cost a quarter of the kernel's time.
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      uint32_t ob[4];
+      const int k = c * kChunk + tid * kPerThread;
+      bool any = false;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const uint32_t lo = kw[c][w] & 0xFFFFu, hi2 = kw[c][w] >> 16;
+        ob[w] = (lo > thr ? 1u : 0u) | (hi2 > thr ? 0x100u : 0u);
+        any |= lo == thr || hi2 == thr;
+      }
+      emit(c, ob);
+      if (any && k < n) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t key = (j & 1) ? (kw[c][j >> 1] >> 16) : (kw[c][j >> 1] & 0xFFFFu);
+          if (key == thr) s_tie[atomicAdd(&s_tie_n, 1)] = k + j;
+        }
+      }
+    }
+    __syncthreads();  // the list is complete, and every byte of the row has been written once
+    if (warp == 0 && thr != min_key) {  // (keys equal to min_dtype are never marked)
+      const int nt = s_tie_n;  // == s_eq_total
+      const int mine = lane < nt ? s_tie[lane] : 0x7FFFFFFF;
+      int rank = 0;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) rank += __shfl_sync(0xffffffffu, mine, j) < mine ? 1 : 0;
+      if (lane < nt && rank < need_eq) rp.out[mine] = 1;
     }
   } else {
     // ties at the threshold: the lowest key indices win. Keys are ranked chunk by chunk, thread by thread; one
