@@ -520,7 +520,11 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
       }
     }
   } else if (warp < 12) {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 176;");
+    // 65536 registers = 128 x 56 (warps 0-3) + 256 x 184 (softmax) + 128 x 88 (dQ writer); the deterministic writer
+    // converts to 64-bit fixed point and keeps 104, leaving the softmax warps 176. (184 / 88 against 176 / 104:
+    // 2-3 % on the backward kernel of the 32k benchmark; 192 and more for the softmax warps make the others spill.)
+    if constexpr (kDet) asm volatile("setmaxnreg.inc.sync.aligned.u32 176;");
+    else asm volatile("setmaxnreg.inc.sync.aligned.u32 184;");
     // ---------------- softmax warpgroups: thread = key, half = which 32 query columns ----------------
     const int half = (warp - 4) >> 2;
     const int krow = (warp & 3) * 32 + lane;  // key inside the tile == TMEM lane
@@ -884,7 +888,8 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
       }
     }
   } else {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
+    if constexpr (kDet) asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
+    else asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
     // ---------------- dQ writer: thread = head-dim index (row of dQ^T) ----------------
     // dQ^T (128 d x 64 q, fp32) leaves TMEM in two halves of 32 queries: transposed into a [32 q][128 d] fp32
     // staging tile in shared memory, then ONE bulk reduce-add (cp.reduce.async.bulk ... add.f32) per half into
