@@ -12,7 +12,7 @@ What is compiled, straight from the reference checkout (nothing is copied into t
 CUTLASS: the reference expects its `csrc/cutlass` submodule, which is empty in the checkout; the CUTLASS headers
 shipped inside the flashinfer wheel of this image are used instead.
 
-    python baseline/build_ref_cuda.py [--reference /root/reference]
+    python baseline/build_ref_cuda.py [--reference <reference checkout>]
 
 Needs nvcc and torch, no GPU. Output: baseline/_ref/flash_sparse_attn_cuda*.so next to the reference's Python
 package (installed there with pip, FLASH_SPARSE_ATTENTION_SKIP_CUDA_BUILD=TRUE)."""
