@@ -273,7 +273,7 @@ class AttentionStep:
     the full key range (compact=False: fdma_fwd, fdma_bwd) or over the gathered kept keys (compact=True: the eight
     calls flash_sparse_attn_func makes for a row-broadcast mask whose position list create_mask has written)."""
 
-    def __init__(self, lib, dev, q, k, v, mask, bias, dout, compact: bool):
+    def __init__(self, lib, dev, q, k, v, mask, bias, dout, compact: bool, packed=None):
         from flash_sparse_attn import _lib, compaction
         from flash_sparse_attn import flash_sparse_attn_interface as iface
 
@@ -308,11 +308,15 @@ class AttentionStep:
                     src, dst, self.key_pos, B, Hk, Sk, cap, d, iface._bsh(src), iface._bsh(dst))))
             self.post.append((lib.fdma_scatter_rows, compaction._rows_params(
                 dbb, self.dbias, self.key_pos, bias.shape[0], bias.shape[1], Sk, cap, 1, bst(dbb), bst(self.dbias))))
-        self.keep = (kk, vv, mm, bb, dkk, dvv, dbb)
+        self.keep = (kk, vv, mm, bb, dkk, dvv, dbb, packed)
         self.fp = _lib.FwdParams()
         self.bp = _lib.BwdParams()
         for p in (self.fp, self.bp.f):
             iface._fill_fwd(p, q, kk, vv, mm, bb, self.out, self.lse, d ** -0.5, True)
+            if packed is not None:  # the mask as one bit per key + tile activity (flash_sparse_attn.packed)
+                p.mask, p.mask_bits, p.h_mask = packed.bits.data_ptr(), 1, packed.bits.shape[1]
+                p.mask_batch_stride, p.mask_head_stride, p.mask_row_stride = packed.bits.stride()[:3]
+                p.tile_activity = packed.activity.data_ptr()
             if compact:
                 p.key_pos, p.key_pos_batch_stride = self.key_pos.data_ptr(), self.key_pos.stride(0)
                 p.key_pos_head_stride, p.h_pos, p.causal_shift = self.key_pos.stride(1), self.key_pos.shape[1], Sk - Sq
@@ -671,7 +675,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             ln = fn(sec_args, 0, 1, local_rank)
             secondary[name] = {"metric": ln["metric"], "ms_per_step": ln["ms_per_step"], "value": ln["value"],
                                "unit": ln["unit"], "roofline": ln["roofline"], "workload": ln["config"]["workload"]}
-            for extra in ("fwd_ms", "bwd_ms", "decode_kernel_ms"):
+            for extra in ("fwd_ms", "bwd_ms", "decode_kernel_ms", "packed_mask"):
                 if extra in ln:
                     secondary[name][extra] = ln[extra]
             torch.cuda.empty_cache()
@@ -1053,6 +1057,41 @@ def measure_perquery(args, rank: int, world: int, local_rank: int):
                      "traffic": None},
         "gpu_launches": args.steps * 5,  # tile_activity x2, fwd_kernel, bwd_prep, bwd_kernel (+ convert_dq)
     }
+    # The same step with the mask as one bit per key + tile activity (create_packed_mask): what the library offers in
+    # place of the reference's bool tensor for per-query masks. Reported beside the line, never mixed into it.
+    try:
+        from flash_sparse_attn.utils.mask import create_packed_mask
+
+        del step
+        md = torch.finfo(torch.bfloat16).min
+        packed = create_packed_mask(bias, None, B, Sq, Sq, w, md)
+        assert torch.equal(packed.to_bool(), mask), "packed mask differs from create_mask"
+        pstep = AttentionStep(lib, dev, q, k, v, mask, bias, dout, False, packed=packed)
+        for _ in range(max(args.warmup, 3)):
+            pstep()
+        p_total, p_fwd, p_bwd = time_steps(pstep, args.steps, stream, lambda: torch.cuda.synchronize(dev))
+        _lib.check(lib.fdma_last_kernel_status(stream.cuda_stream, None), "kernel status")
+
+        def timed(fn, n=5):
+            for _ in range(2):
+                fn()
+            torch.cuda.synchronize(dev)
+            a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            for _ in range(n):
+                fn()
+            b_.record(stream)
+            torch.cuda.synchronize(dev)
+            return a.elapsed_time(b_) / n
+
+        line["packed_mask"] = {
+            "what": "same step, mask as 1 bit per key + tile activity (64 MiB instead of 512 MiB)",
+            "ms_per_step": p_total / args.steps, "fwd_ms": p_fwd, "bwd_ms": p_bwd,
+            "create_packed_mask_ms": timed(lambda: create_packed_mask(bias, None, B, Sq, Sq, w, md)),
+            "create_mask_ms": timed(lambda: create_mask(bias, None, B, Sq, Sq, w, md)),
+        }
+    except Exception as e:  # the comparison is an extra: never let it take the line down
+        line["packed_mask"] = {"unavailable": str(e)[:200]}
     return line
 
 

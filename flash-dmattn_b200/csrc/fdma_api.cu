@@ -77,6 +77,7 @@ int validate_bwd(const fdma_bwd_params& p) {
 fdma_fwd_params normalise(const fdma_fwd_params& in) {
   fdma_fwd_params p = in;
   if (!p.mask) p.h_mask = 1;
+  if (!p.mask) p.mask_bits = 0;
   if (!p.bias) p.h_bias = 1;
   if (p.seqlen_q == 1) p.is_causal = 0;
   if (!p.key_pos || !p.is_causal) {
@@ -218,12 +219,13 @@ int fdma_fwd(const fdma_fwd_params* pp, void* stream_) {
   const fdma_fwd_params p = normalise(*pp);
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (p.path == FDMA_PATH_AUTO || p.path == FDMA_PATH_DECODE) {
-    if (decode_supported(p)) return decode_fwd(p, stream);
+    if (decode_supported(p) && !(p.mask && p.mask_bits)) return decode_fwd(p, stream);
     if (p.path == FDMA_PATH_DECODE) return FDMA_ERR_UNSUPPORTED;
   }
   const bool tc_ok = tc_fwd_supported(p);
   if (p.path == FDMA_PATH_TCGEN05 && !tc_ok) return FDMA_ERR_UNSUPPORTED;
   if (p.path != FDMA_PATH_SIMT && tc_ok) return tc_fwd(p, stream);
+  if (p.mask && p.mask_bits) return FDMA_ERR_UNSUPPORTED;  // only the tcgen05 kernels read a bit-packed mask
   return simt_fwd(p, stream);
 }
 
@@ -247,17 +249,22 @@ int fdma_bwd(const fdma_bwd_params* pp, void* stream_) {
   const bool tc_ok = tc_bwd_supported(p);
   if (p.f.path == FDMA_PATH_TCGEN05 && !tc_ok) return FDMA_ERR_UNSUPPORTED;
   if (p.f.path != FDMA_PATH_SIMT && tc_ok) return tc_bwd(p, stream);
+  if (p.f.mask && p.f.mask_bits) return FDMA_ERR_UNSUPPORTED;  // only the tcgen05 kernels read a bit-packed mask
   return simt_bwd(p, stream);
 }
 
 int fdma_create_mask(const fdma_mask_params* p, void* stream_) {
-  if (!p || !p->bias || (!p->out && !p->key_pos)) return FDMA_ERR_BAD_ARG;
+  if (!p || !p->bias || (!p->out && !p->key_pos && !p->bits)) return FDMA_ERR_BAD_ARG;
   if (p->out_b < 0 || p->out_h < 0 || p->out_rows < 0 || p->keys < 0) return FDMA_ERR_BAD_ARG;
   if (p->kind != FDMA_MASK_TOPK && p->kind != FDMA_MASK_RELU) return FDMA_ERR_BAD_ARG;
   if (p->key_pos) {  // position output: top-k selection without block smoothing, every selection must fit
     if (!p->count || p->capacity <= 0) return FDMA_ERR_BAD_ARG;
     if (p->kind != FDMA_MASK_TOPK || p->block_size > 1) return FDMA_ERR_UNSUPPORTED;
     if (p->window <= 0 || p->capacity < (p->window < p->keys ? p->window : p->keys)) return FDMA_ERR_BAD_ARG;
+  }
+  if (p->bits) {  // bit-packed output: top-k selection without block smoothing, with its tile activity
+    if (!p->activity) return FDMA_ERR_BAD_ARG;
+    if (p->kind != FDMA_MASK_TOPK || p->block_size > 1 || p->window <= 0 || p->key_pos) return FDMA_ERR_UNSUPPORTED;
   }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (p->kind == FDMA_MASK_TOPK && p->window <= 0) {

@@ -62,6 +62,7 @@ struct BwdKernelParams {
   float* dbias_part;   // nsplit > 1, column-sum mode: fp32 partials [nsplit][B][h_k][NT*128]
   int nsplit;          // query-range splits per key tile
   const uint8_t* act;  // per-query mask: activity bytes [B][h_mask][ceil(Sq/128)][ceil(Sk/128)], else null
+  int mask_bits;       // per-query mask given as one bit per key (uint32 words, strides in words)
   int* status;
   int64_t mask_batch_stride, mask_head_stride, mask_row_stride;
   int64_t bias_batch_stride, bias_head_stride, bias_row_stride;
@@ -638,8 +639,31 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
             const uint16_t* bcol = p.bias ? reinterpret_cast<const uint16_t*>(p.bias) + b * p.bias_batch_stride +
                                                 hb * p.bias_head_stride + key
                                           : nullptr;
-            const uint8_t* mcol = p.mask ? p.mask + b * p.mask_batch_stride + hm * p.mask_head_stride + key : nullptr;
+            const bool mbits = p.mask && p.mask_bits;
+            const uint8_t* mcol = (p.mask && !mbits) ? p.mask + b * p.mask_batch_stride + hm * p.mask_head_stride + key
+                                                     : nullptr;
             const int wkey = -lane;  // the warp's first key, relative to this lane's
+            // Bit-packed mask: the warp's 32 x 32 block is one word per query row. Lane j fetches row j's word and a
+            // five-step exchange transposes the bit matrix across the lanes: lane k ends up with column k (its key).
+            uint32_t colbits = 0xFFFFFFFFu;
+            if (mbits) {
+              const uint32_t* mw32 = reinterpret_cast<const uint32_t*>(p.mask) + b * p.mask_batch_stride +
+                                     hm * p.mask_head_stride + ((n * kBN + (warp & 3) * 32) >> 5);
+              if (g == 0 && m + 1 < M64)
+                prefetch_l2(mw32 + static_cast<int64_t>(min((m + 1) * kBM + half * 32 + lane, Sq - 1)) * p.mask_row_stride);
+              uint32_t a = __ldg(mw32 + static_cast<int64_t>(min(q0 + lane, Sq - 1)) * p.mask_row_stride);
+              uint32_t msk = 0x0000FFFFu;
+#pragma unroll
+              for (int j = 16; j > 0; j >>= 1) {
+                const uint32_t other = __shfl_xor_sync(0xffffffffu, a, j);
+                // blocks of j x j bits: the upper-right one (rows without bit j, columns with it) changes places
+                // with the lower-left one
+                if ((lane & j) == 0) a ^= (((a >> j) ^ other) & msk) << j;
+                else a ^= (a ^ (other >> j)) & msk;
+                msk ^= msk << (j >> 1);
+              }
+              colbits = a;
+            }
             if (g == 0 && m + 1 < M64) {
               // next query tile's bias / mask sectors of this warp's 32 keys: lane j asks L2 for row j
               const int64_t qn = min((m + 1) * kBM + half * 32 + lane, Sq - 1);
@@ -678,16 +702,25 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_kernel(const __grid_constant_
               for (int j = 0; j < 16; ++j) braw[r * 16 + j] = raw16_to_float<kBf16>(tr16[j * 32 + lane]) * kLog2e;
               __syncwarp();
             }
-            tr4[lane] = vm[0];
-            tr4[lane + 32] = vm[1];
-            __syncwarp();
+            if (mbits) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const bool k0 = key_ok && s_tr[(2 * j) * 32 + lane] != 0;
-              const bool k1 = key_ok && s_tr[(2 * j + 1) * 32 + lane] != 0;
-              bias2[j] = make_float2(k0 ? braw[2 * j] : -CUDART_INF_F, k1 ? braw[2 * j + 1] : -CUDART_INF_F);
+              for (int j = 0; j < 16; ++j) {
+                const bool k0 = key_ok && ((colbits >> (2 * j)) & 1u);
+                const bool k1 = key_ok && ((colbits >> (2 * j + 1)) & 1u);
+                bias2[j] = make_float2(k0 ? braw[2 * j] : -CUDART_INF_F, k1 ? braw[2 * j + 1] : -CUDART_INF_F);
+              }
+            } else {
+              tr4[lane] = vm[0];
+              tr4[lane + 32] = vm[1];
+              __syncwarp();
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const bool k0 = key_ok && s_tr[(2 * j) * 32 + lane] != 0;
+                const bool k1 = key_ok && s_tr[(2 * j + 1) * 32 + lane] != 0;
+                bias2[j] = make_float2(k0 ? braw[2 * j] : -CUDART_INF_F, k1 ? braw[2 * j + 1] : -CUDART_INF_F);
+              }
+              __syncwarp();
             }
-            __syncwarp();
           }
           if (causal && static_cast<int64_t>(ckey_wmax) > static_cast<int64_t>(q0) + coff) {
 #pragma unroll
@@ -1144,7 +1177,10 @@ int launch(const fdma_bwd_params& bp, const BwdPlan& pl, cudaStream_t stream) {
     if (st) return st;
   }
   kp.act = nullptr;
-  if (pl.needs_act) {
+  kp.mask_bits = p.mask ? p.mask_bits : 0;
+  if (pl.needs_act && p.tile_activity) {
+    kp.act = p.tile_activity;
+  } else if (pl.needs_act) {
     uint8_t* act = reinterpret_cast<uint8_t*>(ws + pl.act_off);
     st = launch_tile_activity(p, act, stream);
     if (st) return st;

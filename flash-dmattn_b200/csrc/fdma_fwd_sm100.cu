@@ -27,6 +27,8 @@
 #include <algorithm>
 #include <mutex>
 
+#include <type_traits>
+
 #include "fdma_internal.h"
 #include "fdma_ptx.cuh"
 
@@ -158,7 +160,8 @@ __device__ __forceinline__ FwdItem fwd_item(const FwdKernelParams& p, int item) 
   return w;
 }
 
-template <int D, bool kBf16, bool kBcast>
+// kBits (per-query kernel only): the mask holds one bit per key instead of one byte.
+template <int D, bool kBf16, bool kBcast, bool kBits = false>
 __global__ void __launch_bounds__(Smem<D>::kThreads, 1) fwd_kernel(const __grid_constant__ FwdKernelParams p) {
   using L = Smem<D>;
   constexpr int kNQ = L::kNQ, kStages = L::kStages;
@@ -556,7 +559,9 @@ __global__ void __launch_bounds__(Smem<D>::kThreads, 1) fwd_kernel(const __grid_
     const uint8_t* mrow = nullptr;
     const uint16_t* brow = nullptr;
     if (!kBcast) {
-      if (p.mask) mrow = p.mask + b * p.mask_batch_stride + w.hm * p.mask_head_stride + qclamp * p.mask_row_stride;
+      if (p.mask)  // bit-packed: 4-byte units, i.e. the same expression on a word pointer
+        mrow = p.mask + (b * p.mask_batch_stride + w.hm * p.mask_head_stride + qclamp * p.mask_row_stride) *
+                            (kBits ? 4 : 1);
       if (p.bias)
         brow = reinterpret_cast<const uint16_t*>(p.bias) + b * p.bias_batch_stride + w.hb * p.bias_head_stride +
                qclamp * p.bias_row_stride;
@@ -586,21 +591,27 @@ __global__ void __launch_bounds__(Smem<D>::kThreads, 1) fwd_kernel(const __grid_
         // Per-query bias / mask: this row's 128 + 256 bytes of the tile are requested BEFORE the wait for the score
         // tile, so the load latency overlaps the wait; the scores then leave TMEM 32 columns at a time and take the
         // place of the addend registers they consume.
-        uint32_t bw[kBcast ? 1 : 8][8], mw[kBcast ? 1 : 4][8];
+        uint32_t bw[kBcast ? 1 : 8][8], mw[(kBcast || kBits) ? 1 : 4][8];
         if (!kBcast) {
           // ... and of the next tile this row will process: into L2 while this tile is worked on
           int jn = j + 1;
           while (jn < nT && !(s_flags[jn] & (1 << t))) ++jn;
           if (jn < nT) {
-            if (mrow) prefetch_l2(mrow + jn * kBN);
+            if (mrow) prefetch_l2(mrow + (kBits ? jn * (kBN / 8) : jn * kBN));
             if (brow) {
               prefetch_l2(brow + jn * kBN);
               prefetch_l2(brow + jn * kBN + 64);
             }
           }
 #pragma unroll
+          if (kBits) {  // 128 bits of this row: one 16-byte load, kept in mw[0][0..3]
+            const uint4 mb = mrow ? ld_nc_v4(mrow + (kbase >> 3)) : make_uint4(~0u, ~0u, ~0u, ~0u);
+            mw[0][0] = mb.x; mw[0][1] = mb.y; mw[0][2] = mb.z; mw[0][3] = mb.w;
+          }
+#pragma unroll
           for (int c2 = 0; c2 < 4; ++c2) {
-            if (!mrow) {
+            if (kBits) {
+            } else if (!mrow) {
 #pragma unroll
               for (int i = 0; i < 8; ++i) mw[c2][i] = 0x01010101u;
             } else if (wide_m) {
@@ -668,9 +679,15 @@ __global__ void __launch_bounds__(Smem<D>::kThreads, 1) fwd_kernel(const __grid_
                   bf = make_float2(__low2float(hh), __high2float(hh));
                 }
                 float2 add = __fmul2_rn(bf, l2e2);
-                const uint32_t mpair = mw[c2][cc * 4 + (i >> 1)] >> ((i & 1) * 16);
-                if ((mpair & 0xFFu) == 0) add.x = -CUDART_INF_F;
-                if ((mpair & 0xFF00u) == 0) add.y = -CUDART_INF_F;
+                if (kBits) {
+                  const uint32_t mpair = mw[0][c2] >> (cc * 16 + 2 * i);
+                  if ((mpair & 1u) == 0) add.x = -CUDART_INF_F;
+                  if ((mpair & 2u) == 0) add.y = -CUDART_INF_F;
+                } else {
+                  const uint32_t mpair = mw[c2][cc * 4 + (i >> 1)] >> ((i & 1) * 16);
+                  if ((mpair & 0xFFu) == 0) add.x = -CUDART_INF_F;
+                  if ((mpair & 0xFF00u) == 0) add.y = -CUDART_INF_F;
+                }
                 s2[c * 8 + i] = __ffma2_rn(make_float2(__uint_as_float(su[cc * 16 + 2 * i]),
                                                        __uint_as_float(su[cc * 16 + 2 * i + 1])), sc2, add);
               }
@@ -883,13 +900,13 @@ FwdPlan plan(const fdma_fwd_params& p) {
   pl.bcast = mask_b && bias_b;
   pl.needs_act = !pl.bcast && p.mask != nullptr;
   const size_t mt = (p.seqlen_q + kBM - 1) / kBM, nt = (p.seqlen_k + kBN - 1) / kBN;
-  pl.act_bytes = pl.needs_act ? align256(static_cast<size_t>(p.b) * p.h_mask * mt * nt) : 0;
+  pl.act_bytes = pl.needs_act && !p.tile_activity ? align256(static_cast<size_t>(p.b) * p.h_mask * mt * nt) : 0;
   return pl;
 }
 
 bool aligned16(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15u) == 0; }
 
-template <int D, bool kBf16, bool kBcast>
+template <int D, bool kBf16, bool kBcast, bool kBits = false>
 int launch(const fdma_fwd_params& p, const FwdPlan& pl, cudaStream_t stream) {
   using L = Smem<D>;
   constexpr int kNQ = L::kNQ;
@@ -933,7 +950,9 @@ int launch(const fdma_fwd_params& p, const FwdPlan& pl, cudaStream_t stream) {
   kp.h_pos = p.h_pos; kp.causal_shift = p.causal_shift;
   kp.scale_log2 = p.softmax_scale * kLog2e;
 
-  if (pl.needs_act) {
+  if (pl.needs_act && p.tile_activity) {
+    kp.act = p.tile_activity;
+  } else if (pl.needs_act) {
     if (!p.workspace || p.workspace_bytes < pl.act_bytes) return FDMA_ERR_WORKSPACE;
     uint8_t* act = static_cast<uint8_t*>(p.workspace);
     st = launch_tile_activity(p, act, stream);
@@ -941,7 +960,7 @@ int launch(const fdma_fwd_params& p, const FwdPlan& pl, cudaStream_t stream) {
     kp.act = act;
   }
 
-  auto kern = fwd_kernel<D, kBf16, kBcast>;
+  auto kern = fwd_kernel<D, kBf16, kBcast, kBits>;
   // The attribute belongs to the (function, device) pair: set it on every call, whichever device is current.
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kAlloc);
   if (e != cudaSuccess) return static_cast<int>(e);
@@ -965,9 +984,11 @@ int launch(const fdma_fwd_params& p, const FwdPlan& pl, cudaStream_t stream) {
 template <int D>
 int launch_d(const fdma_fwd_params& p, const FwdPlan& pl, cudaStream_t stream) {
   if (p.dtype == FDMA_BF16) {
-    return pl.bcast ? launch<D, true, true>(p, pl, stream) : launch<D, true, false>(p, pl, stream);
+    if (pl.bcast) return launch<D, true, true>(p, pl, stream);
+    return (p.mask && p.mask_bits) ? launch<D, true, false, true>(p, pl, stream) : launch<D, true, false>(p, pl, stream);
   }
-  return pl.bcast ? launch<D, false, true>(p, pl, stream) : launch<D, false, false>(p, pl, stream);
+  if (pl.bcast) return launch<D, false, true>(p, pl, stream);
+  return (p.mask && p.mask_bits) ? launch<D, false, false, true>(p, pl, stream) : launch<D, false, false>(p, pl, stream);
 }
 
 }  // namespace
@@ -1005,7 +1026,11 @@ bool tc_fwd_supported(const fdma_fwd_params& p) {
     if (!aligned16(p.bias)) return false;
     if (p.bias_batch_stride % 8 || p.bias_head_stride % 8 || p.bias_row_stride % 8) return false;
   }
-  if (p.mask) {
+  if (p.mask && p.mask_bits) {  // bit-packed: per-query rows of 16-byte multiples, tile activity supplied
+    if (!aligned16(p.mask) || !p.tile_activity) return false;
+    if (p.mask_batch_stride % 4 || p.mask_head_stride % 4 || p.mask_row_stride % 4) return false;
+    if (p.mask_row_stride == 0 || p.seqlen_q == 1) return false;
+  } else if (p.mask) {
     if (!aligned16(p.mask)) return false;
     if (p.mask_batch_stride % 16 || p.mask_head_stride % 16 || p.mask_row_stride % 16) return false;
   }

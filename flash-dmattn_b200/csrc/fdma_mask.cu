@@ -345,6 +345,10 @@ __global__ void __launch_bounds__(kThreads, CHUNKS <= 4 ? 4 : 1) topk16_reg_kern
   // (Fetching the next row while this one is processed was measured on B200: more registers, fewer CTAs, slower.)
   for (int64_t row = blockIdx.x; row < total_rows; row += gridDim.x) {
   const RowPtrs rp = locate(p, row, 2);
+  // bit-packed output: this row's bits as bytes (key k -> bit k & 7 of byte k >> 3, the little-endian view of the
+  // uint32 words)
+  uint8_t* bits_row = nullptr;
+  if (p.bits) bits_row = reinterpret_cast<uint8_t*>(p.bits + row * (((n + 127) / 128) * 4));
   fetch(row);
   // ---- transform: chunk c holds keys [c*2048 + tid*8, +8) of the row ----
   uint32_t kw[CHUNKS][4];
@@ -468,10 +472,13 @@ __global__ void __launch_bounds__(kThreads, CHUNKS <= 4 ? 4 : 1) topk16_reg_kern
     uint2 o;
     o.x = ob[0] | (ob[1] << 16);
     o.y = ob[2] | (ob[3] << 16);
-    if (!kPos || rp.out) *reinterpret_cast<uint2*>(rp.out + k) = o;
-    if (kPos) {  // bit j of the chunk's byte = key k + j selected
+    if (rp.out) *reinterpret_cast<uint2*>(rp.out + k) = o;
+    if (kPos || bits_row) {  // bit j of the chunk's byte = key k + j selected
       const uint32_t b8 = (((o.x & 0x01010101u) * 0x01020408u) >> 24) | ((((o.y & 0x01010101u) * 0x01020408u) >> 24) << 4);
-      selbits[c >> 2] |= b8 << ((c & 3) * 8);
+      if (kPos) selbits[c >> 2] |= b8 << ((c & 3) * 8);
+      if (bits_row && b8) {
+        bits_row[k >> 3] = static_cast<uint8_t>(b8);   // (the row was zero-filled by the caller)
+      }
     }
   };
   if (all_eq) {  // every key equal to the threshold is kept
@@ -517,7 +524,12 @@ __global__ void __launch_bounds__(kThreads, CHUNKS <= 4 ? 4 : 1) topk16_reg_kern
       int rank = 0;
 #pragma unroll
       for (int j = 0; j < 32; ++j) rank += __shfl_sync(0xffffffffu, mine, j) < mine ? 1 : 0;
-      if (lane < nt && rank < need_eq) rp.out[mine] = 1;
+      if (lane < nt && rank < need_eq) {
+        if (rp.out) rp.out[mine] = 1;
+        if (bits_row) {
+          atomicOr(reinterpret_cast<unsigned*>(bits_row) + (mine >> 5), 1u << (mine & 31));
+        }
+      }
     }
   } else {
     // ties at the threshold: the lowest key indices win. Keys are ranked chunk by chunk, thread by thread; one
@@ -622,6 +634,31 @@ __global__ void __launch_bounds__(kThreads, CHUNKS <= 4 ? 4 : 1) topk16_reg_kern
   }  // row loop
 }
 
+// Tile activity of a bit-packed mask: act[bh][mt][nt] = 1 iff some row of query tile mt has a bit set among the 128
+// keys of key tile nt. One warp per tile, four rows per lane, 16 bytes per row.
+__global__ void activity_from_bits_kernel(const uint32_t* __restrict__ bits, uint8_t* __restrict__ act, int bh_count,
+                                          int rows, int key_tiles) {
+  const int lane = threadIdx.x & 31;
+  const int row_tiles = (rows + 127) / 128;
+  const int64_t total = static_cast<int64_t>(bh_count) * row_tiles * key_tiles;
+  const int64_t w = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
+  if (w >= total) return;
+  const int nt = static_cast<int>(w % key_tiles);
+  const int mt = static_cast<int>((w / key_tiles) % row_tiles);
+  const int64_t bh = w / (static_cast<int64_t>(key_tiles) * row_tiles);
+  uint32_t any = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = mt * 128 + i * 32 + lane;
+    if (r < rows) {
+      const uint4 v = *reinterpret_cast<const uint4*>(bits + ((bh * rows + r) * key_tiles + nt) * 4);
+      any |= v.x | v.y | v.z | v.w;
+    }
+  }
+  const bool set = __any_sync(0xffffffffu, any != 0);
+  if (lane == 0) act[w] = set ? 1 : 0;
+}
+
 template <int DT>
 bool reg_path_ok(const fdma_mask_params& p) {
   if (DT == FDMA_FP32) return false;
@@ -691,6 +728,7 @@ int launch_mask(const fdma_mask_params& p, cudaStream_t stream) {
   const int64_t rows = static_cast<int64_t>(p.out_b) * p.out_h * p.out_rows;
   if (rows == 0 || p.keys == 0) return 0;
   if (rows > 0x7FFFFFFF) return FDMA_ERR_UNSUPPORTED;
+  if (p.bits && (p.kind != FDMA_MASK_TOPK || !reg_path_ok<DT>(p))) return FDMA_ERR_UNSUPPORTED;  // register kernel only
   if (p.kind == FDMA_MASK_RELU) {
     relu_mask_kernel<DT><<<static_cast<unsigned>(rows), kThreads, 0, stream>>>(p);
   } else if (reg_path_ok<DT>(p)) {
@@ -711,6 +749,14 @@ int launch_mask(const fdma_mask_params& p, cudaStream_t stream) {
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
+  if (p.bits) {
+    const int key_tiles = (p.keys + 127) / 128;
+    const int64_t tiles = static_cast<int64_t>(p.out_b) * p.out_h * ((p.out_rows + 127) / 128) * key_tiles;
+    activity_from_bits_kernel<<<static_cast<unsigned>((tiles * 32 + 255) / 256), 256, 0, stream>>>(
+        p.bits, p.activity, p.out_b * p.out_h, p.out_rows, key_tiles);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
   if (p.block_size > 1) {
     const int nblk = (p.keys + p.block_size - 1) / p.block_size;
     const int64_t warps = rows * nblk;

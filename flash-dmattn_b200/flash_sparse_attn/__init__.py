@@ -10,6 +10,7 @@ __version__ = "1.0.0"
 from .flash_sparse_attn_interface import (FlashDMAttnFunc, flash_sparse_attn_func,  # noqa: F401
                                           flash_sparse_attn_varlen_func)
 from .compaction import compact_keys, flash_sparse_attn_compact_func  # noqa: F401
+from .packed import PackedMask, pack_mask  # noqa: F401
 
 CUDA_AVAILABLE = True
 TRITON_AVAILABLE = False

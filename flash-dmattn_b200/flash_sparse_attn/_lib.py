@@ -13,6 +13,7 @@ LIB_PATH = os.environ.get("FDMA_LIB", os.path.join(_HERE, "lib", "libfdma_sm100.
 FDMA_BF16, FDMA_FP16, FDMA_FP32 = 0, 1, 2
 PATH_AUTO, PATH_SIMT, PATH_TCGEN05, PATH_DECODE = 0, 1, 2, 3
 MASK_TOPK, MASK_RELU = 0, 1
+ERR_UNSUPPORTED = -2
 
 
 class FwdParams(Structure):
@@ -25,6 +26,7 @@ class FwdParams(Structure):
         + [("workspace", c_void_p), ("workspace_bytes", c_size_t)]
         + [("key_pos", c_void_p), ("key_pos_batch_stride", c_int64), ("key_pos_head_stride", c_int64)]
         + [("h_pos", c_int32), ("causal_shift", c_int32)]
+        + [("mask_bits", c_int32), ("reserved", c_int32), ("tile_activity", c_void_p)]
     )
 
 
@@ -48,6 +50,7 @@ class MaskParams(Structure):
         + [(n, c_int32) for n in ("out_b", "out_h", "out_rows", "keys", "window", "dtype", "kind", "block_size")]
         + [("min_value", c_float)]
         + [("key_pos", c_void_p), ("count", c_void_p), ("slot_mask", c_void_p), ("capacity", c_int32), ("reserved", c_int32)]
+        + [("bits", c_void_p), ("activity", c_void_p)]
     )
 
 

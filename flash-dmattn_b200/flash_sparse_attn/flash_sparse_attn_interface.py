@@ -432,8 +432,17 @@ def flash_sparse_attn_func(
     A row-broadcast mask (one keep-set per batch and kv head) is run over its gathered kept keys, which gives the
     same result in far fewer key tiles when the kept keys are scattered; `set_compaction("off")` disables that.
     """
+    from .packed import PackedMask
     from .utils.mask import KeptKeys
 
+    if isinstance(attn_mask, PackedMask):  # one bit per (query, key): utils.mask.create_packed_mask
+        from .packed import flash_sparse_attn_packed_func
+
+        if softcap or return_attn_probs:
+            attn_mask = attn_mask.to_bool()
+        else:
+            return flash_sparse_attn_packed_func(query, key, value, attn_mask, attn_bias, softmax_scale, is_causal,
+                                                 deterministic)
     d = query.shape[-1]
     needs_grad = torch.is_grad_enabled() and any(t.requires_grad for t in (query, key, value))
     d_run = _kernel_head_dim(d, needs_grad) if query.dim() == 4 and not return_attn_probs else d

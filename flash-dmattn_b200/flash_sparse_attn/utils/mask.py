@@ -60,12 +60,22 @@ def _launch(attention_bias, attention_mask, window_size, min_dtype, block_size, 
             pm = pm.expand(*pm.shape[:-1], keys).contiguous()
     if kind == _lib.MASK_TOPK and window_size > keys:
         raise RuntimeError("selected index k out of range")  # what torch.topk raises in the reference
-    out = torch.empty(out_shape, dtype=torch.bool, device=bias.device) if positions != "only" else None
+    out = torch.empty(out_shape, dtype=torch.bool, device=bias.device) if positions not in ("only", "bits") else None
     p = _lib.MaskParams()
     p.bias, p.premask = bias.data_ptr(), (pm.data_ptr() if pm is not None else None)
     p.out = out.data_ptr() if out is not None else None
     kept = None
-    if positions != "none":
+    packed = None
+    if positions == "bits":  # one bit per key (zero-filled: the kernel only sets bits) + tile activity
+        from ..packed import PackedMask
+
+        words = (keys + _TILE - 1) // _TILE * (_TILE // 32)
+        bits = torch.zeros(tuple(out_shape[:3]) + (words,), dtype=torch.int32, device=bias.device)
+        act = torch.empty(tuple(out_shape[:2]) + ((out_shape[2] + 127) // 128, (keys + _TILE - 1) // _TILE),
+                          dtype=torch.uint8, device=bias.device)
+        p.bits, p.activity = bits.data_ptr(), act.data_ptr()
+        packed = PackedMask(bits, act, keys)
+    elif positions != "none":
         cap = max(_TILE, (min(int(window_size), keys) + _TILE - 1) // _TILE * _TILE)
         lead = tuple(out_shape[:2]) if out_shape[2] == 1 else tuple(out_shape[:3])
         key_pos = torch.empty(lead + (cap,), dtype=torch.int32, device=bias.device)
@@ -89,7 +99,12 @@ def _launch(attention_bias, attention_mask, window_size, min_dtype, block_size, 
     lib = _lib.load()
     with torch.cuda.device(bias.device):
         stream = torch.cuda.current_stream(bias.device).cuda_stream
-        _lib.check(lib.fdma_create_mask(ctypes.byref(p), stream), "fdma_create_mask")
+        status = lib.fdma_create_mask(ctypes.byref(p), stream)
+        if positions == "bits" and status == _lib.ERR_UNSUPPORTED:
+            return None  # the caller builds the bool mask and packs it
+        _lib.check(status, "fdma_create_mask")
+    if positions == "bits":
+        return packed
     if positions == "only":
         return kept
     return (out, kept) if positions == "also" else out
@@ -203,3 +218,26 @@ def create_kept_keys(
     if attention_mask is not None and attention_mask.shape[2] != 1:
         raise RuntimeError("create_kept_keys needs a pre-mask with one query row")
     return _launch(attention_bias, attention_mask, window_size, min_dtype, None, _lib.MASK_TOPK, positions="only")
+
+
+def create_packed_mask(
+    attention_bias: torch.Tensor,
+    attention_mask: Optional[torch.Tensor],
+    batch_size: int,
+    query_len: int,
+    key_len: int,
+    window_size: int,
+    min_dtype: float,
+):
+    """`create_mask(..., type="topk")` returned as a `packed.PackedMask` -- one bit per (query, key) and one activity
+    byte per 128 x 128 tile -- instead of a bool tensor. Same selection as `create_mask` (the `window_size` largest
+    entries per row, never an entry equal to `min_dtype`; `attention_mask` pre-masks keys). Pass the result as
+    `attn_mask` to `flash_sparse_attn_func`. Meant for per-query biases (B, H, Sq, Sk), where the bool mask is as large
+    as half the bias; for a row-broadcast bias `create_kept_keys` is the better form."""
+    from ..packed import pack_mask
+
+    attention_mask = _reshape_padding_mask(attention_mask, batch_size, query_len, key_len)
+    packed = _launch(attention_bias, attention_mask, window_size, min_dtype, None, _lib.MASK_TOPK, positions="bits")
+    if packed is None:  # a configuration the bit-writing kernel does not serve: bool mask first
+        packed = pack_mask(_launch(attention_bias, attention_mask, window_size, min_dtype, None, _lib.MASK_TOPK))
+    return packed

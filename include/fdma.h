@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define FDMA_VERSION 10000 /* 1.0.0 */
+#define FDMA_VERSION 10100 /* 1.1.0: fdma_fwd_params grew by mask_bits / tile_activity, fdma_mask_params by bits / activity */
 
 enum fdma_dtype { FDMA_BF16 = 0, FDMA_FP16 = 1, FDMA_FP32 = 2 };
 
@@ -89,6 +89,20 @@ typedef struct fdma_fwd_params {
   int64_t key_pos_batch_stride, key_pos_head_stride;
   int32_t h_pos;
   int32_t causal_shift;
+  /* Optional bit-packed per-query mask (what fdma_create_mask writes through fdma_mask_params::bits, together with
+   * the tile activity below): non-zero mask_bits says that `mask` points to uint32 words -- bit (k & 31) of word
+   * k >> 5 of a row is key k -- and that the three mask strides count WORDS; a row holds round_up(Sk,128)/32 words
+   * (bits of keys >= Sk are zero), base and strides multiples of 16 bytes. One eighth of the bool tensor's bytes on
+   * every pass of the forward and the backward. Taken by the tcgen05 kernels for masks with one row per query
+   * (mask_row_stride != 0; forward at d = 64 / 128 / 256, backward at d = 128) and only together with
+   * tile_activity; every other combination returns FDMA_ERR_UNSUPPORTED, and the caller expands the bits to bytes.
+   * No counterpart in the reference (its mask is always a bool tensor, flash_api.cpp:388-391). */
+  int32_t mask_bits;
+  int32_t reserved;
+  /* Optional, per-query masks: one byte per 128 x 128 tile, (B, h_mask, ceil(Sq/128), ceil(Sk/128)) contiguous,
+   * non-zero iff the tile holds a kept element (tiles wholly beyond the causal limit may be marked either way).
+   * When given, the kernels use it instead of deriving it from the mask into the workspace first. */
+  const uint8_t* tile_activity;
 } fdma_fwd_params;
 
 size_t fdma_fwd_workspace_bytes(const fdma_fwd_params* p);
@@ -173,6 +187,15 @@ typedef struct fdma_mask_params {
   void* slot_mask;
   int32_t capacity;
   int32_t reserved;
+  /* Optional bit-packed output for per-query masks (kind TOPK, no block smoothing, 16-bit bias rows of at most 32768
+   * keys with keys % 8 == 0): `bits` (out_b, out_h, out_rows, round_up(keys,128)/32) uint32, contiguous, bit (k & 31)
+   * of word k >> 5 = key k selected, and `activity` (out_b, out_h, ceil(out_rows/128), ceil(keys/128)) bytes, 1 for
+   * every 128 x 128 tile that holds a selected key and 0 otherwise. `bits` MUST BE ZERO-FILLED by the caller before
+   * the call (the kernel only sets bits); `activity` is written in full. With `bits` given, `out` may be NULL. These
+   * are the tensors fdma_fwd_params takes as mask (mask_bits = 1) and tile_activity. Other configurations return
+   * FDMA_ERR_UNSUPPORTED. */
+  uint32_t* bits;
+  uint8_t* activity;
 } fdma_mask_params;
 
 int fdma_create_mask(const fdma_mask_params* p, void* stream);

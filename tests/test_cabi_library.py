@@ -25,7 +25,7 @@ def test_library_exports_every_declared_symbol():
     lib = _lib.load()
     for name in _declared_functions():
         assert hasattr(lib, name), name
-    assert lib.fdma_version() == 10000
+    assert lib.fdma_version() == 10100
 
 
 def test_strerror_covers_every_status():
@@ -94,4 +94,4 @@ def test_struct_layout_matches_the_header(tmp_path):
             if fname == "f":
                 continue
             assert getattr(cls, fname).offset == int(want[f"{cname}.{fname}"]), f"{cname}.{fname}"
-    assert ctypes.sizeof(_lib.FwdParams) == 296  # the forward block is frozen: fdma_bwd_params embeds it first
+    assert ctypes.sizeof(_lib.FwdParams) == 312  # fdma_bwd_params embeds it first: growing it moves every later field
