@@ -183,3 +183,25 @@ def test_packed_visibility_matches_brute_force():
                     if not causal or j <= i + lk - lq:
                         want[cu_q[s] + i, cu_k[s] + j] = True
         assert torch.equal(got, want)
+
+
+def test_pack_mask_round_trip_and_tile_activity():
+    """`pack_mask` / `PackedMask.to_bool` on CPU tensors: bit k & 31 of word k >> 5 is key k, rows hold
+    round_up(Sk,128)/32 words with zero padding bits, one activity byte per 128 x 128 tile."""
+    from flash_sparse_attn.packed import PackedMask, pack_mask
+
+    g = torch.Generator().manual_seed(5)
+    mask = torch.rand((2, 3, 200, 333), generator=g) < 0.2
+    mask[:, :, :128, 128:256] = False          # an empty tile
+    mask[0, 0, 5, 31] = True                   # the sign bit of a word
+    packed = pack_mask(mask)
+    assert isinstance(packed, PackedMask) and packed.shape == (2, 3, 200, 333)
+    assert packed.bits.shape == (2, 3, 200, 12) and packed.bits.dtype == torch.int32
+    assert packed.activity.shape == (2, 3, 2, 3) and packed.activity.dtype == torch.uint8
+    assert torch.equal(packed.to_bool(), mask)
+    assert (packed.bits[0, 0, 5, 0].item() >> 31) & 1 == 1
+    assert packed.bits[..., 10].bitwise_and(~((1 << 13) - 1)).eq(0).all()   # keys 333..351 of word 10 stay zero
+    assert packed.bits[..., 11].eq(0).all()
+    assert packed.activity[:, :, 0, 1].eq(0).all() and packed.activity[:, :, 0, 0].ne(0).all()
+    want = torch.nn.functional.pad(mask, [0, 51, 0, 56]).reshape(2, 3, 2, 128, 3, 128).any(dim=5).any(dim=3)
+    assert torch.equal(packed.activity != 0, want)
