@@ -675,7 +675,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             ln = fn(sec_args, 0, 1, local_rank)
             secondary[name] = {"metric": ln["metric"], "ms_per_step": ln["ms_per_step"], "value": ln["value"],
                                "unit": ln["unit"], "roofline": ln["roofline"], "workload": ln["config"]["workload"]}
-            for extra in ("fwd_ms", "bwd_ms", "decode_kernel_ms", "packed_mask"):
+            for extra in ("fwd_ms", "bwd_ms", "decode_kernel_ms", "bool_mask"):
                 if extra in ln:
                     secondary[name][extra] = ln[extra]
             torch.cuda.empty_cache()
@@ -1035,7 +1035,12 @@ def measure_perquery(args, rank: int, world: int, local_rank: int):
     del vis
     flops = 4 * D * 128 * 128 * tiles_f + 10 * D * 64 * 128 * tiles_b
     stream = torch.cuda.current_stream(dev)
-    step = AttentionStep(lib, dev, q, k, v, mask, bias, dout, False)
+    # As flash_sparse_attn_func does for a mask that create_mask made: the kernels read the bit-packed form and the
+    # tile activity create_mask wrote in the same launch (cached on the mask tensor) instead of the bool bytes.
+    from flash_sparse_attn import flash_sparse_attn_interface as iface
+
+    packed = iface._cached_packed_mask(mask)
+    step = AttentionStep(lib, dev, q, k, v, mask, bias, dout, False, packed=packed)
     for _ in range(max(args.warmup, 3)):
         step()
     ms_total, fwd_ms, bwd_ms = time_steps(step, args.steps, stream, lambda: torch.cuda.synchronize(dev))
@@ -1049,49 +1054,29 @@ def measure_perquery(args, rank: int, world: int, local_rank: int):
         "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"per-query: B=1 S={Sq} Hq={HQ} Hkv={HKV} d={D} W={w} causal, bias and mask (B,Hkv,Sq,Sk)",
-                   "l2": "bias (1 GiB) and mask (0.5 GiB) are larger than L2",
+                   "l2": "bias (1 GiB) and mask (0.5 GiB bool, 64 MiB bit-packed) are larger than L2",
+                   "mask_form": ("bit-packed + tile activity, as create_mask leaves them beside the bool tensor"
+                                 if packed is not None else "bool bytes"),
                    "tiles": {"fwd": list(FWD_TILE), "bwd": list(BWD_TILE)}},
         "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
         "roofline": {"bound": "tensor", "kernel": "bwd_kernel", "achieved": bwd_tf, "peak": peak, "unit": "TFLOP/s",
                      "frac": bwd_tf / peak, "peak_source": peak_src, "frac_sustained": bwd_tf / pk["sustained"],
                      "traffic": None},
-        "gpu_launches": args.steps * 5,  # tile_activity x2, fwd_kernel, bwd_prep, bwd_kernel (+ convert_dq)
+        # fwd_kernel, bwd_prep, bwd_kernel, 2 partial reductions, convert_dq (+ 2 tile_activity with a bool mask)
+        "gpu_launches": args.steps * (6 if packed is not None else 8),
     }
-    # The same step with the mask as one bit per key + tile activity (create_packed_mask): what the library offers in
-    # place of the reference's bool tensor for per-query masks. Reported beside the line, never mixed into it.
-    try:
-        from flash_sparse_attn.utils.mask import create_packed_mask
-
-        del step
-        md = torch.finfo(torch.bfloat16).min
-        packed = create_packed_mask(bias, None, B, Sq, Sq, w, md)
-        assert torch.equal(packed.to_bool(), mask), "packed mask differs from create_mask"
-        pstep = AttentionStep(lib, dev, q, k, v, mask, bias, dout, False, packed=packed)
-        for _ in range(max(args.warmup, 3)):
-            pstep()
-        p_total, p_fwd, p_bwd = time_steps(pstep, args.steps, stream, lambda: torch.cuda.synchronize(dev))
-        _lib.check(lib.fdma_last_kernel_status(stream.cuda_stream, None), "kernel status")
-
-        def timed(fn, n=5):
-            for _ in range(2):
-                fn()
-            torch.cuda.synchronize(dev)
-            a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record(stream)
-            for _ in range(n):
-                fn()
-            b_.record(stream)
-            torch.cuda.synchronize(dev)
-            return a.elapsed_time(b_) / n
-
-        line["packed_mask"] = {
-            "what": "same step, mask as 1 bit per key + tile activity (64 MiB instead of 512 MiB)",
-            "ms_per_step": p_total / args.steps, "fwd_ms": p_fwd, "bwd_ms": p_bwd,
-            "create_packed_mask_ms": timed(lambda: create_packed_mask(bias, None, B, Sq, Sq, w, md)),
-            "create_mask_ms": timed(lambda: create_mask(bias, None, B, Sq, Sq, w, md)),
-        }
-    except Exception as e:  # the comparison is an extra: never let it take the line down
-        line["packed_mask"] = {"unavailable": str(e)[:200]}
+    if packed is not None:  # the same step reading the bool tensor (what a mask from elsewhere gets)
+        try:
+            del step
+            bstep = AttentionStep(lib, dev, q, k, v, mask, bias, dout, False)
+            for _ in range(max(args.warmup, 3)):
+                bstep()
+            b_total, b_fwd, b_bwd = time_steps(bstep, args.steps, stream, lambda: torch.cuda.synchronize(dev))
+            _lib.check(lib.fdma_last_kernel_status(stream.cuda_stream, None), "kernel status")
+            line["bool_mask"] = {"what": "same step, kernels read the bool tensor and derive the tile activity themselves",
+                                 "ms_per_step": b_total / args.steps, "fwd_ms": b_fwd, "bwd_ms": b_bwd}
+        except Exception as e:  # an extra: never let it take the line down
+            line["bool_mask"] = {"unavailable": str(e)[:200]}
     return line
 
 

@@ -93,6 +93,16 @@ def _cached_kept_keys(attn_mask, seqlen_k):
     return None
 
 
+def _cached_packed_mask(attn_mask):
+    """The bit-packed form `create_mask` wrote together with this per-query bool mask, if the mask is unchanged."""
+    if torch.compiler.is_compiling() or not isinstance(attn_mask, torch.Tensor):
+        return None
+    tag = getattr(attn_mask, "_fdma_packed", None)
+    if tag is not None and tag[1] == attn_mask._version and tuple(tag[0].shape) == tuple(attn_mask.shape):
+        return tag[0]
+    return None
+
+
 def _raise_if_kernel_timed_out(lib) -> None:
     """A tcgen05 kernel whose bounded wait gave up leaves partly written results behind and a code in page-locked
     host memory. Checked (one host load, no GPU work) at the entry of every operator call, so that the failure
@@ -442,6 +452,13 @@ def flash_sparse_attn_func(
             attn_mask = attn_mask.to_bool()
         else:
             return flash_sparse_attn_packed_func(query, key, value, attn_mask, attn_bias, softmax_scale, is_causal,
+                                                 deterministic)
+    cached = _cached_packed_mask(attn_mask)
+    if cached is not None and not softcap and not return_attn_probs and query.dim() == 4:
+        from .packed import _native, flash_sparse_attn_packed_func
+
+        if _native(query, key, cached, attn_bias, True):
+            return flash_sparse_attn_packed_func(query, key, value, cached, attn_bias, softmax_scale, is_causal,
                                                  deterministic)
     d = query.shape[-1]
     needs_grad = torch.is_grad_enabled() and any(t.requires_grad for t in (query, key, value))

@@ -61,12 +61,13 @@ def _launch(attention_bias, attention_mask, window_size, min_dtype, block_size, 
     if kind == _lib.MASK_TOPK and window_size > keys:
         raise RuntimeError("selected index k out of range")  # what torch.topk raises in the reference
     out = torch.empty(out_shape, dtype=torch.bool, device=bias.device) if positions not in ("only", "bits") else None
+    want_bits = positions in ("bits", "bits_also")
     p = _lib.MaskParams()
     p.bias, p.premask = bias.data_ptr(), (pm.data_ptr() if pm is not None else None)
     p.out = out.data_ptr() if out is not None else None
     kept = None
     packed = None
-    if positions == "bits":  # one bit per key (zero-filled: the kernel only sets bits) + tile activity
+    if want_bits:  # one bit per key (zero-filled: the kernel only sets bits) + tile activity
         from ..packed import PackedMask
 
         words = (keys + _TILE - 1) // _TILE * (_TILE // 32)
@@ -75,7 +76,7 @@ def _launch(attention_bias, attention_mask, window_size, min_dtype, block_size, 
                           dtype=torch.uint8, device=bias.device)
         p.bits, p.activity = bits.data_ptr(), act.data_ptr()
         packed = PackedMask(bits, act, keys)
-    elif positions != "none":
+    elif positions in ("also", "only"):
         cap = max(_TILE, (min(int(window_size), keys) + _TILE - 1) // _TILE * _TILE)
         lead = tuple(out_shape[:2]) if out_shape[2] == 1 else tuple(out_shape[:3])
         key_pos = torch.empty(lead + (cap,), dtype=torch.int32, device=bias.device)
@@ -100,11 +101,16 @@ def _launch(attention_bias, attention_mask, window_size, min_dtype, block_size, 
     with torch.cuda.device(bias.device):
         stream = torch.cuda.current_stream(bias.device).cuda_stream
         status = lib.fdma_create_mask(ctypes.byref(p), stream)
-        if positions == "bits" and status == _lib.ERR_UNSUPPORTED:
-            return None  # the caller builds the bool mask and packs it
+        if want_bits and status == _lib.ERR_UNSUPPORTED:
+            if positions == "bits":
+                return None  # the caller builds the bool mask and packs it
+            p.bits, p.activity, packed = None, None, None  # bool mask alone
+            status = lib.fdma_create_mask(ctypes.byref(p), stream)
         _lib.check(status, "fdma_create_mask")
     if positions == "bits":
         return packed
+    if positions == "bits_also":
+        return out, packed
     if positions == "only":
         return kept
     return (out, kept) if positions == "also" else out
@@ -191,6 +197,17 @@ def create_mask(
             # to the mask's current contents (any in-place edit invalidates it).
             mask, kept = _topk_mask_with_positions(attention_bias, attention_mask, window_size, min_dtype)
             mask._fdma_kept = (kept, mask._version)
+            return mask
+        if (rows > 1 and (block_size is None or block_size <= 1) and 0 < window_size <= attention_bias.shape[-1]
+                and attention_bias.is_cuda and attention_bias.dim() == 4):
+            # Per-query selection: the same launch also writes the mask as one bit per key, and a small kernel derives
+            # the tile activity from the bits. Both ride on the returned tensor as a cache (tied to its version
+            # counter like the position list above); `flash_sparse_attn_func` hands them to the kernels, which then
+            # read an eighth of the mask bytes and need no activity pass of their own over the bool tensor.
+            mask, packed = _launch(attention_bias, attention_mask, window_size, min_dtype, None, _lib.MASK_TOPK,
+                                   positions="bits_also")
+            if packed is not None:
+                mask._fdma_packed = (packed, mask._version)
             return mask
         return topk_mask(attention_bias, attention_mask, window_size, min_dtype, block_size)
     if type == "relu":

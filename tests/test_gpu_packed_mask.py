@@ -91,3 +91,40 @@ def test_attention_with_a_packed_mask(dev, geom, bias_shape, causal, dtype):
     check("dv", vl.grad.cpu(), ref[4], dtype, reduced=True)
     if bl is not None:
         check("dbias", bl.grad.cpu(), ref[5], dtype, reduced=True)
+
+
+def test_create_mask_leaves_the_packed_form_on_a_per_query_mask(dev):
+    """`create_mask` on a per-query bias returns the reference's bool tensor and caches the bit-packed form on it;
+    `flash_sparse_attn_func` then reads the bits (checked through the result against the oracle), an in-place edit of
+    the mask voids the cache, and a row-broadcast mask gets the position list instead."""
+    from flash_sparse_attn import flash_sparse_attn_func
+    from flash_sparse_attn import flash_sparse_attn_interface as iface
+    from flash_sparse_attn.utils.mask import create_mask
+
+    B, Sq, Sk, H, Hk, d = 1, 256, 384, 4, 2, 128
+    q, k, v, bias, dout = oracle.make_inputs(B, Sq, Sk, H, Hk, d, (B, Hk, Sq, Sk), seed=31, dtype=torch.bfloat16)
+    md = torch.finfo(torch.bfloat16).min
+    want_mask = oracle.create_mask(bias, None, B, Sq, Sk, 96, md)
+    mask = create_mask(bias.to(dev), None, B, Sq, Sk, 96, md)
+    assert mask.dtype == torch.bool and torch.equal(mask.cpu(), want_mask)
+    cached = iface._cached_packed_mask(mask)
+    assert cached is not None and torch.equal(cached.to_bool(), mask)
+    ref = oracle.attention_forward_backward(q, k, v, want_mask, bias, dout, None, True)
+    ql, kl, vl, bl = (t.to(dev).requires_grad_(True) for t in (q, k, v, bias))
+    out = flash_sparse_attn_func(ql, kl, vl, attn_mask=mask, attn_bias=bl, is_causal=True)
+    out.backward(dout.to(dev))
+    torch.cuda.synchronize()
+    _kernel_status_ok()
+    check("out", out.detach().cpu(), ref[0], torch.bfloat16)
+    check("dq", ql.grad.cpu(), ref[2], torch.bfloat16)
+    check("dbias", bl.grad.cpu(), ref[5], torch.bfloat16, reduced=True)
+    # an edited mask must be read as it is now
+    mask[0, 0, 10, :] = False
+    assert iface._cached_packed_mask(mask) is None
+    want_mask[0, 0, 10, :] = False
+    ref2 = oracle.attention_forward_backward(q, k, v, want_mask, bias, dout, None, True)
+    out2 = flash_sparse_attn_func(ql.detach(), kl.detach(), vl.detach(), attn_mask=mask, attn_bias=bl.detach(), is_causal=True)
+    check("out", out2.cpu(), ref2[0], torch.bfloat16)
+    # row-broadcast: position list, no packed form
+    rb = create_mask(bias[:, :, :1].to(dev), None, B, Sq, Sk, 96, md)
+    assert iface._cached_packed_mask(rb) is None and iface._cached_kept_keys(rb, Sk) is not None
