@@ -476,9 +476,7 @@ __global__ void __launch_bounds__(kThreads, CHUNKS <= 4 ? 4 : 1) topk16_reg_kern
     if (kPos || bits_row) {  // bit j of the chunk's byte = key k + j selected
       const uint32_t b8 = (((o.x & 0x01010101u) * 0x01020408u) >> 24) | ((((o.y & 0x01010101u) * 0x01020408u) >> 24) << 4);
       if (kPos) selbits[c >> 2] |= b8 << ((c & 3) * 8);
-      if (bits_row && b8) {
-        bits_row[k >> 3] = static_cast<uint8_t>(b8);   // (the row was zero-filled by the caller)
-      }
+      if (bits_row) bits_row[k >> 3] = static_cast<uint8_t>(b8);  // every byte of keys [0, n); the caller zeroed the rest
     }
   };
   if (all_eq) {  // every key equal to the threshold is kept

@@ -67,11 +67,12 @@ def _launch(attention_bias, attention_mask, window_size, min_dtype, block_size, 
     p.out = out.data_ptr() if out is not None else None
     kept = None
     packed = None
-    if want_bits:  # one bit per key (zero-filled: the kernel only sets bits) + tile activity
+    if want_bits:  # one bit per key (the kernel writes keys [0, keys); padding bits must be zero) + tile activity
         from ..packed import PackedMask
 
         words = (keys + _TILE - 1) // _TILE * (_TILE // 32)
-        bits = torch.zeros(tuple(out_shape[:3]) + (words,), dtype=torch.int32, device=bias.device)
+        alloc = torch.empty if keys % _TILE == 0 else torch.zeros
+        bits = alloc(tuple(out_shape[:3]) + (words,), dtype=torch.int32, device=bias.device)
         act = torch.empty(tuple(out_shape[:2]) + ((out_shape[2] + 127) // 128, (keys + _TILE - 1) // _TILE),
                           dtype=torch.uint8, device=bias.device)
         p.bits, p.activity = bits.data_ptr(), act.data_ptr()

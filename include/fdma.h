@@ -190,8 +190,9 @@ typedef struct fdma_mask_params {
   /* Optional bit-packed output for per-query masks (kind TOPK, no block smoothing, 16-bit bias rows of at most 32768
    * keys with keys % 8 == 0): `bits` (out_b, out_h, out_rows, round_up(keys,128)/32) uint32, contiguous, bit (k & 31)
    * of word k >> 5 = key k selected, and `activity` (out_b, out_h, ceil(out_rows/128), ceil(keys/128)) bytes, 1 for
-   * every 128 x 128 tile that holds a selected key and 0 otherwise. `bits` MUST BE ZERO-FILLED by the caller before
-   * the call (the kernel only sets bits); `activity` is written in full. With `bits` given, `out` may be NULL. These
+   * every 128 x 128 tile that holds a selected key and 0 otherwise. The kernel writes the bits of keys [0, keys) of
+   * every row and `activity` in full; when keys is not a multiple of 128 the caller zero-fills `bits` first (the
+   * padding bits of each row's last words must read 0). With `bits` given, `out` may be NULL. These
    * are the tensors fdma_fwd_params takes as mask (mask_bits = 1) and tile_activity. Other configurations return
    * FDMA_ERR_UNSUPPORTED. */
   uint32_t* bits;
