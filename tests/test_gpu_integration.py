@@ -47,6 +47,31 @@ def test_forward_matches_oracle(dev, window, fp32_in):
     check("out", out.cpu(), ref, dtype)
 
 
+def test_per_query_bias_through_the_caller(dev):
+    """A bias with one row per query: the caller's `create_mask` leaves the bit-packed mask beside the bool tensor
+    and the attention call reads it; result and the gradient of the bias against the oracle."""
+    from flash_sparse_attn.integrations import flash_sparse_attention_forward
+
+    B, S, H, Hk, d, window = 1, 384, 4, 2, 128, 96
+    dtype = torch.bfloat16
+    q, k, v, bias, dout = oracle.make_inputs(B, S, S, H, Hk, d, (B, Hk, S, S), seed=13, dtype=dtype)
+    # values distinct within a row: the selection then has no ties and equals the oracle's
+    g = torch.Generator().manual_seed(14)
+    bias = (torch.argsort(torch.rand((B, Hk, S, S), generator=g), dim=-1).float() / S - 0.5).to(dtype)
+    want_mask = oracle.create_mask(bias, None, B, S, S, window, torch.finfo(dtype).min)
+    ref = oracle.attention_forward_backward(q, k, v, want_mask, bias, dout, d ** -0.5, True)
+    module = _Attn(dtype).to(dev)
+    ql = q.to(dev).transpose(1, 2).requires_grad_(True)
+    bl = bias.to(dev).requires_grad_(True)
+    out, _ = flash_sparse_attention_forward(module, ql, k.to(dev).transpose(1, 2), v.to(dev).transpose(1, 2), None, bl,
+                                            scaling=d ** -0.5, window_size=window)
+    out.backward(dout.to(dev))
+    torch.cuda.synchronize()
+    check("out", out.detach().cpu(), ref[0], dtype)
+    check("dq", ql.grad.transpose(1, 2).cpu(), ref[2], dtype)
+    check("dbias", bl.grad.cpu(), ref[5], dtype, reduced=True)
+
+
 @pytest.mark.parametrize("side", ["right", "left"])
 @pytest.mark.parametrize("lengths", [(256, 100, 37), (256, 256, 200)])
 def test_padding_mask_matches_unpadded_attention(dev, side, lengths):
